@@ -1,0 +1,103 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Every kernel here is launched through an extern "C" function that takes raw
+// device pointers, sizes and a CUDA stream; the Python side (csrc/ops.py) checks
+// shapes, types and contiguity before it calls.  Element types are passed as an
+// integer code so that one entry point serves the bfloat16 and the float32 path.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define BN_F32 0
+#define BN_BF16 1
+
+// Tokens per cache page.  A sequence holds whole pages; position p of a sequence
+// lies in page_table[slot][p / BN_PAGE] at row p % BN_PAGE.
+#define BN_PAGE 64
+
+// Launch status: 0 ok, otherwise a code that csrc/ops.py turns into an exception.
+#define BN_OK 0
+#define BN_ERR_BAD_ARG 1
+#define BN_ERR_LAUNCH 2
+
+#define BN_CHECK_LAUNCH()                                    \
+  do {                                                       \
+    cudaError_t e__ = cudaGetLastError();                    \
+    if (e__ != cudaSuccess) return BN_ERR_LAUNCH + (int)e__; \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Load/store of one element of a buffer whose type is only known by code.
+__device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i) {
+  return dtype == BN_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ __forceinline__ void store_from_f32(void* p, int dtype, size_t i, float v) {
+  if (dtype == BN_F32) ((float*)p)[i] = v;
+  else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `scratch` holds 32 floats.
+// Every thread gets the result.  The order of additions depends only on the
+// block size, never on what else runs, so a row's result does not change with
+// the batch around it.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (threadIdx.x < nwarp) ? scratch[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    r = warp_sum(r);
+    if (lane == 0) scratch[0] = r;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (threadIdx.x < nwarp) ? scratch[threadIdx.x] : -INFINITY;
+  if (warp == 0) {
+    r = warp_max(r);
+    if (lane == 0) scratch[0] = r;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+// Address of row (p % BN_PAGE) of key/value head `kvh` in the page that holds position p.
+// Cache layout per schedule entry: [n_pages][n_kv_heads][BN_PAGE][head_dim].
+__device__ __forceinline__ size_t cache_row_offset(const int* page_table_row, int p,
+                                                   int n_kv_heads, int kvh, int head_dim) {
+  int page = page_table_row[p / BN_PAGE];
+  return (((size_t)page * n_kv_heads + kvh) * BN_PAGE + (p % BN_PAGE)) * (size_t)head_dim;
+}

@@ -1,0 +1,254 @@
+"""Python face of the CUDA kernels: argument checks, then a ``ctypes`` call on the current stream.
+
+Every function here launches hand-written kernels from this folder (matrix products
+with many rows go to cuBLAS through ``torch.matmul``, as the reference's prefill does
+with ``cublasGemmEx``/``cublasSgemm``, src/gpu_cuda.cu:11788-11879).  Nothing falls
+back to the CPU: tensors that are not on a CUDA device are refused.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+PAGE = 64  # tokens per cache page; must equal BN_PAGE in common.cuh
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got {tuple(t.shape)}")
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == 1:
+        raise KernelError(f"{what}: sizes or pointers refused by the kernel launcher")
+    raise KernelError(f"{what}: CUDA launch failed with error {status - 2}")
+
+
+def _fn(family: str, name: str):
+    f = getattr(build.library(family), name)
+    f.restype = c_int
+    return f
+
+
+# ---- embedding ----------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, bad_token: torch.Tensor,
+                 scale: float = 1.0) -> torch.Tensor:
+    """out[t] = float32(table[tokens[t]]) * scale; sets bad_token[0] = 1 on an id outside the table."""
+    _need(table, "table", dims=2)
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(out, "out", torch.float32, 2)
+    _need(bad_token, "bad_token", torch.int32)
+    n, width = tokens.shape[0], table.shape[1]
+    if out.shape[0] < n or out.shape[1] != width:
+        raise KernelError(f"out {tuple(out.shape)} does not hold {n} rows of width {width}")
+    _check(_fn("embed", "bn_embed_gather")(_ptr(table), _code(table), _ptr(tokens), _ptr(out), c_int(n),
+                                           c_int(width), c_int(table.shape[0]), c_float(scale),
+                                           _ptr(bad_token), _stream()), "embed_gather")
+    return out
+
+
+# ---- norm ---------------------------------------------------------------------------------
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
+    """x += delta (if given), out = rmsnorm(x) * weight.  With ``rows`` only those rows are read
+    and ``out`` holds them densely; x is then left as it is."""
+    _need(x, "x", torch.float32, 2)
+    _need(weight, "weight", dims=1)
+    _need(out, "out", dims=2)
+    width = x.shape[1]
+    if weight.shape[0] != width or out.shape[1] != width:
+        raise KernelError(f"widths differ: x {width}, weight {weight.shape[0]}, out {out.shape[1]}")
+    if delta is not None:
+        _need(delta, "delta", dims=2)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows, write_x = rows.shape[0], False
+    else:
+        n_rows = x.shape[0]
+    if out.shape[0] < n_rows:
+        raise KernelError(f"out has {out.shape[0]} rows, {n_rows} are written")
+    _check(_fn("norm", "bn_add_rmsnorm")(_ptr(x), _ptr(delta), c_int(_code(delta) if delta is not None else 0),
+                                         _ptr(weight), c_int(_code(weight)), _ptr(out), c_int(_code(out)),
+                                         _ptr(rows), c_int(n_rows), c_int(width), c_float(eps),
+                                         c_int(1 if write_x else 0), _stream()), "add_rmsnorm")
+    return out
+
+
+# ---- activation ---------------------------------------------------------------------------
+def silu_mul(h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(h[t, i]) * h[t, I + i] for rows h = [gate | up]."""
+    _need(h, "h", dims=2)
+    _need(out, "out", h.dtype, 2)
+    inter = h.shape[1] // 2
+    if h.shape[1] != 2 * inter or out.shape != (h.shape[0], inter):
+        raise KernelError(f"silu_mul: h {tuple(h.shape)} and out {tuple(out.shape)} do not fit")
+    _check(_fn("act", "bn_silu_mul")(_ptr(h), _ptr(out), c_int(_code(h)), c_int(h.shape[0]), c_int(inter),
+                                     _stream()), "silu_mul")
+    return out
+
+
+# ---- rotary + cache append ----------------------------------------------------------------
+def rope_append(x: torch.Tensor, n_rot_heads: int, head_dim: int, rotary_dims: int, theta_scale: float,
+                tok_pos: torch.Tensor, *, k_off: int = 0, v_off: int = 0, n_kv_heads: int = 0,
+                tok_seq: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                page_table: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
+                v_cache: Optional[torch.Tensor] = None) -> None:
+    """Rotate the first ``n_rot_heads`` heads of every row of x in place; when a cache is given,
+    write the key heads at ``k_off`` and the value heads at ``v_off`` of each row into it."""
+    _need(x, "x", dims=2)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    n = tok_pos.shape[0]
+    if x.shape[0] < n or n_rot_heads * head_dim > x.shape[1]:
+        raise KernelError("rope_append: x is too small for the heads and tokens given")
+    pt_stride = 0
+    if k_cache is not None:
+        for t, nm in ((tok_seq, "tok_seq"), (slots, "slots")):
+            _need(t, nm, torch.int32, 1)
+        _need(page_table, "page_table", torch.int32, 2)
+        _need(k_cache, "k_cache", x.dtype, 4)
+        _need(v_cache, "v_cache", x.dtype, 4)
+        if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+            raise KernelError(f"rope_append: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+        if max(k_off, v_off) + n_kv_heads * head_dim > x.shape[1]:
+            raise KernelError("rope_append: key/value offsets run past the row")
+        pt_stride = page_table.shape[1]
+    _check(_fn("rope", "bn_rope_append")(_ptr(x), c_int(_code(x)), c_int(n), c_int(x.shape[1]), c_int(n_rot_heads),
+                                         c_int(head_dim), c_int(rotary_dims), c_float(theta_scale), _ptr(tok_pos),
+                                         c_int(k_off), c_int(v_off), c_int(n_kv_heads), _ptr(tok_seq), _ptr(slots),
+                                         _ptr(page_table), c_int(pt_stride), _ptr(k_cache), _ptr(v_cache),
+                                         _stream()), "rope_append")
+
+
+# ---- attention ----------------------------------------------------------------------------
+def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_tokens: int, n_heads: int,
+                      n_kv_heads: int, head_dim: int, scale: float, window: int, tok_seq: torch.Tensor,
+                      tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
+    """Causal attention of every new token over its sequence's pages; q may be a view into a wider row."""
+    if not q.is_cuda or q.stride(-1) != 1:
+        raise KernelError("attention: q must be a CUDA tensor with unit inner stride")
+    _need(out, "out", q.dtype, 2)
+    for t, nm in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", q.dtype, 4)
+    _need(v_cache, "v_cache", q.dtype, 4)
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention: head_dim={head_dim} must be a multiple of 16 up to 256")
+    if n_heads % n_kv_heads:
+        raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+    if out.shape[0] < n_tokens or out.shape[1] != n_heads * head_dim:
+        raise KernelError("attention: out does not fit")
+    _check(_fn("attention", "bn_attention_general")(
+        _ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), c_int(_code(q)), c_int(n_tokens), c_int(n_heads),
+        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), _ptr(tok_seq), _ptr(tok_pos),
+        _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()),
+        "attention_general")
+    return out
+
+
+# ---- matrix products ----------------------------------------------------------------------
+SKINNY_MAX_ROWS = 16
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is."""
+    _need(x, "x", dims=2)
+    _need(w, "w", dims=2)
+    if x.shape[1] != w.shape[1]:
+        raise KernelError(f"linear: x {tuple(x.shape)} and w {tuple(w.shape)} do not share the inner size")
+    out_dtype = out_dtype or x.dtype
+    if x.dtype != w.dtype:
+        x = x.to(w.dtype)
+    M, K = x.shape
+    N = w.shape[0]
+    if M <= SKINNY_MAX_ROWS and K % 8 == 0:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        _check(_fn("linear", "bn_linear_skinny")(_ptr(x), _ptr(w), c_int(_code(w)), _ptr(out), c_int(_DT[out_dtype]),
+                                                 c_int(M), c_int(N), c_int(K), c_int(N), _stream()), "linear_skinny")
+        return out
+    # Many rows: the library product, float32 accumulation, no reduced-precision float32 mode.
+    if w.dtype == torch.float32:
+        if torch.backends.cuda.matmul.allow_tf32:
+            raise KernelError("float32 products need torch.backends.cuda.matmul.allow_tf32 = False")
+        y = torch.matmul(x, w.t())
+    elif out_dtype == torch.float32:
+        y = torch.mm(x, w.t(), out_dtype=torch.float32)
+    else:
+        y = torch.matmul(x, w.t())
+    return y if y.dtype == out_dtype else y.to(out_dtype)
+
+
+# ---- sampling -----------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, "logits", torch.float32, 2)
+    out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, 1)
+    _check(_fn("sampling", "bn_argmax")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
+                                        c_int(logits.shape[1]), _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample_temperature(logits: torch.Tensor, temperature: float, rng_state: torch.Tensor,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One draw per row from softmax(logits / temperature); rng_state holds one xorshift64* state
+    per row (int64 bit patterns) and is advanced by one draw."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(rng_state, "rng_state", torch.int64, 1)
+    if rng_state.shape[0] < logits.shape[0]:
+        raise KernelError("sample_temperature: one generator state per row is needed")
+    out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, 1)
+    _check(_fn("sampling", "bn_sample_temperature")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
+                                                    c_int(logits.shape[1]), c_float(temperature), _ptr(rng_state),
+                                                    _ptr(out), _stream()), "sample_temperature")
+    return out
+
+
+def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch.Tensor, penalty: float) -> None:
+    """In place: for each distinct id among the first recent_len[r] entries of recent[r],
+    logit > 0 ? logit / penalty : logit * penalty."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(recent, "recent", torch.int32, 2)
+    _need(recent_len, "recent_len", torch.int32, 1)
+    _check(_fn("sampling", "bn_repeat_penalty")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
+                                                c_int(logits.shape[1]), _ptr(recent), c_int(recent.shape[1]),
+                                                _ptr(recent_len), c_float(penalty), _stream()), "repeat_penalty")

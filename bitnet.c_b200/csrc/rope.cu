@@ -1,0 +1,72 @@
+// Rotary position encoding of the query and key heads of a packed row, fused with
+// the write of the new keys and values into the paged cache.
+//
+// Reference: pairs (i, i + rotary_dims/2) are rotated,
+//   x[i] = a cos - b sin,  x[i + half] = a sin + b cos   (src/transformer/cpu_backend.c:283-296)
+// with angle_0 = pos and angle_{i+1} = angle_i * theta^(-2/rotary_dims) as a running
+// float32 product (src/model_arch.c:322-338, src/transformer.c:143-162); keys are
+// stored rotated and values as they are (src/transformer/cpu.c:859-898).
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ x, int row_stride, int n_rot_heads, int head_dim,
+                                   int rotary_dims, float theta_scale, const int* __restrict__ tok_pos,
+                                   int k_off, int v_off, int n_kv_heads, const int* __restrict__ tok_seq,
+                                   const int* __restrict__ slots, const int* __restrict__ page_table,
+                                   int pt_stride, T* __restrict__ k_cache,
+                                   T* __restrict__ v_cache) {
+  int t = blockIdx.x;
+  int pos = tok_pos[t];
+  T* row = x + (size_t)t * row_stride;
+  int half = rotary_dims >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float angle = (float)pos;
+    for (int k = 0; k < i; ++k) angle *= theta_scale;
+    float s, c;
+    sincosf(angle, &s, &c);
+    for (int h = 0; h < n_rot_heads; ++h) {
+      T* hd = row + (size_t)h * head_dim;
+      float a = to_f32<T>(hd[i]), b = to_f32<T>(hd[i + half]);
+      hd[i] = from_f32<T>(a * c - b * s);
+      hd[i + half] = from_f32<T>(a * s + b * c);
+    }
+  }
+  if (!k_cache) return;
+  __syncthreads();
+  int slot = slots[tok_seq[t]];
+  const int* pt = page_table + (size_t)slot * pt_stride;
+  int n = n_kv_heads * head_dim;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    int kvh = e / head_dim, d = e - kvh * head_dim;
+    size_t off = cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d;
+    k_cache[off] = row[k_off + e];
+    v_cache[off] = row[v_off + e];
+  }
+}
+
+// x: [n_tokens, row_stride] with the heads to rotate first in each row.  When k_cache is
+// not null the n_kv_heads key heads at element offset k_off (already rotated if they are
+// among the first n_rot_heads) and the value heads at v_off are written to the cache.
+extern "C" int bn_rope_append(void* x, int dtype, int n_tokens, int row_stride, int n_rot_heads, int head_dim,
+                              int rotary_dims, float theta_scale, const int* tok_pos, int k_off, int v_off,
+                              int n_kv_heads, const int* tok_seq, const int* slots, const int* page_table,
+                              int pt_stride, void* k_cache, void* v_cache,
+                              cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (head_dim <= 0 || rotary_dims < 0 || rotary_dims > head_dim || (rotary_dims & 1)) return BN_ERR_BAD_ARG;
+  if (k_cache && (!v_cache || !tok_seq || !slots || !page_table)) return BN_ERR_BAD_ARG;
+  int threads = 128;
+  if (dtype == BN_F32)
+    rope_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        (float*)x, row_stride, n_rot_heads, head_dim, rotary_dims, theta_scale, tok_pos, k_off, v_off,
+        n_kv_heads, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache);
+  else if (dtype == BN_BF16)
+    rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (__nv_bfloat16*)x, row_stride, n_rot_heads, head_dim, rotary_dims, theta_scale, tok_pos, k_off, v_off,
+        n_kv_heads, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache,
+        (__nv_bfloat16*)v_cache);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}

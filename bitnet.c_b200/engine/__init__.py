@@ -1,0 +1,5 @@
+"""The engine: the model with its step function, and the generation loop above it."""
+from .batch import SeqStep, StepContext, pack_step
+from .model import Model, StepError, parameter_table, resolve_dtype
+
+__all__ = ["SeqStep", "StepContext", "pack_step", "Model", "StepError", "parameter_table", "resolve_dtype"]

@@ -1,0 +1,73 @@
+"""One step's batch: which sequences run, with which new tokens, at which positions.
+
+A step brings, for each sequence, one or more new tokens.  Tokens of all sequences
+are packed into one row dimension ``[T]``; for every packed token the device knows
+its sequence (``tok_seq``) and its position in that sequence (``tok_pos``), and for
+every sequence its slot.  Kernels work from these arrays alone, so prompts of unequal
+length, pieces of prompts and single decoded tokens all take the same path, and no
+padding exists that could change a result.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class SeqStep:
+    """The next tokens of one sequence and the places among them whose logits are wanted."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepContext:
+    n_seqs: int
+    n_tokens: int
+    tokens: torch.Tensor  # [T] int32
+    tok_seq: torch.Tensor  # [T] int32: index into this step's sequences
+    tok_pos: torch.Tensor  # [T] int32: position within the sequence
+    slots: torch.Tensor  # [n_seqs] int32
+    seq_start: torch.Tensor  # [n_seqs + 1] int32: first packed row of each sequence
+    seq_pos0: torch.Tensor  # [n_seqs] int32: sequence length before this step
+    rows: Optional[torch.Tensor]  # [n_wanted] int32 packed rows whose logits are wanted
+    max_new: int  # longest run of new tokens in this step
+    max_len: int  # longest sequence after this step
+    decode: bool  # every sequence brings exactly one token
+    host_new: List[int] = field(default_factory=list)
+    host_pos0: List[int] = field(default_factory=list)
+
+
+def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepContext:
+    """Build the device arrays of a step with one host-to-device copy."""
+    n = len(seqs)
+    new = [len(s.tokens) for s in seqs]
+    T = sum(new)
+    n_rows = sum(len(s.want) for s in seqs)
+    buf = np.empty(3 * T + 3 * n + 1 + n_rows, dtype=np.int32)
+    tokens, tok_seq, tok_pos = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
+    o = 3 * T
+    slots, seq_start, seq_pos0, rows = buf[o:o + n], buf[o + n:o + 2 * n + 1], buf[o + 2 * n + 1:o + 3 * n + 1], buf[o + 3 * n + 1:]
+    at, r = 0, 0
+    for i, s in enumerate(seqs):
+        c = new[i]
+        tokens[at:at + c] = np.asarray(s.tokens, dtype=np.int64)
+        tok_seq[at:at + c] = i
+        tok_pos[at:at + c] = np.arange(lengths[i], lengths[i] + c, dtype=np.int32)
+        slots[i], seq_start[i], seq_pos0[i] = s.slot, at, lengths[i]
+        for w in s.want:
+            rows[r] = at + w
+            r += 1
+        at += c
+    seq_start[n] = T
+    dev = torch.from_numpy(buf).pin_memory().to(device, non_blocking=True)
+    return StepContext(
+        n_seqs=n, n_tokens=T, tokens=dev[0:T], tok_seq=dev[T:2 * T], tok_pos=dev[2 * T:3 * T],
+        slots=dev[o:o + n], seq_start=dev[o + n:o + 2 * n + 1], seq_pos0=dev[o + 2 * n + 1:o + 3 * n + 1],
+        rows=dev[o + 3 * n + 1:] if n_rows else None, max_new=max(new), max_len=max(l + c for l, c in zip(lengths, new)),
+        decode=all(c == 1 for c in new), host_new=new, host_pos0=list(lengths))

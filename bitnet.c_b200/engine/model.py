@@ -1,0 +1,188 @@
+"""The model: embedding, blocks in schedule order, final norm, output head — and its step function.
+
+The reference's model is an immutable ``BnModel`` shared by all sessions, with per-request
+state in ``BnSession`` (include/model.h:14-20, include/session.h:13-20).  Here ``Model`` is the
+shared, immutable half; ``Cache`` (cache/cache.py) is the per-sequence half.  The reference has
+two forward entry points, many tokens of one sequence (bn_transformer_prefill,
+src/transformer/prefill.c:2494) and one token (bn_transformer_forward, src/transformer.c:183);
+``Model.step`` is both at once, for a batch of sequences.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import Cache, CacheFull
+from ..config import ConfigError, ModelSpec, architecture_of, read_config_json
+from ..csrc import build as kernel_build
+from ..csrc import ops
+from ..parts import BuildContext, ParamSpec, Part, build_part
+from .batch import SeqStep, StepContext, pack_step
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class StepError(ValueError):
+    """A step that cannot run: a token outside the vocabulary, a slot that is not open, a wanted
+    place outside the step's tokens.  Raised before anything is launched or reserved."""
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+def _walk(prefix: str, part: Part, out: Dict[str, tuple]) -> None:
+    for name, p in part.params().items():
+        out[f"{prefix}.{name}"] = (part, name, p)
+    for cname, child in part.children().items():
+        _walk(f"{prefix}.{cname}", child, out)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype="bfloat16", device="cuda:0", arch=None, config=None):
+        spec.validate()
+        self.spec, self.arch, self.config = spec, arch, config
+        self.dtype = resolve_dtype(dtype)
+        self.device = torch.device(device) if device is not None else None
+        b = BuildContext(dtype=self.dtype, device=self.device)
+        self.blocks = [build_part("block", bs, b) for bs in spec.blocks]
+        self.final_norm = build_part("norm", spec.final_norm, b)
+        self.embedding: Optional[torch.Tensor] = None
+        self.head: Optional[torch.Tensor] = None
+        self._bad_token: Optional[torch.Tensor] = None
+        self._owners: Dict[str, tuple] = {}
+        for i, blk in enumerate(self.blocks):
+            _walk(f"blocks.{i}", blk, self._owners)
+        _walk("final_norm", self.final_norm, self._owners)
+
+    # ---- parameters -----------------------------------------------------------------------
+    def parameter_table(self) -> Dict[str, ParamSpec]:
+        """Every parameter of the model by path, e.g. ``blocks.0.mixer.q``."""
+        t: Dict[str, ParamSpec] = {"embedding.table": ParamSpec((self.spec.vocab_size, self.spec.width))}
+        for path, (_part, _name, p) in self._owners.items():
+            t[path] = p
+        if not self.spec.tie_embeddings:
+            t["head.weight"] = ParamSpec((self.spec.vocab_size, self.spec.width))
+        return t
+
+    def kernel_families(self) -> List[str]:
+        fams = ["embed", "linear", "sampling"]
+        for blk in self.blocks:
+            fams.extend(blk.all_kernels())
+        fams.extend(self.final_norm.all_kernels())
+        return list(dict.fromkeys(fams))
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> "Model":
+        """Hand every parameter to the part that owns it.  ``tensors`` maps paths to device tensors."""
+        table = self.parameter_table()
+        missing = sorted(set(table) - set(tensors))
+        extra = sorted(set(tensors) - set(table))
+        if missing or extra:
+            raise ValueError(f"bind: missing {missing}, unexpected {extra}")
+        per_part: Dict[int, tuple] = {}
+        for path, (part, name, _p) in self._owners.items():
+            per_part.setdefault(id(part), (part, {}))[1][name] = tensors[path]
+        for part, group in per_part.values():
+            part.bind(group)
+        self.embedding = tensors["embedding.table"]
+        self.head = tensors["head.weight"] if not self.spec.tie_embeddings else self.embedding
+        self._bad_token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self
+
+    @classmethod
+    def from_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0", max_seq: int = 0) -> "Model":
+        """Load ``config.json`` and the safetensors weights of ``model_dir``; the model class is
+        chosen by ``architectures[0]``."""
+        from ..weights import load_weights
+        cfg_dict = read_config_json(model_dir)
+        arch = architecture_of(cfg_dict)
+        cfg = arch.read_config(cfg_dict)
+        if max_seq:
+            cfg = arch.cap_positions(cfg, max_seq)
+        model = cls(arch.to_spec(cfg), dtype=dtype, device=device, arch=arch, config=cfg)
+        require_cuda(model.device)
+        kernel_build.ensure_built(model.kernel_families())
+        tensors = load_weights(model_dir, model.parameter_table(), arch.tensor_name, model.dtype, model.device)
+        return model.bind(tensors)
+
+    # ---- cache ----------------------------------------------------------------------------
+    def new_cache(self, max_tokens: int, max_seqs: Optional[int] = None, allocate: bool = True) -> Cache:
+        sched = self.spec.schedule
+        kv = [self.blocks[e.block].cache_request() for e in sched]
+        st = [self.blocks[e.block].state_request() for e in sched]
+        return Cache(kv, [e.cache_of for e in sched], st, max_tokens, self.spec.max_positions, self.dtype,
+                     self.device, max_seqs=max_seqs, allocate=allocate)
+
+    # ---- the step -------------------------------------------------------------------------
+    def check_step(self, cache: Cache, seqs: Sequence[SeqStep]) -> List[int]:
+        if not seqs:
+            raise StepError("a step needs at least one sequence")
+        seen = set()
+        lengths = []
+        V = self.spec.vocab_size
+        for s in seqs:
+            if s.slot in seen:
+                raise StepError(f"slot {s.slot} appears twice in one step")
+            seen.add(s.slot)
+            lengths.append(cache.length(s.slot))
+            if len(s.tokens) == 0:
+                raise StepError(f"slot {s.slot} brings no token")
+            for t in s.tokens:
+                if not 0 <= int(t) < V:
+                    raise StepError(f"token {t} is outside the vocabulary of {V}")
+            for w in s.want:
+                if not 0 <= w < len(s.tokens):
+                    raise StepError(f"wanted place {w} is outside the {len(s.tokens)} tokens of slot {s.slot}")
+        return lengths
+
+    def step(self, cache: Cache, seqs: Sequence[SeqStep]) -> Optional[torch.Tensor]:
+        """Run the given tokens of the given sequences as one batch from the cache.
+
+        Returns float32 logits ``[wanted, vocab]`` in the order of ``seqs`` and of each
+        ``want``, or None when nothing is wanted.  On return the sequences are longer by the
+        tokens they brought.  If the cache cannot hold them, nothing has changed.
+        """
+        lengths = self.check_step(cache, seqs)
+        reserved = []
+        try:
+            for s in seqs:
+                cache.reserve(s.slot, len(s.tokens))
+                reserved.append(s)
+        except CacheFull:
+            for s in reserved:  # give back what this step took
+                cache.unreserve(s.slot)
+            raise
+        cache.sync()
+        ctx = pack_step(seqs, lengths, self.device)
+        logits = self.forward(cache, ctx)
+        for s in seqs:
+            cache.advance(s.slot, len(s.tokens))
+        return logits
+
+    def forward(self, cache: Cache, ctx: StepContext) -> Optional[torch.Tensor]:
+        """Embedding, every scheduled run, final norm and head at the wanted rows."""
+        x = torch.empty((ctx.n_tokens, self.spec.width), dtype=torch.float32, device=self.device)
+        ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
+        pending = None
+        for i, e in enumerate(self.spec.schedule):
+            pending = self.blocks[e.block].forward(x, pending, ctx, cache.view(i), cache.state(i))
+        if ctx.rows is None:
+            return None
+        h = self.final_norm.add_norm(x, pending, ctx, rows=ctx.rows)
+        return ops.linear(h, self.head, out_dtype=torch.float32)
+
+
+def require_cuda(device) -> None:
+    if device is None or torch.device(device).type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("this library runs on a CUDA device only (no CPU path); "
+                           f"asked for device {device!r}, torch.cuda.is_available()={torch.cuda.is_available()}")
+
+
+def parameter_table(spec: ModelSpec) -> Dict[str, ParamSpec]:
+    """The parameters a model of ``spec`` has, without building anything on a device."""
+    return Model(spec, dtype="float32", device=None).parameter_table()

@@ -1,0 +1,129 @@
+"""What every part of a layer looks like to the rest of the library.
+
+A part is built from its spec (sizes and constants only) and a ``BuildContext``
+(compute type and device).  It declares its parameters by local name and shape,
+gets them handed over by ``bind`` and is then called with tensors and the step's
+``StepContext``.  A part never asks which model it is in, which block it is, or
+what runs before or after it.
+
+Interfaces
+----------
+Norm           ``add_norm(x, delta, ctx, rows=None) -> h``: x (float32 residual, [T, width]) +=
+               delta when given; h = norm(x) in the compute type.  With ``rows`` only those
+               rows are normed and x is left alone.
+Position       ``rotate(x, n_heads, head_dim, ctx)``: encode positions into the first
+               ``n_heads`` heads of each row of x, in place.  May also offer
+               ``rotate_and_append(x, n_heads, head_dim, ctx, kv, k_off, v_off)`` that writes
+               the new keys/values into the cache in the same pass.
+Mixer          ``cache_request()`` -> KvRequest or None; ``state_request()`` -> StateRequest or
+               None; ``forward(h, ctx, kv, state) -> delta [T, width]``.  ``kv`` is the view of
+               this run's cache planes (``kv.owner`` tells whether this run writes them);
+               ``state`` is this run's per-sequence state tensor ``[n_slots, ...]``.
+FeedForward    ``forward(h, ctx) -> delta [T, width]``.
+Block          ``forward(x, pending, ctx, kv, state) -> pending``: runs its parts on the residual
+               x; ``pending`` is a delta not yet added to x (added by the next norm, which
+               saves one pass over the residual).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """A parameter of a part: its shape, how random weights fill it, whether it is an integer table."""
+
+    shape: Tuple[int, ...]
+    init: str = "normal"  # "normal": N(0, std) matrix; "ones": gain around 1; "zeros"
+    integer: bool = False
+
+
+@dataclass(frozen=True)
+class BuildContext:
+    dtype: torch.dtype  # compute type: torch.bfloat16 or torch.float32
+    device: Any
+
+
+@dataclass(frozen=True)
+class KvRequest:
+    """Keys and values per token that a mixer wants cached.  Runs whose requests are equal
+    share one storage group; ``window`` > 0 means only the last ``window`` positions are kept."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Fixed-size state per sequence: one tensor of ``shape`` and ``dtype`` for every slot,
+    zero when a sequence starts."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    """Base of all parts.  ``kernels`` names the kernel families (csrc/build.py) the part launches."""
+
+    kernels: Tuple[str, ...] = ()
+
+    def __init__(self, spec: Any, build: BuildContext):
+        self.spec = spec
+        self.build = build
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if tensors:
+            raise ValueError(f"{type(self).__name__} takes no parameters, got {sorted(tensors)}")
+
+    def children(self) -> Dict[str, "Part"]:
+        return {}
+
+    def all_kernels(self) -> Tuple[str, ...]:
+        seen = list(self.kernels)
+        for c in self.children().values():
+            seen.extend(c.all_kernels())
+        return tuple(dict.fromkeys(seen))
+
+
+class Mixer(Part):
+    def cache_request(self) -> Optional[KvRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, h, ctx, kv, state):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h, ctx):
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def add_norm(self, x, delta, ctx, rows=None):
+        raise NotImplementedError
+
+
+class Position(Part):
+    def rotate(self, x, n_heads, head_dim, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    def cache_request(self) -> Optional[KvRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, x, pending, ctx, kv, state):
+        raise NotImplementedError

@@ -1,0 +1,29 @@
+"""RMSNorm with the residual add fused in front of it."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc import ops
+from .base import Norm, ParamSpec
+from .registry import register_norm
+
+
+@register_norm("rmsnorm")
+class RmsNorm(Norm):
+    """out = v / sqrt(mean(v^2) + eps) * weight with v = x + delta, statistics in float32
+    (src/transformer/rmsnorm_scalar.c:4-13; fused with the residual as src/gpu_cuda.cu:5077)."""
+
+    kernels = ("norm",)
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.spec.width,), init="ones")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"]
+
+    def add_norm(self, x, delta, ctx, rows=None):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.spec.width), dtype=self.build.dtype, device=x.device)
+        return ops.add_rmsnorm(x, delta, self.weight, self.spec.eps, out, rows=rows)
