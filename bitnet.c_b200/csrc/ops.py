@@ -228,27 +228,70 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
 
 
 def sample_temperature(logits: torch.Tensor, temperature: float, rng_state: torch.Tensor,
-                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One draw per row from softmax(logits / temperature); rng_state holds one xorshift64* state
-    per row (int64 bit patterns) and is advanced by one draw."""
+                       out: Optional[torch.Tensor] = None, index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One draw per row from softmax(logits / temperature).  ``rng_state`` holds xorshift64* states
+    (int64 bit patterns); row r uses and advances state ``index[r]`` (or r without an index)."""
     _need(logits, "logits", torch.float32, 2)
     _need(rng_state, "rng_state", torch.int64, 1)
-    if rng_state.shape[0] < logits.shape[0]:
+    if index is not None:
+        _need(index, "index", torch.int32, 1)
+    elif rng_state.shape[0] < logits.shape[0]:
         raise KernelError("sample_temperature: one generator state per row is needed")
     out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, 1)
     _check(_fn("sampling", "bn_sample_temperature")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
                                                     c_int(logits.shape[1]), c_float(temperature), _ptr(rng_state),
-                                                    _ptr(out), _stream()), "sample_temperature")
+                                                    _ptr(index), _ptr(out), _stream()), "sample_temperature")
     return out
 
 
-def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch.Tensor, penalty: float) -> None:
-    """In place: for each distinct id among the first recent_len[r] entries of recent[r],
-    logit > 0 ? logit / penalty : logit * penalty."""
+def sample_topp(logits: torch.Tensor, temperature: float, topp: float, rng_state: torch.Tensor,
+                out: Optional[torch.Tensor] = None, index: Optional[torch.Tensor] = None,
+                probs: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Nucleus sampling: one draw per row from the smallest set of most probable tokens whose
+    mass exceeds ``topp``.  ``probs`` is scratch of the shape of ``logits``."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(rng_state, "rng_state", torch.int64, 1)
+    if index is not None:
+        _need(index, "index", torch.int32, 1)
+    if probs is None:
+        probs = torch.empty_like(logits)
+    _need(probs, "probs", torch.float32, 2)
+    if probs.shape[0] < logits.shape[0] or probs.shape[1] != logits.shape[1]:
+        raise KernelError("sample_topp: probs scratch does not fit")
+    out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, 1)
+    _check(_fn("sampling", "bn_sample_topp")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
+                                             c_int(logits.shape[1]), c_float(temperature), c_float(topp),
+                                             _ptr(rng_state), _ptr(index), _ptr(probs), _ptr(out), _stream()),
+           "sample_topp")
+    return out
+
+
+def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch.Tensor, penalty: float,
+                   index: Optional[torch.Tensor] = None) -> None:
+    """In place: for each distinct id among the first recent_len[s] entries of recent[s] (s = index[r]
+    or r), logit > 0 ? logit / penalty : logit * penalty."""
     _need(logits, "logits", torch.float32, 2)
     _need(recent, "recent", torch.int32, 2)
     _need(recent_len, "recent_len", torch.int32, 1)
+    if index is not None:
+        _need(index, "index", torch.int32, 1)
     _check(_fn("sampling", "bn_repeat_penalty")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
                                                 c_int(logits.shape[1]), _ptr(recent), c_int(recent.shape[1]),
-                                                _ptr(recent_len), c_float(penalty), _stream()), "repeat_penalty")
+                                                _ptr(recent_len), _ptr(index), c_float(penalty), _stream()),
+           "repeat_penalty")
+
+
+def sampler_accept(recent: torch.Tensor, recent_len: torch.Tensor, recent_pos: torch.Tensor, tokens: torch.Tensor,
+                   index: Optional[torch.Tensor] = None) -> None:
+    """Push tokens[r] into the ring of recent tokens of state row index[r] (or r)."""
+    _need(recent, "recent", torch.int32, 2)
+    _need(recent_len, "recent_len", torch.int32, 1)
+    _need(recent_pos, "recent_pos", torch.int32, 1)
+    _need(tokens, "tokens", torch.int32, 1)
+    if index is not None:
+        _need(index, "index", torch.int32, 1)
+    _check(_fn("sampling", "bn_sampler_accept")(_ptr(recent), c_int(recent.shape[1]), _ptr(recent_len),
+                                                _ptr(recent_pos), _ptr(index), _ptr(tokens), c_int(tokens.shape[0]),
+                                                _stream()), "sampler_accept")

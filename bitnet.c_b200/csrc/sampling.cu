@@ -20,12 +20,16 @@ __device__ __forceinline__ float rng_next_float(unsigned long long* state) {
   return (float)(u >> 8) / 16777216.0f;
 }
 
+// `index` (may be null) maps a row of logits to its row of sampler state: sequences leave a
+// batch at different times, their state rows stay where they are.
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, int ld, int vocab,
                                       const int* __restrict__ recent, int recent_stride,
-                                      const int* __restrict__ recent_len, float penalty) {
+                                      const int* __restrict__ recent_len, const int* __restrict__ index,
+                                      float penalty) {
   int r = blockIdx.x;
-  const int* ids = recent + (size_t)r * recent_stride;
-  int n = min(recent_len[r], recent_stride);
+  int sr = index ? index[r] : r;
+  const int* ids = recent + (size_t)sr * recent_stride;
+  int n = min(recent_len[sr], recent_stride);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     int tok = ids[i];
     if (tok < 0 || tok >= vocab) continue;
@@ -40,9 +44,34 @@ __global__ void repeat_penalty_kernel(float* __restrict__ logits, int ld, int vo
 }
 
 extern "C" int bn_repeat_penalty(float* logits, int ld, int n_rows, int vocab, const int* recent,
-                                 int recent_stride, const int* recent_len, float penalty, cudaStream_t stream) {
+                                 int recent_stride, const int* recent_len, const int* index, float penalty,
+                                 cudaStream_t stream) {
   if (n_rows <= 0 || recent_stride <= 0) return BN_OK;
-  repeat_penalty_kernel<<<n_rows, 64, 0, stream>>>(logits, ld, vocab, recent, recent_stride, recent_len, penalty);
+  repeat_penalty_kernel<<<n_rows, 64, 0, stream>>>(logits, ld, vocab, recent, recent_stride, recent_len, index,
+                                                  penalty);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// The sampler's window of recent tokens is a ring (src/sampler.c:54-59): write at recent_pos,
+// advance it, grow recent_len up to the window.
+__global__ void accept_kernel(int* __restrict__ recent, int recent_stride, int* __restrict__ recent_len,
+                              int* __restrict__ recent_pos, const int* __restrict__ index,
+                              const int* __restrict__ tokens, int n_rows) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  int sr = index ? index[r] : r;
+  int pos = recent_pos[sr];
+  recent[(size_t)sr * recent_stride + pos] = tokens[r];
+  recent_pos[sr] = (pos + 1) % recent_stride;
+  if (recent_len[sr] < recent_stride) recent_len[sr] += 1;
+}
+
+extern "C" int bn_sampler_accept(int* recent, int recent_stride, int* recent_len, int* recent_pos,
+                                 const int* index, const int* tokens, int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0 || recent_stride <= 0) return BN_OK;
+  accept_kernel<<<(n_rows + 127) / 128, 128, 0, stream>>>(recent, recent_stride, recent_len, recent_pos, index,
+                                                         tokens, n_rows);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
@@ -90,7 +119,8 @@ extern "C" int bn_argmax(const float* logits, int ld, int n_rows, int vocab, int
 // One block per row.  Each thread owns a contiguous run of the vocabulary so that the
 // cumulative distribution is walked in index order.
 __global__ void sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
-                                          unsigned long long* __restrict__ rng, int* __restrict__ out) {
+                                          unsigned long long* __restrict__ rng, const int* __restrict__ index,
+                                          int* __restrict__ out) {
   __shared__ float scratch[32];
   __shared__ float tsum[SAMPLE_THREADS];
   __shared__ float r_shared;
@@ -109,7 +139,7 @@ __global__ void sample_temperature_kernel(const float* __restrict__ logits, int 
   for (int i = lo; i < hi; ++i) local += expf(l[i] / temperature - m) / s;
   tsum[threadIdx.x] = local;
   if (threadIdx.x == 0) {
-    r_shared = rng_next_float(rng + row);
+    r_shared = rng_next_float(rng + (index ? index[row] : row));
     pick = vocab - 1;
   }
   __syncthreads();
@@ -134,10 +164,187 @@ __global__ void sample_temperature_kernel(const float* __restrict__ logits, int 
 }
 
 extern "C" int bn_sample_temperature(const float* logits, int ld, int n_rows, int vocab, float temperature,
-                                     unsigned long long* rng, int* out, cudaStream_t stream) {
+                                     unsigned long long* rng, const int* index, int* out, cudaStream_t stream) {
   if (n_rows <= 0) return BN_OK;
   if (vocab <= 0 || !(temperature > 0.f)) return BN_ERR_BAD_ARG;
-  sample_temperature_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, rng, out);
+  sample_temperature_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, rng, index, out);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// ---- nucleus (top-p) sampling -----------------------------------------------------------------
+// Reference (src/sampler.c:95-135): keep tokens with p >= (1 - topp) / (n - 1), sort them by
+// falling probability, cut after the first whose running sum exceeds topp, draw
+// r = rng_float() * that sum and take the first token whose running sum exceeds r.
+// Both cuts are "the first token, in sorted order, whose running sum exceeds a threshold".
+// Instead of sorting, the kernel bisects on the probability value: with
+// F(x) = sum of candidates with p >= x, the wanted token has the largest p with F(p) > threshold;
+// among tokens of exactly that probability the lower index comes first.  Sums are double.
+
+__device__ __forceinline__ double block_sum_double(double v, double* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  double r = (threadIdx.x < nwarp) ? scratch[threadIdx.x] : 0.0;
+  if (warp == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    if (lane == 0) scratch[0] = r;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+// Sum of p[i] over candidates (p >= cutoff) whose bit pattern is >= key.  Probabilities are
+// non-negative floats, so their bit patterns order like their values.
+__device__ double mass_at_least(const float* p, int n, unsigned cutoff_bits, unsigned key, double* scratch) {
+  double s = 0.0;
+  unsigned k = max(key, cutoff_bits);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = p[i];
+    if (__float_as_uint(v) >= k) s += (double)v;
+  }
+  return block_sum_double(s, scratch);
+}
+
+// First token in (falling p, rising index) order whose running sum exceeds thr; *cum_out is that
+// running sum.  If none exceeds it, the last candidate in that order and the whole mass.
+__device__ int nucleus_first_exceeding(const float* p, int n, unsigned cutoff_bits, unsigned max_bits, double thr,
+                                       double* cum_out, double* dscratch, int* iscratch) {
+  double total = mass_at_least(p, n, cutoff_bits, cutoff_bits, dscratch);
+  unsigned lo = cutoff_bits, hi = max_bits;
+  bool none = !(total > thr);
+  if (!none) {
+    while (lo < hi) {
+      unsigned mid = lo + (hi - lo + 1) / 2;
+      if (mass_at_least(p, n, cutoff_bits, mid, dscratch) > thr) lo = mid;
+      else hi = mid - 1;
+    }
+  }
+  // `lo` is now the probability (as bits) of the wanted token, or, if none exceeds thr, the
+  // cut-off: then the smallest candidate probability is looked up and its last index taken.
+  __shared__ unsigned s_key;
+  if (none) {
+    unsigned best = 0xffffffffu;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      unsigned b = __float_as_uint(p[i]);
+      if (b >= cutoff_bits) best = min(best, b);
+    }
+    for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) iscratch[threadIdx.x >> 5] = (int)best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned b = 0xffffffffu;
+      for (int w = 0; w < (int)((blockDim.x + 31) >> 5); ++w) b = min(b, (unsigned)iscratch[w]);
+      s_key = b;
+    }
+    __syncthreads();
+    lo = s_key;
+  }
+  double above = (lo == 0xffffffffu) ? 0.0 : mass_at_least(p, n, cutoff_bits, lo + 1, dscratch);
+  float pv = __uint_as_float(lo);
+  // how many tokens of probability pv are needed: the k-th (1-based) in index order
+  __shared__ int s_k;
+  __shared__ double s_cum;
+  // count the ties
+  int mine = 0;
+  int per = (n + blockDim.x - 1) / blockDim.x;
+  int a = threadIdx.x * per, b = min(n, a + per);
+  for (int i = a; i < b; ++i) mine += (__float_as_uint(p[i]) == lo);
+  __syncthreads();
+  iscratch[threadIdx.x] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ties = 0;
+    for (int t = 0; t < (int)blockDim.x; ++t) ties += iscratch[t];
+    int k = ties;  // none exceeds: the last of them
+    double cum = above;
+    if (!none) {
+      for (int j = 1; j <= ties; ++j) {
+        cum += (double)pv;
+        if (cum > thr) { k = j; break; }
+      }
+    } else {
+      cum = total;
+    }
+    s_k = k;
+    s_cum = cum;
+  }
+  __syncthreads();
+  int k = s_k;
+  *cum_out = s_cum;
+  // locate the k-th tie in index order
+  __shared__ int s_pick;
+  if (threadIdx.x == 0) {
+    int seen = 0, owner = 0;
+    for (int t = 0; t < (int)blockDim.x; ++t) {
+      if (seen + iscratch[t] >= k) { owner = t; break; }
+      seen += iscratch[t];
+    }
+    int a0 = owner * per, b0 = min(n, a0 + per), pick = max(0, b0 - 1);
+    for (int i = a0; i < b0; ++i) {
+      if (__float_as_uint(p[i]) == lo) {
+        ++seen;
+        if (seen == k) { pick = i; break; }
+      }
+    }
+    s_pick = pick;
+  }
+  __syncthreads();
+  return s_pick;
+}
+
+__global__ void sample_topp_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
+                                   float topp, unsigned long long* __restrict__ rng, const int* __restrict__ index,
+                                   float* __restrict__ probs, int* __restrict__ out) {
+  __shared__ float scratch[32];
+  __shared__ double dscratch[32];
+  __shared__ int iscratch[SAMPLE_THREADS];
+  __shared__ float r_shared;
+  int row = blockIdx.x;
+  const float* l = logits + (size_t)row * ld;
+  float* p = probs + (size_t)row * vocab;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, l[i] / temperature);
+  m = block_max(m, scratch);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += expf(l[i] / temperature - m);
+  s = block_sum(s, scratch);
+  float pmax = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    float v = expf(l[i] / temperature - m) / s;
+    p[i] = v;
+    pmax = fmaxf(pmax, v);
+  }
+  pmax = block_max(pmax, scratch);  // also orders the writes of p before the reads below
+  if (threadIdx.x == 0) r_shared = rng_next_float(rng + (index ? index[row] : row));
+  __syncthreads();
+  if (vocab == 1) {
+    if (threadIdx.x == 0) out[row] = 0;
+    return;
+  }
+  float cutoff = (1.0f - topp) / (float)(vocab - 1);
+  unsigned cutoff_bits = __float_as_uint(fmaxf(cutoff, 0.f));
+  unsigned max_bits = __float_as_uint(pmax);
+  double cumulative, c2;
+  int last = nucleus_first_exceeding(p, vocab, cutoff_bits, max_bits, (double)topp, &cumulative, dscratch, iscratch);
+  float r = r_shared * (float)cumulative;
+  int pick = nucleus_first_exceeding(p, vocab, cutoff_bits, max_bits, (double)r, &c2, dscratch, iscratch);
+  if (threadIdx.x == 0) out[row] = (c2 > cumulative) ? last : pick;
+}
+
+// probs: scratch of n_rows * vocab floats.
+extern "C" int bn_sample_topp(const float* logits, int ld, int n_rows, int vocab, float temperature, float topp,
+                              unsigned long long* rng, const int* index, float* probs, int* out,
+                              cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (vocab <= 0 || !(temperature > 0.f) || !(topp > 0.f && topp < 1.f) || !probs) return BN_ERR_BAD_ARG;
+  sample_topp_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, topp, rng, index, probs,
+                                                           out);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }

@@ -1,0 +1,80 @@
+"""The device side of the generation loop: the model's step function plus the sampler."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache import Cache
+from ..sampling import Sampler, SamplingParams
+from .batch import SeqStep
+from .generate import Completion, Engine, generate
+from .model import Model
+
+
+class ModelEngine(Engine):
+    """Runs steps of ``model`` on ``cache`` and samples on the device; token ids cross to the host
+    once per step (the loop's stop decisions need them)."""
+
+    def __init__(self, model: Model, cache: Cache, params: SamplingParams):
+        self.model, self.cache, self.params = model, cache, params
+        self.max_positions = model.spec.max_positions
+        self.sampler: Optional[Sampler] = None
+
+    def free_tokens(self) -> int:
+        return self.cache.tokens_free()
+
+    def max_batch(self) -> int:
+        return self.cache.slots.n_free
+
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def start_batch(self, first_index: int, prompts: Sequence[Sequence[int]]) -> None:
+        self.sampler = Sampler(self.params, len(prompts), self.model.spec.vocab_size, self.model.device,
+                               first_index=first_index, prompts=prompts)
+
+    def _index(self, rows: Sequence[int], n_state_rows: int) -> Optional[torch.Tensor]:
+        if list(rows) == list(range(n_state_rows)):
+            return None
+        return torch.tensor(list(rows), dtype=torch.int32).to(self.model.device, non_blocking=True)
+
+    def step_and_sample(self, seqs: Sequence[SeqStep], rows: Sequence[int]) -> List[int]:
+        logits = self.model.step(self.cache, seqs)
+        out = self.sampler.sample(logits, self._index(rows, self.sampler.n_rows))
+        return out.cpu().tolist()
+
+    def accept(self, tokens: Sequence[int], rows: Sequence[int]) -> None:
+        if self.sampler.penalised:
+            t = torch.tensor(list(tokens), dtype=torch.int32).to(self.model.device, non_blocking=True)
+            self.sampler.accept(t, self._index(rows, self.sampler.n_rows))
+
+
+def generate_with_model(model: Model, prompts: Sequence[Sequence[int]], max_new_tokens=256, *,
+                        temperature: float = 0.0, top_p: float = 0.9, seed: int = 42,
+                        repeat_penalty: float = 1.0, repeat_window: int = 64,
+                        stop_ids: Optional[Sequence[int]] = None, max_batch: Optional[int] = None,
+                        cache: Optional[Cache] = None, max_tokens: Optional[int] = None,
+                        callback=None) -> List[Completion]:
+    """Generate for every prompt (lists of token ids).  ``stop_ids`` default to the model's
+    end-of-sequence ids.  The cache is sized for the whole call unless ``max_tokens`` or a
+    ``cache`` is given; requests that do not fit together run in batches one after another."""
+    from ..cache.pages import PAGE, pages_for
+    params = SamplingParams(temperature=temperature, top_p=top_p, seed=seed, repeat_penalty=repeat_penalty,
+                            repeat_window=repeat_window)
+    n = len(prompts)
+    mx = [int(max_new_tokens)] * n if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
+    if cache is None:
+        S = model.spec.max_positions
+        if max_batch:
+            per = sorted((pages_for(min(len(p) + m, S)) * PAGE for p, m in zip(prompts, mx)), reverse=True)
+            need = sum(per[:max_batch])
+        else:
+            need = sum(pages_for(min(len(p) + m, S)) * PAGE for p, m in zip(prompts, mx))
+        cache = model.new_cache(max_tokens=max_tokens or max(need, PAGE), max_seqs=max_batch or max(n, 1))
+    stops = tuple(model.spec.stop_ids) if stop_ids is None else tuple(stop_ids)
+    return generate(ModelEngine(model, cache, params), prompts, mx, stop_ids=stops, callback=callback,
+                    max_batch=max_batch)

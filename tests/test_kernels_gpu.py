@@ -1,0 +1,220 @@
+"""Each CUDA kernel alone against a plain PyTorch/NumPy float32-or-better reference of the same
+operation, at sizes other than the engine's test models."""
+import numpy as np
+import pytest
+import torch
+
+import bitnet_c_b200  # noqa: F401
+from bitnet_c_b200.csrc import ops
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == "float32" else bf16
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,vocab", [(72, 101), (4096, 777)])
+def test_embed_gather(cuda_device, dtype, width, vocab):
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(vocab, width, generator=g).to(DT[dtype]).to(cuda_device)
+    toks = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32, device=cuda_device)
+    out = torch.full((5, width), 7.0, device=cuda_device)
+    bad = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    ops.embed_gather(table, toks, out, bad)
+    assert torch.equal(out, table.float()[toks.long()])
+    assert bad.item() == 0
+    toks[2] = vocab  # outside: zero row and flag, nothing read out of bounds
+    ops.embed_gather(table, toks, out, bad)
+    assert bad.item() == 1 and out[2].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,width,eps", [(5, 72, 1e-5), (3, 4096, 1e-6), (2, 13000, 1e-3)])
+def test_add_rmsnorm(cuda_device, dtype, rows, width, eps):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(rows, width, generator=g).to(cuda_device) * 3
+    delta = torch.randn(rows, width, generator=g).to(DT[dtype]).to(cuda_device)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DT[dtype]).to(cuda_device)
+    ref_x = x.double() + delta.double()
+    ref = ref_x / torch.sqrt((ref_x * ref_x).mean(-1, keepdim=True) + eps) * w.double()
+    out = torch.empty(rows, width, dtype=DT[dtype], device=cuda_device)
+    x1 = x.clone()
+    ops.add_rmsnorm(x1, delta, w, eps, out)
+    assert (x1.double() - ref_x).abs().max().item() < 1e-6
+    assert (out.double() - ref).abs().max().item() < tol(dtype, 1e-5, 3e-2)
+    # with a row index: only those rows, x untouched, no delta
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=cuda_device)
+    out2 = torch.empty(2, width, dtype=DT[dtype], device=cuda_device)
+    x2 = x.clone()
+    ops.add_rmsnorm(x2, None, w, eps, out2, rows=idx)
+    r2 = x.double()[idx.long()]
+    r2 = r2 / torch.sqrt((r2 * r2).mean(-1, keepdim=True) + eps) * w.double()
+    assert torch.equal(x2, x)
+    assert (out2.double() - r2).abs().max().item() < tol(dtype, 1e-5, 3e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(cuda_device, dtype):
+    g = torch.Generator().manual_seed(3)
+    h = (torch.randn(7, 2 * 200, generator=g) * 3).to(DT[dtype]).to(cuda_device)
+    out = torch.empty(7, 200, dtype=DT[dtype], device=cuda_device)
+    ops.silu_mul(h, out)
+    gte, up = h.double()[:, :200], h.double()[:, 200:]
+    ref = gte / (1 + torch.exp(-gte)) * up
+    assert (out.double() - ref).abs().max().item() < tol(dtype, 1e-5, 5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 50, 72), (8, 333, 4096), (11, 17, 200), (16, 1000, 64)])
+def test_linear_skinny(cuda_device, dtype, M, N, K):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(M, K, generator=g).to(DT[dtype]).to(cuda_device)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(DT[dtype]).to(cuda_device)
+    y = ops.linear(x, w, out_dtype=torch.float32)
+    ref = x.double() @ w.double().t()
+    assert y.dtype == torch.float32 and y.shape == (M, N)
+    assert (y.double() - ref).abs().max().item() < 1e-4 * max(1.0, K / 256)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_linear_many_rows_is_float32_exact(cuda_device, dtype):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(100, 512, generator=g).to(DT[dtype]).to(cuda_device)
+    w = (torch.randn(300, 512, generator=g) * 0.05).to(DT[dtype]).to(cuda_device)
+    y = ops.linear(x, w, out_dtype=torch.float32)
+    ref = x.double() @ w.double().t()
+    # float32 accumulation of exact products: no tf32, no bf16 output rounding
+    assert (y.double() - ref).abs().max().item() < 2e-5
+
+
+def _paged_cache(cuda_device, dtype, n_pages, kv, hd, seed):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(n_pages, kv, 64, hd, generator=g).to(DT[dtype]).to(cuda_device)
+    v = torch.randn(n_pages, kv, 64, hd, generator=g).to(DT[dtype]).to(cuda_device)
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,theta,pos", [(4, 2, 16, 1e4, [0, 5, 63, 64]), (3, 1, 48, 5e5, [700, 1, 129, 130]),
+                                               (5, 5, 128, 1e6, [4000, 4001, 3, 64])])
+def test_rope_append(cuda_device, dtype, H, KV, hd, theta, pos):
+    T = len(pos)
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(T, (H + 2 * KV) * hd, generator=g).to(DT[dtype]).to(cuda_device)
+    x0 = x.clone()
+    # two sequences: tokens 0,1 in slot 2; tokens 2,3 in slot 0; scattered pages
+    tok_seq = torch.tensor([0, 0, 1, 1], dtype=torch.int32, device=cuda_device)
+    tok_pos = torch.tensor(pos, dtype=torch.int32, device=cuda_device)
+    slots = torch.tensor([2, 0], dtype=torch.int32, device=cuda_device)
+    n_pages, per_seq = 200, 64
+    perm = torch.randperm(n_pages, generator=g)[: 3 * per_seq].reshape(3, per_seq).to(torch.int32).to(cuda_device)
+    k, v = _paged_cache(cuda_device, dtype, n_pages, KV, hd, 7)
+    k0, v0 = k.clone(), v.clone()
+    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(hd)))
+    ops.rope_append(x, H + KV, hd, hd, scale, tok_pos, k_off=H * hd, v_off=(H + KV) * hd, n_kv_heads=KV,
+                    tok_seq=tok_seq, slots=slots, page_table=perm, k_cache=k, v_cache=v)
+    heads = x0.double().cpu().numpy().reshape(T, H + 2 * KV, hd)
+    rot = plain_llama.apply_rope(heads[:, : H + KV], pos, theta)
+    got = x.double().cpu().numpy().reshape(T, H + 2 * KV, hd)
+    t_ = tol(dtype, 2e-6, 2e-2)
+    assert np.abs(got[:, : H + KV] - rot).max() < t_
+    assert np.array_equal(got[:, H + KV:], heads[:, H + KV:])  # values untouched
+    touched = torch.zeros_like(k, dtype=torch.bool)
+    for t in range(T):
+        slot = [2, 2, 0, 0][t]
+        page = perm[slot, pos[t] // 64].item()
+        row = pos[t] % 64
+        assert np.abs(k[page, :, row].double().cpu().numpy() - got[t, H:H + KV]).max() == 0
+        assert torch.equal(v[page, :, row], x0.reshape(T, H + 2 * KV, hd)[t, H + KV:])
+        touched[page, :, row] = True
+    assert torch.equal(k[~touched], k0[~touched]) and torch.equal(v[~touched], v0[~touched])
+
+
+def _attention_reference(q, k_seq, v_seq, scale, window):
+    return plain_llama.attention(q, k_seq, v_seq, scale, window)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,lens,news,window", [
+    (4, 2, 16, [5, 64, 130], [5, 1, 3], 0),
+    (3, 1, 48, [200, 1, 65], [200, 1, 1], 0),
+    (8, 2, 128, [300, 129], [2, 129], 0),
+    (2, 2, 256, [70], [70], 0),
+    (4, 4, 32, [150, 40], [150, 1], 17),
+])
+def test_attention_general(cuda_device, dtype, H, KV, hd, lens, news, window):
+    """Sequences of total length ``lens`` whose last ``news`` tokens are new; keys live in
+    scattered pages; one query and key are scaled so that a far key dominates its row."""
+    g = torch.Generator().manual_seed(8)
+    n_seq, n_pages, per_seq = len(lens), 64, 8
+    perm = torch.randperm(n_pages, generator=g)[: n_seq * per_seq].reshape(n_seq, per_seq).to(torch.int32)
+    k, v = _paged_cache(cuda_device, dtype, n_pages, KV, hd, 9)
+    ks = [torch.randn(L, KV, hd, generator=g).to(DT[dtype]) for L in lens]
+    vs = [torch.randn(L, KV, hd, generator=g).to(DT[dtype]) for L in lens]
+    qs = [torch.randn(n, H, hd, generator=g).to(DT[dtype]) * 0.5 for n in news]
+    # a far key that must win: key 1 of sequence 0 (if it has one) lines up with the last query
+    if lens[0] > 2 and window == 0:
+        ks[0][1, 0] = (qs[0][-1, 0].float() * 4).to(DT[dtype])
+    slots = list(range(n_seq))[::-1]
+    for s, L in enumerate(lens):
+        for p in range(L):
+            page = perm[slots[s], p // 64].item()
+            k[page, :, p % 64] = ks[s][p].to(cuda_device)
+            v[page, :, p % 64] = vs[s][p].to(cuda_device)
+    q = torch.cat([x.reshape(x.shape[0], H * hd) for x in qs]).contiguous().to(cuda_device)
+    T = q.shape[0]
+    tok_seq = torch.tensor(sum(([s] * n for s, n in enumerate(news)), []), dtype=torch.int32, device=cuda_device)
+    tok_pos = torch.tensor(sum((list(range(L - n, L)) for L, n in zip(lens, news)), []), dtype=torch.int32,
+                           device=cuda_device)
+    out = torch.empty(T, H * hd, dtype=DT[dtype], device=cuda_device)
+    ops.attention_general(q, H * hd, out, T, H, KV, hd, hd ** -0.5, window, tok_seq, tok_pos,
+                          torch.tensor(slots, dtype=torch.int32, device=cuda_device), perm.to(cuda_device), k, v)
+    got = out.double().cpu().numpy().reshape(T, H, hd)
+    at = 0
+    for s, (L, n) in enumerate(zip(lens, news)):
+        qfull = np.zeros((L, H, hd))
+        qfull[L - n:] = qs[s].double().numpy()
+        ref = _attention_reference(qfull, ks[s].double().numpy(), vs[s].double().numpy(), hd ** -0.5, window)[L - n:]
+        err = np.abs(got[at:at + n] - ref).max()
+        assert err < tol(dtype, 2e-5, 2e-2), f"sequence {s}: {err}"
+        at += n
+
+
+def test_argmax_ties_and_sizes(cuda_device):
+    g = torch.Generator().manual_seed(10)
+    logits = torch.randn(5, 3001, generator=g).to(cuda_device)
+    logits[0, 100] = logits[0, 2000] = 50.0  # tie: lower index wins
+    logits[1, 3000] = 60.0
+    logits[2, 0] = 60.0
+    got = ops.argmax(logits).cpu().tolist()
+    ref = [int(np.argmax(r)) for r in logits.cpu().numpy()]
+    assert got == ref and got[0] == 100
+
+
+def test_sample_temperature_follows_the_reference_walk(cuda_device):
+    V, rows, temp = 1013, 6, 0.8
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn(rows, V, generator=g) * 2).to(cuda_device)
+    seeds = [42, 1, 7, 123456789, 99, 2**40 + 5]
+    state = torch.tensor(seeds, dtype=torch.int64, device=cuda_device)
+    rngs = [plain_llama.Xorshift64Star(s) for s in seeds]
+    for _ in range(5):
+        got = ops.sample_temperature(logits, temp, state).cpu().tolist()
+        for r in range(rows):
+            want = plain_llama.sample(logits[r].cpu().numpy(), temp, 1.0, rngs[r])
+            if got[r] != want:
+                # only a draw within rounding of a boundary of the cumulative sum may differ, by one place
+                assert abs(got[r] - want) == 1, (r, got[r], want)
+        assert state.cpu().tolist() == [np.int64(np.uint64(x.state)) for x in rngs]
+
+
+def test_repeat_penalty(cuda_device):
+    logits = torch.tensor([[1.0, -2.0, 3.0, 4.0, -5.0], [1.0, 1.0, 1.0, 1.0, 1.0]], device=cuda_device)
+    recent = torch.tensor([[2, 4, 2, 9, 0], [1, 1, 1, 1, 1]], dtype=torch.int32, device=cuda_device)
+    n = torch.tensor([4, 2], dtype=torch.int32, device=cuda_device)
+    ops.repeat_penalty(logits, recent, n, 2.0)
+    assert logits.cpu().tolist() == [[1.0, -2.0, 1.5, 4.0, -10.0], [1.0, 0.5, 1.0, 1.0, 1.0]]
