@@ -1,0 +1,279 @@
+#!/usr/bin/env python3
+"""Benchmark of the library's serving step on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default workload: the layer sizes of Llama-3.1-8B with random weights (bfloat16), a batch of 8
+sequences with 512-token prompts in a cache sized for a context of 4096, K decode steps.
+Prints ONE JSON line.  ``value`` is decoded tokens per second, timed on the device with CUDA
+events; ``e2e`` is the same through the public Python entry point with host token ids in and
+out every step.  The line also carries the prefill of one 2,048-token prompt, the decode step's
+roofline fraction against the measured HBM bandwidth, and decode at batch 1 and 64.
+A step reads all 15 GB of weights, far more than the 126 MB L2, so no L2 flush is needed
+between timed iterations (``config.l2`` says so).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 4096,
+    "intermediate_size": 14336, "num_hidden_layers": 32, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256, "max_position_embeddings": 4096,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+PROMPT_LEN = 512
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm():
+    """The reference is a C11 project with a Makefile and no Python packaging; the prescribed
+    offline ``pip install --target baseline/_ref /root/reference`` therefore installs nothing."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "artalis-io/bitnet.c is a C/Makefile project without setup.py or pyproject.toml: "
+                                     "the offline pip install into baseline/_ref fails, and it has no safetensors or "
+                                     "random-weights loader to run this model with"}))
+    return 0
+
+
+def weight_bytes(model):
+    seen, total = set(), 0
+    tensors = [model.embedding, model.head]
+    for blk in model.blocks:
+        tensors += [blk.mixer.w_qkv, blk.mixer.w_o, blk.ffn.w_gate_up, blk.ffn.w_down, blk.mixer_norm.weight,
+                    blk.ffn_norm.weight]
+    tensors.append(model.final_norm.weight)
+    for t in tensors:
+        if t.data_ptr() not in seen:
+            seen.add(t.data_ptr())
+            total += t.numel() * t.element_size()
+    return total
+
+
+def decode_read_bytes(model, cfg, batch, context_len):
+    """Bytes a decode step has to read: every weight it uses once (the embedding table only the
+    rows it gathers) and the cached keys and values of the live sequences."""
+    emb = model.embedding.numel() * model.embedding.element_size()
+    w = weight_bytes(model) - (emb if model.head is not model.embedding else 0)
+    w += batch * cfg["hidden_size"] * model.embedding.element_size() if model.head is not model.embedding else 0
+    kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    return w + batch * context_len * kv_per_token
+
+
+def prefill_flops(cfg, T):
+    d, I, L, H, KV, hs, V = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"],
+                             cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"])
+    per_layer = 2 * T * d * (H * hs + 2 * KV * hs) + 2 * T * H * hs * d + 3 * 2 * T * d * I
+    attn = 2 * 2 * (T * (T + 1) // 2) * hs * H
+    return L * (per_layer + attn) + 2 * V * d
+
+
+def run_decode(bn, model, cfg, batch, steps, warmup, e2e=False, clock=None):
+    """Prefill ``batch`` prompts of PROMPT_LEN tokens, then time ``steps`` decode steps."""
+    import torch
+    from bitnet_c_b200.engine import ModelEngine
+    from bitnet_c_b200.engine.batch import SeqStep
+    from bitnet_c_b200.sampling import SamplingParams
+    from bitnet_c_b200.csrc import ops
+
+    g = torch.Generator().manual_seed(1234 + batch)
+    prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
+    cache = model.new_cache(max_tokens=batch * cfg["max_position_embeddings"], max_seqs=batch)
+    eng = ModelEngine(model, cache, SamplingParams(temperature=0.0))
+    eng.start_batch(0, prompts)
+    slots = [eng.open() for _ in range(batch)]
+    rows = list(range(batch))
+    # prompts in groups of 8 so that the activations of 64 x 512 tokens need not live at once
+    toks = []
+    for a in range(0, batch, 8):
+        idx = list(range(a, min(batch, a + 8)))
+        toks += eng.step_and_sample([SeqStep(slots[i], prompts[i], [PROMPT_LEN - 1]) for i in idx], idx)
+
+    def one_step(t):
+        return eng.step_and_sample([SeqStep(slots[i], [t[i]], [0]) for i in range(batch)], rows)
+
+    for _ in range(warmup):
+        toks = one_step(toks)
+    torch.cuda.synchronize()
+    ops.LAUNCHES = 0
+    if clock is not None:
+        clock.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        toks = one_step(toks)
+    end.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    dev_ms = start.elapsed_time(end)
+    clocks = clock.stop() if clock is not None else None
+    launches = ops.LAUNCHES
+    ctx_len = PROMPT_LEN + warmup + steps // 2
+    for s in slots:
+        eng.close(s)
+    del cache
+    torch.cuda.empty_cache()
+    return {"dev_ms": dev_ms, "wall_ms": wall_ms, "launches": launches, "clocks": clocks, "context": ctx_len,
+            "h2d": getattr(eng, "h2d_bytes_last_step", 4 * (6 * batch + 1)), "d2h": 4 * batch}
+
+
+def run_prefill(bn, model, cfg, warmup=3, iters=5):
+    import torch
+    from bitnet_c_b200.engine.batch import SeqStep
+    g = torch.Generator().manual_seed(99)
+    prompt = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+    cache = model.new_cache(max_tokens=cfg["max_position_embeddings"], max_seqs=1)
+    times = []
+    for i in range(warmup + iters):
+        slot = cache.open()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        logits = model.step(cache, [SeqStep(slot, prompt, [PREFILL_TOKENS - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(s.elapsed_time(e))
+        cache.close(slot)
+    del cache, logits
+    torch.cuda.empty_cache()
+    times.sort()
+    return times[len(times) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64 and the prefill (quick runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    import bitnet_c_b200 as bn
+    from bitnet_c_b200.engine import Model
+
+    cfg = dict(LLAMA_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
+
+    main_run = run_decode(bn, model, cfg, 8, args.steps, warmup, clock=ClockSampler())
+    ms_per_step = main_run["dev_ms"] / args.steps
+    value = 8 * args.steps / (main_run["dev_ms"] / 1e3)
+    e2e_run = run_decode(bn, model, cfg, 8, args.steps, warmup)
+    e2e_value = 8 * args.steps / (e2e_run["wall_ms"] / 1e3)
+    read_bytes = decode_read_bytes(model, cfg, 8, main_run["context"])
+    achieved = read_bytes / (ms_per_step / 1e3) / 1e9
+
+    out = {
+        "metric": "decode tokens/s at batch 8 (Llama-3.1-8B sizes, bf16)", "value": round(value, 2), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "llama-3.1-8b-sizes-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": 8, "seq_len": cfg["max_position_embeddings"], "prompt_len": PROMPT_LEN,
+                   "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied": False,
+                   "parallelism": "single-gpu", "l2": "inputs larger than L2 (15 GB of weights per step)",
+                   "peaks": pk["source"]},
+        "clocks": main_run["clocks"],
+        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": e2e_run["h2d"],
+                "d2h_bytes_per_step": e2e_run["d2h"]},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if not args.skip_points:
+        pre_ms = run_prefill(bn, model, cfg)
+        fl = prefill_flops(cfg, PREFILL_TOKENS)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(pre_ms, 3), "frac": round(fl / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        points = {}
+        for b in (1, 64):
+            r = run_decode(bn, model, cfg, b, args.steps, warmup)
+            points[f"decode_b{b}"] = round(b * args.steps / (r["dev_ms"] / 1e3), 2)
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

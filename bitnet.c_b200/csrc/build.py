@@ -120,6 +120,14 @@ def _compile(family: str, out: str, log: List[str]) -> None:
             pass
         raise KernelBuildError(f"nvcc failed on {SOURCES[family]}:\n{' '.join(cmd)}\n{p.stdout}")
     os.replace(tmp, out)
+    # libraries of older versions of this source are of no use any more
+    folder, keep = os.path.dirname(out), os.path.basename(out)
+    for fn in os.listdir(folder):
+        if fn.startswith(f"libbn_{family}-") and fn.endswith(".so") and fn != keep:
+            try:
+                os.remove(os.path.join(folder, fn))
+            except OSError:
+                pass
     if p.stdout.strip():
         log.append(p.stdout)
 

@@ -58,7 +58,12 @@ def _check(status: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA launch failed with error {status - 2}")
 
 
+LAUNCHES = 0  # kernels of this library launched through this module (bench.py reads and resets it)
+
+
 def _fn(family: str, name: str):
+    global LAUNCHES
+    LAUNCHES += 1
     f = getattr(build.library(family), name)
     f.restype = c_int
     return f

@@ -39,8 +39,9 @@ class StepContext:
     max_new: int  # longest run of new tokens in this step
     max_len: int  # longest sequence after this step
     decode: bool  # every sequence brings exactly one token
-    host_new: List[int] = field(default_factory=list)
-    host_pos0: List[int] = field(default_factory=list)
+    host_new: List[int] = field(default_factory=list)  # the same facts on the host, for parts that
+    host_pos0: List[int] = field(default_factory=list)  # loop over sequences there
+    host_slots: List[int] = field(default_factory=list)
 
 
 def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepContext:
@@ -70,4 +71,5 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
         n_seqs=n, n_tokens=T, tokens=dev[0:T], tok_seq=dev[T:2 * T], tok_pos=dev[2 * T:3 * T],
         slots=dev[o:o + n], seq_start=dev[o + n:o + 2 * n + 1], seq_pos0=dev[o + 2 * n + 1:o + 3 * n + 1],
         rows=dev[o + 3 * n + 1:] if n_rows else None, max_new=max(new), max_len=max(l + c for l, c in zip(lengths, new)),
-        decode=all(c == 1 for c in new), host_new=new, host_pos0=list(lengths))
+        decode=all(c == 1 for c in new), host_new=new, host_pos0=list(lengths),
+        host_slots=[s.slot for s in seqs])

@@ -110,6 +110,37 @@ class Model:
         tensors = load_weights(model_dir, model.parameter_table(), arch.tensor_name, model.dtype, model.device)
         return model.bind(tensors)
 
+    @classmethod
+    def from_random(cls, config: Dict[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0",
+                    matrix_std: float = 0.02, norm_std: float = 0.1) -> "Model":
+        """A model of ``config`` (config.json keys) with random weights made on the device: matrices
+        N(0, matrix_std), norm gains 1 + N(0, norm_std).  For sizes whose weights would be too
+        large to write to a folder first; the values are those of torch's CUDA generator, not of
+        ``write_random_model``."""
+        arch = architecture_of(config)
+        cfg = arch.read_config(config)
+        model = cls(arch.to_spec(cfg), dtype=dtype, device=device, arch=arch, config=cfg)
+        require_cuda(model.device)
+        kernel_build.ensure_built(model.kernel_families())
+        g = torch.Generator(device=model.device).manual_seed(seed)
+        tensors: Dict[str, torch.Tensor] = {}
+        for path, p in model.parameter_table().items():
+            if p.integer:
+                tensors[path] = torch.zeros(p.shape, dtype=torch.int32, device=model.device)
+                continue
+            mean, std = (1.0, norm_std) if p.init == "ones" else (0.0, matrix_std if p.init == "normal" else 0.0)
+            t = torch.empty(p.shape, dtype=model.dtype, device=model.device)
+            flat = t.view(-1)
+            step = 1 << 26
+            for a in range(0, flat.numel(), step):
+                n = min(step, flat.numel() - a)
+                if std:
+                    flat[a:a + n] = torch.randn(n, generator=g, device=model.device, dtype=torch.float32) * std + mean
+                else:
+                    flat[a:a + n] = mean
+            tensors[path] = t
+        return model.bind(tensors)
+
     # ---- cache ----------------------------------------------------------------------------
     def new_cache(self, max_tokens: int, max_seqs: Optional[int] = None, allocate: bool = True) -> Cache:
         sched = self.spec.schedule

@@ -1,0 +1,211 @@
+"""Each part alone against the plain implementation, and the proof that a new part needs no change
+to the library: a toy mixer with state of its own, defined here, is registered, built and stepped."""
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import bitnet_c_b200 as bn
+from bitnet_c_b200.config import (AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NoPositionSpec, RmsNormSpec,
+                                  RotarySpec, ScheduleEntry)
+from bitnet_c_b200.engine import Model, SeqStep, pack_step
+from bitnet_c_b200.parts import (BuildContext, Mixer, ParamSpec, StateRequest, build_part, register_mixer,
+                                 unregister)
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+
+def ctx_for(dev, lengths_new):
+    """A step of fresh sequences of the given lengths in slots 0..n-1."""
+    seqs = [SeqStep(i, [0] * n) for i, n in enumerate(lengths_new)]
+    return pack_step(seqs, [0] * len(seqs), dev)
+
+
+def randn(gen, *shape, scale=1.0):
+    return torch.randn(*shape, generator=gen) * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(cuda_device, dtype):
+    g = torch.Generator().manual_seed(0)
+    part = build_part("norm", RmsNormSpec(width=72, eps=3e-6), BuildContext(dtype, cuda_device))
+    assert part.params()["weight"].shape == (72,)
+    w = (1 + randn(g, 72, scale=0.1)).to(dtype)
+    part.bind({"weight": w.to(cuda_device)})
+    x, d = randn(g, 5, 72), randn(g, 5, 72).to(dtype)
+    xd = x.to(cuda_device)
+    h = part.add_norm(xd, d.to(cuda_device), None)
+    ref = plain_llama.rmsnorm(x.double().numpy() + d.double().numpy(), w.double().numpy(), 3e-6)
+    assert h.dtype == dtype
+    assert np.abs(h.double().cpu().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 3e-2)
+    assert np.abs(xd.double().cpu().numpy() - (x.double() + d.double()).numpy()).max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rotary_part(cuda_device, dtype):
+    g = torch.Generator().manual_seed(1)
+    part = build_part("position", RotarySpec(head_dim=48, theta=50000.0), BuildContext(dtype, cuda_device))
+    ctx = ctx_for(cuda_device, [5, 130])
+    x = randn(g, 135, 3 * 48).to(dtype)
+    xd = x.to(cuda_device).contiguous()
+    part.rotate(xd, 2, 48, ctx)  # only the first two heads
+    pos = list(range(5)) + list(range(130))
+    heads = x.double().numpy().reshape(135, 3, 48)
+    ref = plain_llama.apply_rope(heads[:, :2], pos, 50000.0)
+    got = xd.double().cpu().numpy().reshape(135, 3, 48)
+    assert np.abs(got[:, :2] - ref).max() < (2e-6 if dtype == torch.float32 else 2e-2)
+    assert np.array_equal(got[:, 2], heads[:, 2])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_mlp_part(cuda_device, dtype):
+    g = torch.Generator().manual_seed(2)
+    part = build_part("ffn", GatedMlpSpec(width=40, intermediate=104), BuildContext(dtype, cuda_device))
+    w = {"gate": randn(g, 104, 40, scale=0.2).to(dtype), "up": randn(g, 104, 40, scale=0.2).to(dtype),
+         "down": randn(g, 40, 104, scale=0.2).to(dtype)}
+    part.bind({k: v.to(cuda_device) for k, v in w.items()})
+    for rows in (3, 50):  # few rows: own kernel; many rows: library product
+        h = randn(g, rows, 40).to(dtype)
+        out = part.forward(h.to(cuda_device), None)
+        ref = plain_llama.swiglu(h.double().numpy(), *(w[k].double().numpy() for k in ("gate", "up", "down")))
+        assert np.abs(out.double().cpu().numpy() - ref).max() < (2e-5 if dtype == torch.float32 else 5e-2)
+
+
+def tiny_spec(mixers, schedule=None, width=32, vocab=50, max_positions=256):
+    norm = RmsNormSpec(width=width, eps=1e-5)
+    blocks = tuple(BlockSpec(mixer=m, ffn=GatedMlpSpec(width=width, intermediate=48), mixer_norm=norm, ffn_norm=norm)
+                   for m in mixers)
+    schedule = schedule or [ScheduleEntry(i) for i in range(len(blocks))]
+    return ModelSpec(vocab_size=vocab, width=width, blocks=blocks, schedule=tuple(schedule), final_norm=norm,
+                     max_positions=max_positions)
+
+
+def random_bind(model, seed, scale=0.3):
+    g = torch.Generator().manual_seed(seed)
+    tensors = {}
+    for path, p in model.parameter_table().items():
+        t = (1 + randn(g, *p.shape, scale=0.1)) if p.init == "ones" else randn(g, *p.shape, scale=scale)
+        tensors[path] = t.to(model.dtype).to(model.device)
+    model.bind(tensors)
+    return {k: v.double().cpu().numpy() for k, v in tensors.items()}
+
+
+def plain_forward_spec(spec, w, tokens):
+    """The plain parts put together for a spec of attention blocks (window and shared caches included)."""
+    T = len(tokens)
+    x = w["embedding.table"][np.asarray(tokens)]
+    kv_of = {}
+    for run, e in enumerate(spec.schedule):
+        b, p = spec.blocks[e.block], f"blocks.{e.block}."
+        a = b.mixer
+        h = plain_llama.rmsnorm(x, w[p + "mixer_norm.weight"], b.mixer_norm.eps)
+        q = (h @ w[p + "mixer.q"].T).reshape(T, a.n_heads, a.head_dim)
+        rot = (lambda z: plain_llama.apply_rope(z, range(T), a.position.theta)) if a.position.kind == "rotary" else (lambda z: z)
+        if e.cache_of is None:
+            k = rot((h @ w[p + "mixer.k"].T).reshape(T, a.n_kv_heads, a.head_dim))
+            v = (h @ w[p + "mixer.v"].T).reshape(T, a.n_kv_heads, a.head_dim)
+            kv_of[run] = (k, v)
+        else:
+            k, v = kv_of[e.cache_of]
+        o = plain_llama.attention(rot(q), k, v, a.softmax_scale, a.window).reshape(T, -1)
+        x = x + o @ w[p + "mixer.o"].T
+        h = plain_llama.rmsnorm(x, w[p + "ffn_norm.weight"], b.ffn_norm.eps)
+        x = x + plain_llama.swiglu(h, w[p + "ffn.gate"], w[p + "ffn.up"], w[p + "ffn.down"])
+    h = plain_llama.rmsnorm(x, w["final_norm.weight"], spec.final_norm.eps)
+    return h @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 6e-2)])
+def test_blocks_differ_layer_by_layer_and_schedule_is_data(cuda_device, dtype, tol):
+    """One model with a full-attention block, a windowed block without position encoding and other head
+    counts, a block that runs twice, and a run that reads another run's cache."""
+    full = AttentionSpec(width=32, n_heads=4, n_kv_heads=2, head_dim=16, position=RotarySpec(16, 10000.0))
+    win = AttentionSpec(width=32, n_heads=2, n_kv_heads=1, head_dim=32, position=NoPositionSpec(), window=70)
+    spec = tiny_spec([full, win], [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(0, cache_of=0),
+                                   ScheduleEntry(1)])
+    model = Model(spec, dtype=dtype, device=cuda_device)
+    w = random_bind(model, 5)
+    cache = model.new_cache(max_tokens=1024, max_seqs=3)
+    assert len(cache.groups) == 2 and cache.groups[0].entries == [0, 2] and cache.groups[1].entries == [1, 4]
+    toks = {"x": np.random.default_rng(0).integers(0, 50, 200).tolist(), "y": [3, 4, 5]}
+    plain = {k: plain_forward_spec(spec, w, v) for k, v in toks.items()}
+    from helpers import compare, replay, trace_batches, trace_tail
+    for steps in (trace_tail(toks, 40), trace_batches([{"x": (toks["x"], 90), "y": (toks["y"], 2)}])):
+        got = replay(model, cache, steps)
+        compare(got, plain, lambda r: tol * max(1.0, np.abs(r).max()), "mixed blocks")
+    # the windowed group gave back the pages that fell out of its window
+    assert cache.groups[1].pool.n_free == cache.groups[1].pool.n_pages
+
+
+@dataclass(frozen=True)
+class DecayMixSpec:
+    """A toy mixer with a state of its own: s_t = decay * s_{t-1} + h_t, out = W s_t."""
+    width: int
+    decay: float
+    kind: str = "toy_decay_mix"
+
+
+def test_a_new_mixer_with_state_needs_no_change_to_the_library(cuda_device):
+    @register_mixer("toy_decay_mix")
+    class DecayMix(Mixer):
+        def params(self):
+            return {"w": ParamSpec((self.spec.width, self.spec.width))}
+
+        def bind(self, tensors):
+            self.w = tensors["w"]
+
+        def state_request(self):
+            return StateRequest((self.spec.width,), torch.float32)
+
+        def forward(self, h, ctx, kv, state):
+            out = torch.empty_like(h, dtype=torch.float32)
+            at = 0
+            for slot, n in zip(ctx.host_slots, ctx.host_new):
+                s = state[slot]
+                for t in range(at, at + n):
+                    s = self.spec.decay * s + h[t].float()
+                    out[t] = s
+                state[slot] = s
+                at += n
+            return (out @ self.w.float().t()).to(h.dtype)
+
+    try:
+        attn = AttentionSpec(width=32, n_heads=2, n_kv_heads=2, head_dim=16, position=RotarySpec(16, 10000.0))
+        spec = tiny_spec([DecayMixSpec(32, 0.9), attn, DecayMixSpec(32, 0.5)])
+        model = Model(spec, dtype="float32", device=cuda_device)
+        assert "blocks.0.mixer.w" in model.parameter_table() and "blocks.1.mixer.q" in model.parameter_table()
+        w = random_bind(model, 6)
+        cache = model.new_cache(max_tokens=512, max_seqs=2)
+        assert set(cache.states) == {0, 2} and cache.states[0].shape == (2, 32) and len(cache.groups) == 1
+
+        def plain(tokens):
+            T = len(tokens)
+            x = w["embedding.table"][np.asarray(tokens)]
+            for i, b in enumerate(spec.blocks):
+                p = f"blocks.{i}."
+                h = plain_llama.rmsnorm(x, w[p + "mixer_norm.weight"], 1e-5)
+                if b.mixer.kind == "toy_decay_mix":
+                    s, rows = np.zeros(32), []
+                    for t in range(T):
+                        s = b.mixer.decay * s + h[t]
+                        rows.append(s)
+                    x = x + np.stack(rows) @ w[p + "mixer.w"].T
+                else:
+                    q = plain_llama.apply_rope((h @ w[p + "mixer.q"].T).reshape(T, 2, 16), range(T), 10000.0)
+                    k = plain_llama.apply_rope((h @ w[p + "mixer.k"].T).reshape(T, 2, 16), range(T), 10000.0)
+                    v = (h @ w[p + "mixer.v"].T).reshape(T, 2, 16)
+                    x = x + plain_llama.attention(q, k, v, 0.25).reshape(T, 32) @ w[p + "mixer.o"].T
+                h = plain_llama.rmsnorm(x, w[p + "ffn_norm.weight"], 1e-5)
+                x = x + plain_llama.swiglu(h, w[p + "ffn.gate"], w[p + "ffn.up"], w[p + "ffn.down"])
+            return plain_llama.rmsnorm(x, w["final_norm.weight"], 1e-5) @ w["head.weight"].T
+
+        from helpers import compare, replay, trace_batches, trace_tail, trace_whole
+        toks = {"p": np.random.default_rng(1).integers(0, 50, 70).tolist(), "q": [9, 8, 7, 6]}
+        ref = {k: plain(v) for k, v in toks.items()}
+        for steps in (trace_whole(toks), trace_tail(toks, 32), trace_batches([{"p": (toks["p"], 10), "q": (toks["q"], 3)}]),
+                      trace_batches([{"q": (toks["q"], 1)}, {"p": (toks["p"], 5)}])):  # the last reuses q's slot: state must be zeroed
+            compare(replay(model, cache, steps), ref, lambda r: 2e-4, "toy mixer")
+    finally:
+        unregister("mixer", "toy_decay_mix")
