@@ -35,6 +35,7 @@ SOURCES: Dict[str, str] = {
     "act": "act.cu",
     "attention": "attention.cu",
     "linear": "linear.cu",
+    "linear_mma": "linear_mma.cu",
     "sampling": "sampling.cu",
 }
 

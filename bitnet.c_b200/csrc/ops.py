@@ -97,9 +97,12 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     width = x.shape[1]
     if weight.shape[0] != width or out.shape[1] != width:
         raise KernelError(f"widths differ: x {width}, weight {weight.shape[0]}, out {out.shape[1]}")
+    n_parts, part_stride = 1, 0
     if delta is not None:
-        _need(delta, "delta", dims=2)
-        if delta.shape != x.shape:
+        _need(delta, "delta")
+        if delta.dim() == 3:  # partial sums of a product that split its inner dimension
+            n_parts, part_stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        if tuple(delta.shape[-2:]) != tuple(x.shape) or delta.dim() not in (2, 3):
             raise KernelError(f"delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
     if rows is not None:
         _need(rows, "rows", torch.int32, 1)
@@ -109,15 +112,24 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     if out.shape[0] < n_rows:
         raise KernelError(f"out has {out.shape[0]} rows, {n_rows} are written")
     _check(_fn("norm", "bn_add_rmsnorm")(_ptr(x), _ptr(delta), c_int(_code(delta) if delta is not None else 0),
-                                         _ptr(weight), c_int(_code(weight)), _ptr(out), c_int(_code(out)),
+                                         c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(weight), c_int(_code(weight)), _ptr(out), c_int(_code(out)),
                                          _ptr(rows), c_int(n_rows), c_int(width), c_float(eps),
                                          c_int(1 if write_x else 0), _stream()), "add_rmsnorm")
     return out
 
 
 # ---- activation ---------------------------------------------------------------------------
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stack gate and up rows as alternating blocks of 8 rows: [g0..g7, u0..u7, g8..g15, u8..u15, ...]."""
+    I, K = gate.shape
+    if I % 8:
+        raise KernelError(f"feed-forward width {I} must be a multiple of 8")
+    return torch.stack([gate.reshape(I // 8, 8, K), up.reshape(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
 def silu_mul(h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(h[t, i]) * h[t, I + i] for rows h = [gate | up]."""
+    """out[t, i] = silu(gate_i) * up_i for rows of h that alternate 8 gate and 8 up values
+    (the layout ``interleave_gate_up`` gives the product's output)."""
     _need(h, "h", dims=2)
     _need(out, "out", h.dtype, 2)
     inter = h.shape[1] // 2
@@ -191,11 +203,27 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
 
 
 # ---- matrix products ----------------------------------------------------------------------
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 16  # float32: warp-per-column kernel up to this many rows
+MMA_MAX_ROWS = 64  # bfloat16: tensor-core streaming kernel up to this many rows
+N_SMS = 148
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is."""
+def _mma_splits(N: int, K: int) -> int:
+    """How many ways the inner dimension is split so that at least two blocks per SM stream weights."""
+    blocks = (N + 63) // 64
+    if blocks >= 2 * N_SMS:
+        return 1
+    return max(1, min((2 * N_SMS + blocks - 1) // blocks, K // 512))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
+           swiglu: bool = False) -> torch.Tensor:
+    """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
+
+    ``allow_partials``: the caller adds the result to the residual and accepts float32 partial
+    sums ``[parts, M, N]`` instead (``add_rmsnorm`` sums them).  ``swiglu``: w holds gate and up
+    rows in alternating blocks of 8 and the result is silu(gate) * up, ``[M, N / 2]``.
+    """
     _need(x, "x", dims=2)
     _need(w, "w", dims=2)
     if x.shape[1] != w.shape[1]:
@@ -205,21 +233,42 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         x = x.to(w.dtype)
     M, K = x.shape
     N = w.shape[0]
+    if w.dtype == torch.bfloat16 and M <= MMA_MAX_ROWS and K % 8 == 0 and (not swiglu or N % 16 == 0):
+        fn = _fn("linear_mma", "bn_linear_mma")
+        if swiglu:
+            out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
+            _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(N // 2),
+                      c_int(2), c_int(1), _stream()), "linear_mma")
+            return out
+        splits = _mma_splits(N, K) if allow_partials else 1
+        if splits > 1:
+            out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+            _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(0), c_int(M), c_int(N), c_int(K), c_int(N), c_int(1),
+                      c_int(splits), _stream()), "linear_mma")
+            return out
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(N), c_int(0),
+                  c_int(1), _stream()), "linear_mma")
+        return out
     if M <= SKINNY_MAX_ROWS and K % 8 == 0:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         _check(_fn("linear", "bn_linear_skinny")(_ptr(x), _ptr(w), c_int(_code(w)), _ptr(out), c_int(_DT[out_dtype]),
                                                  c_int(M), c_int(N), c_int(K), c_int(N), _stream()), "linear_skinny")
-        return out
-    # Many rows: the library product, float32 accumulation, no reduced-precision float32 mode.
-    if w.dtype == torch.float32:
-        if torch.backends.cuda.matmul.allow_tf32:
-            raise KernelError("float32 products need torch.backends.cuda.matmul.allow_tf32 = False")
-        y = torch.matmul(x, w.t())
-    elif out_dtype == torch.float32:
-        y = torch.mm(x, w.t(), out_dtype=torch.float32)
     else:
-        y = torch.matmul(x, w.t())
-    return y if y.dtype == out_dtype else y.to(out_dtype)
+        # Many rows: the library product, float32 accumulation, no reduced-precision float32 mode.
+        if w.dtype == torch.float32:
+            if torch.backends.cuda.matmul.allow_tf32:
+                raise KernelError("float32 products need torch.backends.cuda.matmul.allow_tf32 = False")
+            out = torch.matmul(x, w.t())
+        elif out_dtype == torch.float32:
+            out = torch.mm(x, w.t(), out_dtype=torch.float32)
+        else:
+            out = torch.matmul(x, w.t())
+        out = out if out.dtype == out_dtype else out.to(out_dtype)
+    if swiglu:
+        act = torch.empty((M, N // 2), dtype=out.dtype, device=x.device)
+        return silu_mul(out, act)
+    return out
 
 
 # ---- sampling -----------------------------------------------------------------------------

@@ -16,7 +16,7 @@ class Attention(Mixer):
     over the causal range (optionally the last ``window`` keys); output projection.
     Order and formulas: src/transformer/cpu.c:859-939, src/transformer/gqa_scalar.c:61-121."""
 
-    kernels = ("linear", "attention", "rope")
+    kernels = ("linear", "linear_mma", "attention", "rope")
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -68,4 +68,4 @@ class Attention(Mixer):
         ops.attention_general(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                               s.softmax_scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
                               kv.page_table, kv.k, kv.v)
-        return ops.linear(out, self.w_o, out_dtype=self.build.dtype)
+        return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True)

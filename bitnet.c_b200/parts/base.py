@@ -10,7 +10,8 @@ Interfaces
 ----------
 Norm           ``add_norm(x, delta, ctx, rows=None) -> h``: x (float32 residual, [T, width]) +=
                delta when given; h = norm(x) in the compute type.  With ``rows`` only those
-               rows are normed and x is left alone.
+               rows are normed and x is left alone.  A delta is ``[T, width]`` in any float
+               type, or float32 partial sums ``[parts, T, width]`` that the norm adds up.
 Position       ``rotate(x, n_heads, head_dim, ctx)``: encode positions into the first
                ``n_heads`` heads of each row of x, in place.  May also offer
                ``rotate_and_append(x, n_heads, head_dim, ctx, kv, k_off, v_off)`` that writes

@@ -14,7 +14,7 @@ from .registry import register_ffn
 class GatedMlp(FeedForward):
     """y = W_down (silu(W_gate h) * (W_up h))   (src/transformer/cpu.c:1247-1303)."""
 
-    kernels = ("linear", "act")
+    kernels = ("linear", "linear_mma", "act")
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -29,11 +29,12 @@ class GatedMlp(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors["gate"], tensors["up"]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
-        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        # gate and up rows in alternating blocks of 8: one product gives both, and with few rows
+        # its epilogue applies the activation (the reference stacks gate and up on upload,
+        # src/gpu_cuda.cu:11521-11558, and fuses gate/up + SiLU for decode, src/gpu_cuda.cu:4547)
+        self.w_gate_up = ops.interleave_gate_up(g.to(dt), u.to(dt))
         self.w_down = tensors["down"]
 
     def forward(self, h, ctx):
-        gu = ops.linear(h, self.w_gate_up, out_dtype=self.build.dtype)
-        act = torch.empty((h.shape[0], self.spec.intermediate), dtype=self.build.dtype, device=h.device)
-        ops.silu_mul(gu, act)
-        return ops.linear(act, self.w_down, out_dtype=self.build.dtype)
+        act = ops.linear(h, self.w_gate_up, out_dtype=self.build.dtype, swiglu=True)
+        return ops.linear(act, self.w_down, out_dtype=self.build.dtype, allow_partials=True)

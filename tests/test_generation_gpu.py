@@ -157,7 +157,8 @@ def test_command_line(tmp_path, cuda_device):
                                                               plain_llama.generate(cfg, w, [9], 6)]
     assert "Generation complete tokens=12" in p.stderr and p.stderr.count("token_id=") == 12
     # --no-prefill feeds the prompt token by token and must give the same tokens
-    p2 = subprocess.run(cmd[:2] + cmd[7:] + ["--no-prefill", "--quiet"], capture_output=True, text=True, timeout=600)
+    again = [c for c in cmd if c not in ("--random-weights",)]  # the folder exists now; the unused --config is harmless
+    p2 = subprocess.run(again + ["--no-prefill", "--quiet"], capture_output=True, text=True, timeout=600)
     assert p2.returncode == 0, p2.stderr[-2000:]
     assert [l for l in p2.stderr.splitlines() if l.startswith("token_id=")] == \
            [l for l in p.stderr.splitlines() if l.startswith("token_id=")]

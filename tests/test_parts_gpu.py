@@ -13,6 +13,7 @@ from bitnet_c_b200.engine import Model, SeqStep, pack_step
 from bitnet_c_b200.parts import (BuildContext, Mixer, ParamSpec, StateRequest, build_part, register_mixer,
                                  unregister)
 import plain_llama
+from helpers import bf16_bound
 
 pytestmark = pytest.mark.gpu
 
@@ -117,8 +118,8 @@ def plain_forward_spec(spec, w, tokens):
     return h @ w["head.weight"].T
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 6e-2)])
-def test_blocks_differ_layer_by_layer_and_schedule_is_data(cuda_device, dtype, tol):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_blocks_differ_layer_by_layer_and_schedule_is_data(cuda_device, dtype):
     """One model with a full-attention block, a windowed block without position encoding and other head
     counts, a block that runs twice, and a run that reads another run's cache."""
     full = AttentionSpec(width=32, n_heads=4, n_kv_heads=2, head_dim=16, position=RotarySpec(16, 10000.0))
@@ -126,7 +127,7 @@ def test_blocks_differ_layer_by_layer_and_schedule_is_data(cuda_device, dtype, t
     spec = tiny_spec([full, win], [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(0, cache_of=0),
                                    ScheduleEntry(1)])
     model = Model(spec, dtype=dtype, device=cuda_device)
-    w = random_bind(model, 5)
+    w = random_bind(model, 5, scale=0.12)
     cache = model.new_cache(max_tokens=1024, max_seqs=3)
     assert len(cache.groups) == 2 and cache.groups[0].entries == [0, 2] and cache.groups[1].entries == [1, 4]
     toks = {"x": np.random.default_rng(0).integers(0, 50, 200).tolist(), "y": [3, 4, 5]}
@@ -134,7 +135,7 @@ def test_blocks_differ_layer_by_layer_and_schedule_is_data(cuda_device, dtype, t
     from helpers import compare, replay, trace_batches, trace_tail
     for steps in (trace_tail(toks, 40), trace_batches([{"x": (toks["x"], 90), "y": (toks["y"], 2)}])):
         got = replay(model, cache, steps)
-        compare(got, plain, lambda r: tol * max(1.0, np.abs(r).max()), "mixed blocks")
+        compare(got, plain, (lambda r: 1e-4) if dtype == "float32" else bf16_bound, "mixed blocks")
     # the windowed group gave back the pages that fell out of its window
     assert cache.groups[1].pool.n_free == cache.groups[1].pool.n_pages
 
