@@ -34,6 +34,7 @@ SOURCES: Dict[str, str] = {
     "rope": "rope.cu",
     "act": "act.cu",
     "attention": "attention.cu",
+    "attention_decode": "attention_decode.cu",
     "linear": "linear.cu",
     "linear_mma": "linear_mma.cu",
     "sampling": "sampling.cu",

@@ -202,6 +202,39 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     return out
 
 
+DECODE_CHUNK = 128  # positions per block of the decode attention; must equal DEC_CHUNK in attention_decode.cu
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_seqs: int, n_heads: int, n_kv_heads: int,
+                     head_dim: int, scale: float, window: int, tok_pos: torch.Tensor, slots: torch.Tensor,
+                     page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, max_len: int) -> torch.Tensor:
+    """bfloat16 attention of one new token per sequence (row b of q is sequence b), split over the
+    keys.  ``max_len`` bounds every sequence's length after this step; it sizes the scratch."""
+    if not q.is_cuda or q.stride(-1) != 1 or q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: q must be a bfloat16 CUDA tensor with unit inner stride")
+    _need(out, "out", torch.bfloat16, 2)
+    for t, nm in ((tok_pos, "tok_pos"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_decode: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+    if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads:
+        raise KernelError(f"attention_decode: head_dim={head_dim}, heads {n_heads}/{n_kv_heads} not supported")
+    if out.shape[0] < n_seqs or out.shape[1] != n_heads * head_dim or tok_pos.shape[0] < n_seqs:
+        raise KernelError("attention_decode: out or tok_pos does not fit")
+    n_splits = max(1, (max_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+    part_o = torch.empty((n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+    _check(_fn("attention_decode", "bn_attention_decode")(
+        _ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_float(scale), c_int(window), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
+        c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part_o), _ptr(part_ml), c_int(n_splits),
+        _stream()), "attention_decode")
+    return out
+
+
 # ---- matrix products ----------------------------------------------------------------------
 SKINNY_MAX_ROWS = 16  # float32: warp-per-column kernel up to this many rows
 MMA_MAX_ROWS = 64  # bfloat16: tensor-core streaming kernel up to this many rows

@@ -1,0 +1,85 @@
+"""The decode step with fixed shapes, replayed from a CUDA graph.
+
+A decode step launches some 300 small kernels; at a batch of one the launches cost more than
+the kernels.  ``DecodeRunner`` keeps everything a step reads in fixed device buffers (tokens,
+positions, slots, sampler rows), runs the model's own forward and the sampler once under
+graph capture and replays the graph afterwards.  What changes between steps is data in those
+buffers: the graph ends by moving the sampled tokens into the token buffer and advancing the
+positions, so consecutive steps of an unchanged batch need no host-to-device copy at all.
+The reference does the same for its single sequence: it records its decode op list into a
+CUDA graph and patches position and length in a device struct (src/gpu_cuda.cu:186-310).
+
+Page tables are brought up to date before each replay, outside the graph.  Attention splits
+its keys for the cache's full context, so one graph serves every length.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import Cache
+from ..sampling import Sampler
+from .batch import StepContext
+
+
+class DecodeRunner:
+    def __init__(self, model, cache: Cache, sampler: Sampler, batch: int, pool=None):
+        self.model, self.cache, self.sampler, self.batch = model, cache, sampler, batch
+        dev = model.device
+        B = batch
+        self.meta = torch.zeros(4 * B, dtype=torch.int32, device=dev)
+        self.tokens, self.tok_pos = self.meta[0:B], self.meta[B:2 * B]
+        self.slots, self.index = self.meta[2 * B:3 * B], self.meta[3 * B:4 * B]
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(n_seqs=B, n_tokens=B, tokens=self.tokens, tok_seq=ar[:B], tok_pos=self.tok_pos,
+                               slots=self.slots, seq_start=ar, seq_pos0=self.tok_pos, rows=ar[:B], max_new=1,
+                               max_len=cache.max_positions, decode=True)
+        self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.pool = pool
+        self.warmed = False
+        self.host_slots: Optional[List[int]] = None
+        self.host_rows: Optional[List[int]] = None
+        self.host_pos: Optional[List[int]] = None
+        self.expect_tokens: Optional[List[int]] = None
+        self.uploads = 0
+
+    def _body(self) -> None:
+        logits = self.model.forward(self.cache, self.ctx)
+        out = self.sampler.sample(logits, self.index)
+        self.sampled.copy_(out)
+        self.tokens.copy_(out)
+        self.tok_pos.add_(1)
+
+    def step(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int], rows: Sequence[int]
+             ) -> torch.Tensor:
+        """One token for each sequence; returns the sampled ids (device tensor, valid until the next step)."""
+        slots, tokens, positions, rows = list(slots), list(tokens), list(positions), list(rows)
+        if (slots != self.host_slots or rows != self.host_rows or positions != self.host_pos
+                or tokens != self.expect_tokens):
+            host = torch.from_numpy(np.asarray(tokens + positions + slots + rows, dtype=np.int32)).pin_memory()
+            self.meta.copy_(host, non_blocking=True)
+            self.uploads += 1
+        self.host_slots, self.host_rows = slots, rows
+        if not self.warmed:
+            # the first step runs directly: kernels and libraries finish their lazy set-up,
+            # which must not happen under capture
+            self._body()
+            self.warmed = True
+        else:
+            if self.graph is None:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=self.pool):
+                    self._body()
+                self.graph = g
+            self.graph.replay()
+        self.host_pos = [p + 1 for p in positions]
+        self.expect_tokens = None  # known once the caller has read ``sampled``
+        return self.sampled
+
+    def note_sampled(self, tokens: Sequence[int]) -> None:
+        """The ids the last step sampled, as read by the host: if the next step feeds exactly these,
+        the device buffers are already right."""
+        self.expect_tokens = list(tokens)

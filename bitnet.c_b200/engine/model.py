@@ -70,6 +70,13 @@ class Model:
             t["head.weight"] = ParamSpec((self.spec.vocab_size, self.spec.width))
         return t
 
+    def graph_safe(self) -> bool:
+        """True when every part reads its step from device buffers only, so that a decode step can
+        be recorded once and replayed (parts say so with ``graph_safe = True``)."""
+        def ok(part) -> bool:
+            return bool(getattr(part, "graph_safe", False)) and all(ok(c) for c in part.children().values())
+        return all(ok(b) for b in self.blocks) and ok(self.final_norm)
+
     def kernel_families(self) -> List[str]:
         fams = ["embed", "linear", "sampling"]
         for blk in self.blocks:

@@ -8,6 +8,7 @@ import torch
 from ..cache import Cache
 from ..sampling import Sampler, SamplingParams
 from .batch import SeqStep
+from .decode import DecodeRunner
 from .generate import Completion, Engine, generate
 from .model import Model
 
@@ -16,10 +17,13 @@ class ModelEngine(Engine):
     """Runs steps of ``model`` on ``cache`` and samples on the device; token ids cross to the host
     once per step (the loop's stop decisions need them)."""
 
-    def __init__(self, model: Model, cache: Cache, params: SamplingParams):
+    def __init__(self, model: Model, cache: Cache, params: SamplingParams, use_graphs: bool = True):
         self.model, self.cache, self.params = model, cache, params
         self.max_positions = model.spec.max_positions
         self.sampler: Optional[Sampler] = None
+        self.use_graphs = use_graphs and model.graph_safe()
+        self.runners = {}
+        self.pool = None
 
     def free_tokens(self) -> int:
         return self.cache.tokens_free()
@@ -36,6 +40,7 @@ class ModelEngine(Engine):
     def start_batch(self, first_index: int, prompts: Sequence[Sequence[int]]) -> None:
         self.sampler = Sampler(self.params, len(prompts), self.model.spec.vocab_size, self.model.device,
                                first_index=first_index, prompts=prompts)
+        self.runners = {}  # graphs hold the sampler's buffers: a new batch records new ones
 
     def _index(self, rows: Sequence[int], n_state_rows: int) -> Optional[torch.Tensor]:
         if list(rows) == list(range(n_state_rows)):
@@ -43,9 +48,37 @@ class ModelEngine(Engine):
         return torch.tensor(list(rows), dtype=torch.int32).to(self.model.device, non_blocking=True)
 
     def step_and_sample(self, seqs: Sequence[SeqStep], rows: Sequence[int]) -> List[int]:
+        if self.use_graphs and all(len(s.tokens) == 1 for s in seqs):
+            return self._decode_step(seqs, rows)
         logits = self.model.step(self.cache, seqs)
         out = self.sampler.sample(logits, self._index(rows, self.sampler.n_rows))
         return out.cpu().tolist()
+
+    def _decode_step(self, seqs: Sequence[SeqStep], rows: Sequence[int]) -> List[int]:
+        """One token per sequence through the recorded graph of this batch size."""
+        lengths = self.model.check_step(self.cache, seqs)
+        done = []
+        try:
+            for s in seqs:
+                self.cache.reserve(s.slot, 1)
+                done.append(s)
+        except Exception:
+            for s in done:
+                self.cache.unreserve(s.slot)
+            raise
+        self.cache.sync()
+        B = len(seqs)
+        runner = self.runners.get(B)
+        if runner is None:
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            runner = self.runners[B] = DecodeRunner(self.model, self.cache, self.sampler, B, pool=self.pool)
+        out = runner.step([s.slot for s in seqs], [int(s.tokens[0]) for s in seqs], lengths, list(rows))
+        for s in seqs:
+            self.cache.advance(s.slot, 1)
+        toks = out.cpu().tolist()
+        runner.note_sampled(toks)
+        return toks
 
     def accept(self, tokens: Sequence[int], rows: Sequence[int]) -> None:
         if self.sampler.penalised:

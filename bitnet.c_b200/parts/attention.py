@@ -16,7 +16,8 @@ class Attention(Mixer):
     over the causal range (optionally the last ``window`` keys); output projection.
     Order and formulas: src/transformer/cpu.c:859-939, src/transformer/gqa_scalar.c:61-121."""
 
-    kernels = ("linear", "linear_mma", "attention", "rope")
+    kernels = ("linear", "linear_mma", "attention", "attention_decode", "rope")
+    graph_safe = True
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -65,7 +66,12 @@ class Attention(Mixer):
             qkv = ops.linear(h, self.w_qkv[: s.q_dim], out_dtype=self.build.dtype)
             self.position.rotate(qkv, s.n_heads, s.head_dim, ctx)
         out = torch.empty((n, s.q_dim), dtype=self.build.dtype, device=h.device)
-        ops.attention_general(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim,
-                              s.softmax_scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
-                              kv.page_table, kv.k, kv.v)
+        if ctx.decode and qkv.dtype == torch.bfloat16:
+            # one token per sequence: row b is sequence b; split over the keys
+            ops.attention_decode(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.softmax_scale,
+                                 s.window, ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, ctx.max_len)
+        else:
+            ops.attention_general(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim,
+                                  s.softmax_scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
+                                  kv.page_table, kv.k, kv.v)
         return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True)

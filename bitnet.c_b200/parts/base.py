@@ -71,6 +71,10 @@ class Part:
     """Base of all parts.  ``kernels`` names the kernel families (csrc/build.py) the part launches."""
 
     kernels: Tuple[str, ...] = ()
+    # True if ``forward`` reads the step only from the device tensors of its StepContext (never
+    # from the host lists), launches on the current stream and allocates through torch: such a
+    # part can be recorded into a CUDA graph of the decode step.
+    graph_safe: bool = False
 
     def __init__(self, spec: Any, build: BuildContext):
         self.spec = spec

@@ -13,6 +13,8 @@ class PreNormBlock(Block):
     it anyway; the block's last delta is returned as ``pending`` for whoever norms next.
     """
 
+    graph_safe = True  # as far as its parts are
+
     def __init__(self, spec, build):
         super().__init__(spec, build)
         self.mixer_norm = build_part("norm", spec.mixer_norm, build)

@@ -15,6 +15,7 @@ class GatedMlp(FeedForward):
     """y = W_down (silu(W_gate h) * (W_up h))   (src/transformer/cpu.c:1247-1303)."""
 
     kernels = ("linear", "linear_mma", "act")
+    graph_safe = True
 
     def __init__(self, spec, build):
         super().__init__(spec, build)

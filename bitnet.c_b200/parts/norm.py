@@ -16,6 +16,7 @@ class RmsNorm(Norm):
     (src/transformer/rmsnorm_scalar.c:4-13; fused with the residual as src/gpu_cuda.cu:5077)."""
 
     kernels = ("norm",)
+    graph_safe = True
 
     def params(self) -> Dict[str, ParamSpec]:
         return {"weight": ParamSpec((self.spec.width,), init="ones")}

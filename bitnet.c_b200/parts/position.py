@@ -14,6 +14,7 @@ class Rotary(Position):
     (src/transformer/cpu_backend.c:283-296, src/model_arch.c:322-338)."""
 
     kernels = ("rope",)
+    graph_safe = True
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -34,5 +35,7 @@ class Rotary(Position):
 
 @register_position("none")
 class NoPosition(Position):
+    graph_safe = True
+
     def rotate(self, x, n_heads, head_dim, ctx):
         return None

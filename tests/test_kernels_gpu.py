@@ -270,3 +270,40 @@ def test_linear_mma_swiglu_epilogue(cuda_device, M, I, K):
     yl = ops.linear(xl, w, swiglu=True)
     refl = a / (1 + torch.exp(-a)) * b
     assert yl.shape == (80, I) and ((yl.double() - refl).abs() <= 2.0 ** -6 * refl.abs() + 2e-2).all()
+
+
+@pytest.mark.parametrize("H,KV,hd,lens,window", [
+    (4, 2, 16, [1, 5, 64, 130], 0), (3, 1, 48, [200, 129, 128], 0), (32, 8, 128, [700, 3], 0),
+    (2, 2, 256, [257], 0), (40, 40, 64, [100, 300], 0), (12, 1, 32, [150, 40, 260], 17), (4, 4, 80, [513], 130),
+])
+def test_attention_decode(cuda_device, H, KV, hd, lens, window):
+    """One new token per sequence over scattered pages; a far key is made to dominate one row."""
+    g = torch.Generator().manual_seed(14)
+    n_seq, n_pages, per_seq = len(lens), 80, 16
+    perm = torch.randperm(n_pages, generator=g)[: n_seq * per_seq].reshape(n_seq, per_seq).to(torch.int32)
+    k, v = _paged_cache(cuda_device, "bfloat16", n_pages, KV, hd, 15)
+    ks = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]
+    vs = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]
+    q = (torch.randn(n_seq, H, hd, generator=g) * 0.5).to(torch.bfloat16)
+    if lens[0] > 140 and window == 0:
+        ks[0][2, 0] = (q[0, 0].float() * 4).to(torch.bfloat16)  # key 2, three chunks back, must win for head 0
+    slots = list(range(n_seq))[::-1]
+    for s, L in enumerate(lens):
+        for p in range(L):
+            page = perm[slots[s], p // 64].item()
+            k[page, :, p % 64] = ks[s][p].to(cuda_device)
+            v[page, :, p % 64] = vs[s][p].to(cuda_device)
+    # q sits in a wider row, as in the packed q|k|v buffer
+    wide = torch.zeros(n_seq, H * hd + 32, dtype=torch.bfloat16, device=cuda_device)
+    wide[:, : H * hd] = q.reshape(n_seq, H * hd).to(cuda_device)
+    out = torch.empty(n_seq, H * hd, dtype=torch.bfloat16, device=cuda_device)
+    ops.attention_decode(wide, wide.shape[1], out, n_seq, H, KV, hd, hd ** -0.5, window,
+                         torch.tensor([L - 1 for L in lens], dtype=torch.int32, device=cuda_device),
+                         torch.tensor(slots, dtype=torch.int32, device=cuda_device), perm.to(cuda_device), k, v,
+                         max(lens))
+    got = out.double().cpu().numpy().reshape(n_seq, H, hd)
+    for s, L in enumerate(lens):
+        qfull = np.zeros((L, H, hd))
+        qfull[L - 1] = q[s].double().numpy()
+        ref = plain_llama.attention(qfull, ks[s].double().numpy(), vs[s].double().numpy(), hd ** -0.5, window)[L - 1]
+        assert np.abs(got[s] - ref).max() < 2e-2, f"sequence {s}"
