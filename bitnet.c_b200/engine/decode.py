@@ -45,6 +45,7 @@ class DecodeRunner:
         self.host_pos: Optional[List[int]] = None
         self.expect_tokens: Optional[List[int]] = None
         self.uploads = 0
+        self.launches_per_step = 0
 
     def _body(self) -> None:
         logits = self.model.forward(self.cache, self.ctx)
@@ -63,18 +64,24 @@ class DecodeRunner:
             self.meta.copy_(host, non_blocking=True)
             self.uploads += 1
         self.host_slots, self.host_rows = slots, rows
+        from ..csrc import ops
         if not self.warmed:
             # the first step runs directly: kernels and libraries finish their lazy set-up,
             # which must not happen under capture
+            before = ops.LAUNCHES
             self._body()
+            self.launches_per_step = ops.LAUNCHES - before
             self.warmed = True
         else:
             if self.graph is None:
                 g = torch.cuda.CUDAGraph()
+                before = ops.LAUNCHES
                 with torch.cuda.graph(g, pool=self.pool):
                     self._body()
+                ops.LAUNCHES = before  # recording launches nothing
                 self.graph = g
             self.graph.replay()
+            ops.LAUNCHES += self.launches_per_step  # the replay launches every recorded kernel
         self.host_pos = [p + 1 for p in positions]
         self.expect_tokens = None  # known once the caller has read ``sampled``
         return self.sampled
