@@ -202,6 +202,35 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     return out
 
 
+def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                      scale: float, window: int, tile_seq: torch.Tensor, tile_row0: torch.Tensor,
+                      seq_start: torch.Tensor, seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
+    """bfloat16 causal attention of runs of new tokens on the tensor cores; block i handles up to 64
+    new tokens of sequence tile_seq[i] from its row tile_row0[i] on."""
+    if not q.is_cuda or q.stride(-1) != 1 or q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
+    _need(out, "out", torch.bfloat16, 2)
+    for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"),
+                  (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_prefill: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+    if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads:
+        raise KernelError(f"attention_prefill: head_dim={head_dim}, heads {n_heads}/{n_kv_heads} not supported")
+    if out.shape[1] != n_heads * head_dim or q_stride % 8:
+        raise KernelError("attention_prefill: out or q_stride does not fit")
+    _check(_fn("attention_prefill", "bn_attention_prefill")(
+        _ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), c_int(tile_seq.shape[0]), c_int(n_heads),
+        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), _ptr(tile_seq), _ptr(tile_row0),
+        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
+        _ptr(v_cache), _stream()), "attention_prefill")
+    return out
+
+
 DECODE_CHUNK = 128  # positions per block of the decode attention; must equal DEC_CHUNK in attention_decode.cu
 
 

@@ -16,6 +16,9 @@ import numpy as np
 import torch
 
 
+TILE_ROWS = 64  # new tokens per block of the prefill attention (PF_M in attention_prefill.cu)
+
+
 @dataclass
 class SeqStep:
     """The next tokens of one sequence and the places among them whose logits are wanted."""
@@ -39,6 +42,8 @@ class StepContext:
     max_new: int  # longest run of new tokens in this step
     max_len: int  # longest sequence after this step
     decode: bool  # every sequence brings exactly one token
+    tile_seq: Optional[torch.Tensor] = None  # [n_tiles] int32: the sequence of each block of 64 new tokens
+    tile_row0: Optional[torch.Tensor] = None  # [n_tiles] int32: its first row within the sequence's new tokens
     host_new: List[int] = field(default_factory=list)  # the same facts on the host, for parts that
     host_pos0: List[int] = field(default_factory=list)  # loop over sequences there
     host_slots: List[int] = field(default_factory=list)
@@ -50,10 +55,17 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
     new = [len(s.tokens) for s in seqs]
     T = sum(new)
     n_rows = sum(len(s.want) for s in seqs)
-    buf = np.empty(3 * T + 3 * n + 1 + n_rows, dtype=np.int32)
+    tiles = [(i, r) for i, c in enumerate(new) for r in range(0, c, TILE_ROWS)]
+    n_tiles = len(tiles)
+    buf = np.empty(3 * T + 3 * n + 1 + n_rows + 2 * n_tiles, dtype=np.int32)
     tokens, tok_seq, tok_pos = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
     o = 3 * T
-    slots, seq_start, seq_pos0, rows = buf[o:o + n], buf[o + n:o + 2 * n + 1], buf[o + 2 * n + 1:o + 3 * n + 1], buf[o + 3 * n + 1:]
+    slots, seq_start, seq_pos0 = buf[o:o + n], buf[o + n:o + 2 * n + 1], buf[o + 2 * n + 1:o + 3 * n + 1]
+    r0 = o + 3 * n + 1
+    rows = buf[r0:r0 + n_rows]
+    t0 = r0 + n_rows
+    buf[t0:t0 + n_tiles] = [i for i, _r in tiles]
+    buf[t0 + n_tiles:t0 + 2 * n_tiles] = [r for _i, r in tiles]
     at, r = 0, 0
     for i, s in enumerate(seqs):
         c = new[i]
@@ -70,6 +82,8 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
     return StepContext(
         n_seqs=n, n_tokens=T, tokens=dev[0:T], tok_seq=dev[T:2 * T], tok_pos=dev[2 * T:3 * T],
         slots=dev[o:o + n], seq_start=dev[o + n:o + 2 * n + 1], seq_pos0=dev[o + 2 * n + 1:o + 3 * n + 1],
-        rows=dev[o + 3 * n + 1:] if n_rows else None, max_new=max(new), max_len=max(l + c for l, c in zip(lengths, new)),
-        decode=all(c == 1 for c in new), host_new=new, host_pos0=list(lengths),
+        rows=dev[r0:r0 + n_rows] if n_rows else None, max_new=max(new),
+        max_len=max(l + c for l, c in zip(lengths, new)), decode=all(c == 1 for c in new),
+        tile_seq=dev[t0:t0 + n_tiles], tile_row0=dev[t0 + n_tiles:t0 + 2 * n_tiles], host_new=new,
+        host_pos0=list(lengths),
         host_slots=[s.slot for s in seqs])

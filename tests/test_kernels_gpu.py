@@ -307,3 +307,50 @@ def test_attention_decode(cuda_device, H, KV, hd, lens, window):
         qfull[L - 1] = q[s].double().numpy()
         ref = plain_llama.attention(qfull, ks[s].double().numpy(), vs[s].double().numpy(), hd ** -0.5, window)[L - 1]
         assert np.abs(got[s] - ref).max() < 2e-2, f"sequence {s}"
+
+
+@pytest.mark.parametrize("H,KV,hd,lens,news,window", [
+    (4, 2, 16, [5, 64, 130], [5, 1, 3], 0),
+    (3, 1, 48, [200, 1, 65], [200, 1, 1], 0),
+    (8, 2, 128, [300, 129], [2, 129], 0),
+    (2, 2, 256, [70, 200], [70, 136], 0),
+    (4, 4, 32, [150, 40], [150, 1], 17),
+    (6, 3, 80, [513], [260], 100),
+    (32, 8, 128, [700], [700], 0),
+])
+def test_attention_prefill(cuda_device, H, KV, hd, lens, news, window):
+    """The tensor-core prefill kernel: ragged runs of new tokens after cached ones, scattered pages,
+    head sizes that are padded inside the kernel, windows, and a far key that must dominate."""
+    from bitnet_c_b200.engine import SeqStep, pack_step
+    g = torch.Generator().manual_seed(16)
+    n_seq, n_pages, per_seq = len(lens), 64, 16
+    perm = torch.randperm(n_pages, generator=g)[: n_seq * per_seq].reshape(n_seq, per_seq).to(torch.int32)
+    k, v = _paged_cache(cuda_device, "bfloat16", n_pages, KV, hd, 17)
+    ks = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]
+    vs = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]
+    qs = [(torch.randn(n, H, hd, generator=g) * 0.5).to(torch.bfloat16) for n in news]
+    if lens[0] > 2 and window == 0:
+        ks[0][1, 0] = (qs[0][-1, 0].float() * 4).to(torch.bfloat16)
+    slots = list(range(n_seq))[::-1]
+    for s, L in enumerate(lens):
+        for p in range(L):
+            page = perm[slots[s], p // 64].item()
+            k[page, :, p % 64] = ks[s][p].to(cuda_device)
+            v[page, :, p % 64] = vs[s][p].to(cuda_device)
+    T = sum(news)
+    wide = torch.zeros(T, H * hd + 2 * KV * hd, dtype=torch.bfloat16, device=cuda_device)
+    wide[:, : H * hd] = torch.cat([x.reshape(x.shape[0], H * hd) for x in qs]).to(cuda_device)
+    ctx = pack_step([SeqStep(slots[i], [0] * news[i]) for i in range(n_seq)], [L - n for L, n in zip(lens, news)],
+                    cuda_device)
+    out = torch.full((T, H * hd), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    ops.attention_prefill(wide, wide.shape[1], out, H, KV, hd, hd ** -0.5, window, ctx.tile_seq, ctx.tile_row0,
+                          ctx.seq_start, ctx.seq_pos0, ctx.slots, perm.to(cuda_device), k, v)
+    got = out.double().cpu().numpy().reshape(T, H, hd)
+    at = 0
+    for s, (L, n) in enumerate(zip(lens, news)):
+        qfull = np.zeros((L, H, hd))
+        qfull[L - n:] = qs[s].double().numpy()
+        ref = plain_llama.attention(qfull, ks[s].double().numpy(), vs[s].double().numpy(), hd ** -0.5, window)[L - n:]
+        err = np.abs(got[at:at + n] - ref).max()
+        assert err < 2e-2, f"sequence {s}: {err}"
+        at += n
