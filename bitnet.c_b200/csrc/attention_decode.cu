@@ -50,6 +50,13 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
   const int c0 = split * DEC_CHUNK;
   if (c0 > pos || c0 + DEC_CHUNK <= lo) return;  // no key of this chunk is visible
   const int* pt = page_table + (size_t)slots[b] * pt_stride;
+  // a chunk of 128 positions lies in two pages; their ids are fetched once
+  const int page_a = pt[c0 / BN_PAGE];
+  const int page_b = (c0 + BN_PAGE <= pos) ? pt[c0 / BN_PAGE + 1] : page_a;
+  auto row_off = [&](int j) -> size_t {  // row of key/value j of this chunk (0 <= j < 128)
+    int page = j < BN_PAGE ? page_a : page_b;
+    return (((size_t)page * n_kv_heads + kvh) * BN_PAGE + (j & (BN_PAGE - 1))) * (size_t)head_dim;
+  };
 
   for (int i = tid; i < G * head_dim; i += DEC_THREADS) {
     int g = i / head_dim, d = i - g * head_dim;
@@ -65,16 +72,20 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
 #pragma unroll
     for (int g = 0; g < DEC_GB; ++g) dot[g] = 0.f;
     if (valid) {
-      const __nv_bfloat16* krow = k_cache + cache_row_offset(pt, p, n_kv_heads, kvh, head_dim);
-      for (int d = 0; d < head_dim; d += 8) {
-        float kf[8];
-        bf16x8_to_f32(*reinterpret_cast<const uint4*>(krow + d), kf);
+      const __nv_bfloat16* krow = k_cache + row_off(tid);
+      // head_dim is a multiple of 16: two 16-byte loads are issued before either is used
+      for (int d = 0; d < head_dim; d += 16) {
+        uint4 raw0 = *reinterpret_cast<const uint4*>(krow + d);
+        uint4 raw1 = *reinterpret_cast<const uint4*>(krow + d + 8);
+        float kf[16];
+        bf16x8_to_f32(raw0, kf);
+        bf16x8_to_f32(raw1, kf + 8);
 #pragma unroll
         for (int g = 0; g < DEC_GB; ++g) {
           if (g < G) {
             const float* qq = q_s + g * 256 + d;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) dot[g] = fmaf(qq[e], kf[e], dot[g]);
+            for (int e = 0; e < 16; ++e) dot[g] = fmaf(qq[e], kf[e], dot[g]);
           }
         }
       }
@@ -121,16 +132,27 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
   if (kg < kp) {
     int j_hi = min(DEC_CHUNK, pos - c0 + 1);
     int j_lo = max(0, lo - c0);
-    for (int j = j_lo + kg; j < j_hi; j += kp) {
-      const __nv_bfloat16* vrow = v_cache + cache_row_offset(pt, c0 + j, n_kv_heads, kvh, head_dim);
-      float vf[8];
-      bf16x8_to_f32(*reinterpret_cast<const uint4*>(vrow + piece * 8), vf);
+    // four value rows are requested before the first is used
+    for (int j = j_lo + kg; j < j_hi; j += 4 * kp) {
+      uint4 raw[4];
 #pragma unroll
-      for (int g = 0; g < DEC_GB; ++g) {
-        if (g < G) {
-          float pj = p_s[g * DEC_CHUNK + j];
+      for (int u = 0; u < 4; ++u) {
+        int ju = j + u * kp;
+        raw[u] = ju < j_hi ? *reinterpret_cast<const uint4*>(v_cache + row_off(ju) + piece * 8) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
+      for (int u = 0; u < 4; ++u) {
+        int ju = j + u * kp;
+        if (ju >= j_hi) break;
+        float vf[8];
+        bf16x8_to_f32(raw[u], vf);
+#pragma unroll
+        for (int g = 0; g < DEC_GB; ++g) {
+          if (g < G) {
+            float pj = p_s[g * DEC_CHUNK + ju];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
+          }
         }
       }
     }

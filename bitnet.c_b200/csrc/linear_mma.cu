@@ -15,6 +15,12 @@
 // Epilogues: (0) store; (1) float32 partial sums per K-split, summed by the kernel that adds
 // them to the residual (norm.cu); (2) SwiGLU for a weight whose rows alternate 8 gate rows and
 // 8 up rows, so that one thread holds gate_i and up_i of the same i.
+//
+// A weight with few rows gives too few blocks to keep enough loads in flight, so K may be split
+// over gridDim.y for modes 0 and 2 as well: every block writes its float32 partial tile to
+// scratch, and the block that arrives last at the tile's counter (an atomic ticket, no waiting)
+// adds the partials up in split order and runs the epilogue.  The order of the additions is
+// fixed, so the result does not depend on which block came last.
 // Reference for the operation: y = W x with float32 accumulation (src/quant/bf16_scalar.c:4-21);
 // its decode path is a warp-per-row matvec (src/gpu_cuda.cu:3995) and a fused gate/up + SiLU
 // kernel (src/gpu_cuda.cu:4547).
@@ -56,6 +62,8 @@ struct LmArgs {
   int k_per_split;  // multiple of LM_KC
   int mode;         // 0 store, 1 partial, 2 swiglu
   int ldo;
+  float* scratch;   // modes 0/2 with gridDim.y > 1: [splits][row blocks][64 rows][8*NT] partial tiles
+  int* counters;    // one ticket counter per row block, zero before and after the launch
 };
 
 template <int NT>
@@ -140,6 +148,40 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LmArgs a) {
 
   // c0: (row g, m 2t)  c1: (row g, m 2t+1)  c2: (row g+8, m 2t)  c3: (row g+8, m 2t+1)
   const int n_lo = row0 + g, n_hi = row0 + g + 8;
+  if (a.mode != 1 && gridDim.y > 1) {
+    __shared__ int s_last;
+    const size_t tile_floats = (size_t)LM_ROWS * MP;
+    float* mine = a.scratch + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * tile_floats;
+    // element (row r of the block, column m) of this thread's fragment lives at r * MP + m
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      int m = nt * 8 + 2 * t;
+      *reinterpret_cast<float2*>(mine + (size_t)(warp * 16 + g) * MP + m) = make_float2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<float2*>(mine + (size_t)(warp * 16 + g + 8) * MP + m) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int ticket = atomicAdd(a.counters + blockIdx.x, 1);
+      s_last = (ticket == (int)gridDim.y - 1);
+      if (s_last) a.counters[blockIdx.x] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    for (int sp = 0; sp < (int)gridDim.y; ++sp) {
+      const float* part = a.scratch + ((size_t)sp * gridDim.x + blockIdx.x) * tile_floats;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        int m = nt * 8 + 2 * t;
+        float2 lo = __ldcg(reinterpret_cast<const float2*>(part + (size_t)(warp * 16 + g) * MP + m));
+        float2 hi = __ldcg(reinterpret_cast<const float2*>(part + (size_t)(warp * 16 + g + 8) * MP + m));
+        acc[nt][0] += lo.x; acc[nt][1] += lo.y; acc[nt][2] += hi.x; acc[nt][3] += hi.y;
+      }
+    }
+  }
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -168,21 +210,32 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LmArgs a) {
 
 // x [M, K], w [N, K] bfloat16.  mode 0: out [M, ldo] of out_dtype.  mode 1: out is float32
 // [n_splits, M, N] (every split writes its whole slice).  mode 2: w has N = 2 I rows in blocks
-// of 8 gate / 8 up rows, out [M, ldo] holds silu(gate) * up for I columns; n_splits must be 1.
+// of 8 gate / 8 up rows, out [M, ldo] holds silu(gate) * up for I columns.
+// With n_splits > 1 in modes 0 and 2, scratch must hold n_splits * ceil(N/64) * 64 * Mp floats
+// (Mp = M rounded up to 8, 16, 32 or 64) and counters ceil(N/64) zeroed ints; both may be
+// shared by launches that do not overlap on the device.
 extern "C" int bn_linear_mma(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
-                             int mode, int n_splits, cudaStream_t stream) {
+                             int mode, int n_splits, float* scratch, long long scratch_floats, int* counters,
+                             int n_counters, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
   if (M > 64 || K <= 0 || K % 8 || n_splits < 1 || mode < 0 || mode > 2) return BN_ERR_BAD_ARG;
-  if (mode != 1 && n_splits != 1) return BN_ERR_BAD_ARG;
   if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return BN_ERR_BAD_ARG;
   LmArgs a;
   a.x = (const __nv_bfloat16*)x; a.w = (const __nv_bfloat16*)w; a.out = out; a.out_dtype = out_dtype;
-  a.M = M; a.N = N; a.K = K; a.mode = mode; a.ldo = ldo;
+  a.M = M; a.N = N; a.K = K; a.mode = mode; a.ldo = ldo; a.scratch = scratch; a.counters = counters;
   int chunks = (K + LM_KC - 1) / LM_KC;
+  if (n_splits > chunks) n_splits = chunks;
   a.k_per_split = ((chunks + n_splits - 1) / n_splits) * LM_KC;
-  dim3 grid((N + LM_ROWS - 1) / LM_ROWS, n_splits);
+  n_splits = (chunks * LM_KC + a.k_per_split - 1) / a.k_per_split;  // no empty split
   int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  int row_blocks = (N + LM_ROWS - 1) / LM_ROWS;
+  if (mode != 1 && n_splits > 1) {
+    if (!scratch || !counters || n_counters < row_blocks ||
+        scratch_floats < (long long)n_splits * row_blocks * LM_ROWS * nt * 8)
+      return BN_ERR_BAD_ARG;
+  }
+  dim3 grid(row_blocks, n_splits);
   size_t smem = (size_t)2 * nt * 8 * LM_XS_STRIDE * sizeof(__nv_bfloat16);
   switch (nt) {
     case 1: linear_mma_kernel<1><<<grid, 128, smem, stream>>>(a); break;

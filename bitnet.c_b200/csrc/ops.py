@@ -270,21 +270,45 @@ MMA_MAX_ROWS = 64  # bfloat16: tensor-core streaming kernel up to this many rows
 N_SMS = 148
 
 
-def _mma_splits(N: int, K: int) -> int:
-    """How many ways the inner dimension is split so that at least two blocks per SM stream weights."""
+_SCRATCH_FLOATS = 8 * 1024 * 1024  # 32 MB of split-K partial tiles, shared by all products of a device
+_N_COUNTERS = 8192
+_scratch = {}
+
+
+def _split_scratch(device):
+    """Scratch and ticket counters of the split-K reduction, one set per device, made on first use."""
+    key = torch.device(device).index or 0
+    got = _scratch.get(key)
+    if got is None:
+        got = _scratch[key] = (torch.empty(_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+                               torch.zeros(_N_COUNTERS, dtype=torch.int32, device=device))
+    return got
+
+
+def _mma_splits(M: int, N: int, K: int) -> int:
+    """How many ways the inner dimension is split so that about four blocks per SM stream weights."""
     blocks = (N + 63) // 64
-    if blocks >= 2 * N_SMS:
+    want = 4 * N_SMS
+    if blocks >= want or blocks > _N_COUNTERS:
         return 1
-    return max(1, min((2 * N_SMS + blocks - 1) // blocks, K // 512))
+    mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+    fit = _SCRATCH_FLOATS // (blocks * 64 * mp)
+    splits = max(1, min((want + blocks - 1) // blocks, K // 256, fit))
+    chunks = (K + 127) // 128  # the kernel works in chunks of 128 along K and leaves no split empty
+    per = (chunks + splits - 1) // splits
+    return (chunks + per - 1) // per
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
-           swiglu: bool = False) -> torch.Tensor:
+           swiglu: bool = False, partial_sums: bool = False) -> torch.Tensor:
     """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
 
-    ``allow_partials``: the caller adds the result to the residual and accepts float32 partial
-    sums ``[parts, M, N]`` instead (``add_rmsnorm`` sums them).  ``swiglu``: w holds gate and up
-    rows in alternating blocks of 8 and the result is silu(gate) * up, ``[M, N / 2]``.
+    ``swiglu``: w holds gate and up rows in alternating blocks of 8 and the result is
+    silu(gate) * up, ``[M, N / 2]``.  ``partial_sums``: return the float32 partial sums
+    ``[parts, M, N]`` of a product that split its inner dimension instead of their sum
+    (``add_rmsnorm`` can add them up); by default the product sums them itself.
+    ``allow_partials`` is accepted for callers that add the result to the residual and is
+    ignored.
     """
     _need(x, "x", dims=2)
     _need(w, "w", dims=2)
@@ -297,20 +321,22 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if w.dtype == torch.bfloat16 and M <= MMA_MAX_ROWS and K % 8 == 0 and (not swiglu or N % 16 == 0):
         fn = _fn("linear_mma", "bn_linear_mma")
+        splits = _mma_splits(M, N, K)
+        scratch, counters = _split_scratch(x.device)
+        tail = (_ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters), c_int(counters.numel()), _stream())
         if swiglu:
             out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
             _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(N // 2),
-                      c_int(2), c_int(1), _stream()), "linear_mma")
+                      c_int(2), c_int(splits), *tail), "linear_mma")
             return out
-        splits = _mma_splits(N, K) if allow_partials else 1
-        if splits > 1:
+        if partial_sums and splits > 1:
             out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
             _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(0), c_int(M), c_int(N), c_int(K), c_int(N), c_int(1),
-                      c_int(splits), _stream()), "linear_mma")
+                      c_int(splits), *tail), "linear_mma")
             return out
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(N), c_int(0),
-                  c_int(1), _stream()), "linear_mma")
+                  c_int(splits), *tail), "linear_mma")
         return out
     if M <= SKINNY_MAX_ROWS and K % 8 == 0:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
@@ -338,8 +364,14 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     _need(logits, "logits", torch.float32, 2)
     out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, 1)
-    _check(_fn("sampling", "bn_argmax")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
-                                        c_int(logits.shape[1]), _ptr(out), _stream()), "argmax")
+    n = logits.shape[0]
+    _scr, counters = _split_scratch(logits.device)
+    if n > counters.numel():
+        raise KernelError(f"argmax: at most {counters.numel()} rows at a time")
+    part_v = torch.empty(n * 64, dtype=torch.float32, device=logits.device)
+    part_i = torch.empty(n * 64, dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "bn_argmax")(_ptr(logits), c_int(logits.shape[1]), c_int(n), c_int(logits.shape[1]),
+                                        _ptr(out), _ptr(part_v), _ptr(part_i), _ptr(counters), _stream()), "argmax")
     return out
 
 

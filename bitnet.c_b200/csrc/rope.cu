@@ -8,40 +8,52 @@
 // stored rotated and values as they are (src/transformer/cpu.c:859-898).
 #include "common.cuh"
 
+#define ROPE_THREADS 256
+
+// Work items of one token, spread over the blocks of gridDim.y:
+//   [0, n_rot_heads * half)           one rotation pair (head, i); a pair of a key head also goes to the cache
+//   [.., + n_kv_heads * head_dim)     one value element -> cache, and the key element at the same place if
+//                                     no rotation touched it (dimensions past rotary_dims, or no rotation at all)
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ x, int row_stride, int n_rot_heads, int head_dim,
                                    int rotary_dims, float theta_scale, const int* __restrict__ tok_pos,
                                    int k_off, int v_off, int n_kv_heads, const int* __restrict__ tok_seq,
                                    const int* __restrict__ slots, const int* __restrict__ page_table,
-                                   int pt_stride, T* __restrict__ k_cache,
-                                   T* __restrict__ v_cache) {
-  int t = blockIdx.x;
-  int pos = tok_pos[t];
+                                   int pt_stride, T* __restrict__ k_cache, T* __restrict__ v_cache) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
   T* row = x + (size_t)t * row_stride;
-  int half = rotary_dims >> 1;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+  const int half = rotary_dims >> 1;
+  const int n_pairs = n_rot_heads * half;
+  const int n_copy = k_cache ? n_kv_heads * head_dim : 0;
+  const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
+  if (item >= n_pairs + n_copy) return;
+  const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
+  if (item < n_pairs) {
+    int h = item / half, i = item - h * half;
     float angle = (float)pos;
     for (int k = 0; k < i; ++k) angle *= theta_scale;
     float s, c;
     sincosf(angle, &s, &c);
-    for (int h = 0; h < n_rot_heads; ++h) {
-      T* hd = row + (size_t)h * head_dim;
-      float a = to_f32<T>(hd[i]), b = to_f32<T>(hd[i + half]);
-      hd[i] = from_f32<T>(a * c - b * s);
-      hd[i + half] = from_f32<T>(a * s + b * c);
+    T* hd = row + (size_t)h * head_dim;
+    float a = to_f32<T>(hd[i]), b = to_f32<T>(hd[i + half]);
+    T lo = from_f32<T>(a * c - b * s), hi = from_f32<T>(a * s + b * c);
+    hd[i] = lo;
+    hd[i + half] = hi;
+    int e = h * head_dim - k_off;  // element offset of this head among the key heads
+    if (k_cache && e >= 0 && e < n_kv_heads * head_dim) {
+      size_t off = cache_row_offset(pt, pos, n_kv_heads, e / head_dim, head_dim);
+      k_cache[off + i] = lo;
+      k_cache[off + i + half] = hi;
     }
+    return;
   }
-  if (!k_cache) return;
-  __syncthreads();
-  int slot = slots[tok_seq[t]];
-  const int* pt = page_table + (size_t)slot * pt_stride;
-  int n = n_kv_heads * head_dim;
-  for (int e = threadIdx.x; e < n; e += blockDim.x) {
-    int kvh = e / head_dim, d = e - kvh * head_dim;
-    size_t off = cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d;
-    k_cache[off] = row[k_off + e];
-    v_cache[off] = row[v_off + e];
-  }
+  int e = item - n_pairs;
+  int kvh = e / head_dim, d = e - kvh * head_dim;
+  size_t off = cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d;
+  v_cache[off] = row[v_off + e];
+  bool rotated = d < rotary_dims && (k_off + kvh * head_dim) < n_rot_heads * head_dim;
+  if (!rotated) k_cache[off] = row[k_off + e];
 }
 
 // x: [n_tokens, row_stride] with the heads to rotate first in each row.  When k_cache is
@@ -55,13 +67,17 @@ extern "C" int bn_rope_append(void* x, int dtype, int n_tokens, int row_stride, 
   if (n_tokens <= 0) return BN_OK;
   if (head_dim <= 0 || rotary_dims < 0 || rotary_dims > head_dim || (rotary_dims & 1)) return BN_ERR_BAD_ARG;
   if (k_cache && (!v_cache || !tok_seq || !slots || !page_table)) return BN_ERR_BAD_ARG;
-  int threads = 128;
+  if (k_cache && (k_off % head_dim)) return BN_ERR_BAD_ARG;  // key heads start at a head border
+  int items = n_rot_heads * (rotary_dims / 2) + (k_cache ? n_kv_heads * head_dim : 0);
+  if (items <= 0) return BN_OK;
+  dim3 grid(n_tokens, (items + ROPE_THREADS - 1) / ROPE_THREADS);
+  const int threads = ROPE_THREADS;
   if (dtype == BN_F32)
-    rope_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
+    rope_append_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)x, row_stride, n_rot_heads, head_dim, rotary_dims, theta_scale, tok_pos, k_off, v_off,
         n_kv_heads, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache);
   else if (dtype == BN_BF16)
-    rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+    rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)x, row_stride, n_rot_heads, head_dim, rotary_dims, theta_scale, tok_pos, k_off, v_off,
         n_kv_heads, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache);

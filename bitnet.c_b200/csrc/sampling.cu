@@ -76,42 +76,80 @@ extern "C" int bn_sampler_accept(int* recent, int recent_stride, int* recent_len
   return BN_OK;
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
+#define ARGMAX_BLOCKS 64  // blocks per row: a row of 128k logits is scanned by 64 SMs at once
+
+__device__ __forceinline__ bool argmax_better(float v, int i, float best, int bi) {
+  // larger value wins; on equal values the lower index (src/gpu_cuda.cu:9013-9018)
+  return bi == 0x7fffffff || (i != 0x7fffffff && (v > best || (v == best && i < bi)));
+}
+
+// Each block reduces its slice of a row to (value, index) in part_v / part_i; the block that
+// draws the last ticket of the row reduces the row's slices and writes the result.
+__global__ void argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
+                              float* __restrict__ part_v, int* __restrict__ part_i, int* __restrict__ tickets) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  int r = blockIdx.x;
+  __shared__ int s_last;
+  const int r = blockIdx.x, nb = gridDim.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* l = logits + (size_t)r * ld;
+  const int per = (vocab + nb - 1) / nb;
+  const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     float v = l[i];
-    if (v > best || (v == best && i < bi) || bi == 0x7fffffff) { best = v; bi = i; }
+    if (argmax_better(v, i, best, bi)) { best = v; bi = i; }
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
-  }
-  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    int nw = blockDim.x >> 5;
-    best = lane < nw ? sv[lane] : -INFINITY;
-    bi = lane < nw ? si[lane] : 0x7fffffff;
+  auto block_reduce = [&]() {
     for (int o = 16; o > 0; o >>= 1) {
       float ov = __shfl_xor_sync(0xffffffffu, best, o);
       int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+      if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
     }
-    if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      int nw = blockDim.x >> 5;
+      best = lane < nw ? sv[lane] : -INFINITY;
+      bi = lane < nw ? si[lane] : 0x7fffffff;
+      for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
+      }
+    }
+    __syncthreads();
+  };
+  block_reduce();
+  if (threadIdx.x == 0) {
+    part_v[(size_t)r * nb + blockIdx.y] = best;
+    part_i[(size_t)r * nb + blockIdx.y] = bi;
+    __threadfence();
+    int ticket = atomicAdd(tickets + r, 1);
+    s_last = (ticket == nb - 1);
+    if (s_last) tickets[r] = 0;
   }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  best = -INFINITY;
+  bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) {
+    float v = __ldcg(part_v + (size_t)r * nb + i);
+    int idx = __ldcg(part_i + (size_t)r * nb + i);
+    if (argmax_better(v, idx, best, bi)) { best = v; bi = idx; }
+  }
+  block_reduce();
+  if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
 }
 
-extern "C" int bn_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// part_v / part_i: scratch of n_rows * 64 entries; tickets: n_rows ints, zero before and after.
+extern "C" int bn_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, float* part_v, int* part_i,
+                         int* tickets, cudaStream_t stream) {
   if (n_rows <= 0) return BN_OK;
-  if (vocab <= 0) return BN_ERR_BAD_ARG;
-  argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
+  if (vocab <= 0 || !part_v || !part_i || !tickets) return BN_ERR_BAD_ARG;
+  int nb = vocab >= 8192 ? ARGMAX_BLOCKS : 1;
+  argmax_kernel<<<dim3(n_rows, nb), 256, 0, stream>>>(logits, ld, vocab, out, part_v, part_i, tickets);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }

@@ -237,7 +237,7 @@ def test_linear_mma_store_and_partials(cuda_device, M, N, K):
     assert y.shape == (M, N) and (y.double() - ref).abs().max().item() < bound
     yb = ops.linear(x, w)
     assert yb.dtype == torch.bfloat16 and ((yb.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + bound).all()
-    parts = ops.linear(x, w, allow_partials=True)
+    parts = ops.linear(x, w, partial_sums=True)
     if K >= 1024:
         assert parts.dim() == 3 and parts.dtype == torch.float32 and parts.shape[0] > 1
     total = parts.double().sum(0) if parts.dim() == 3 else parts.double()
@@ -354,3 +354,68 @@ def test_attention_prefill(cuda_device, H, KV, hd, lens, news, window):
         err = np.abs(got[at:at + n] - ref).max()
         assert err < 2e-2, f"sequence {s}: {err}"
         at += n
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_add_rmsnorm_with_partial_sums_and_few_rows(cuda_device, dtype):
+    """Wide rows and few of them take the path that spreads a row over a cluster of blocks."""
+    g = torch.Generator().manual_seed(18)
+    rows, width, parts = 6, 2048, 5
+    x = torch.randn(rows, width, generator=g).to(cuda_device)
+    delta = torch.randn(parts, rows, width, generator=g).to(cuda_device)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DT[dtype]).to(cuda_device)
+    ref_x = x.double() + delta.double().sum(0)
+    ref = ref_x / torch.sqrt((ref_x * ref_x).mean(-1, keepdim=True) + 1e-5) * w.double()
+    out = torch.empty(rows, width, dtype=DT[dtype], device=cuda_device)
+    x1 = x.clone()
+    ops.add_rmsnorm(x1, delta, w, 1e-5, out)
+    assert (x1.double() - ref_x).abs().max().item() < 1e-5
+    assert (out.double() - ref).abs().max().item() < tol(dtype, 1e-5, 3e-2)
+    idx = torch.tensor([4, 1], dtype=torch.int32, device=cuda_device)
+    out2 = torch.empty(2, width, dtype=DT[dtype], device=cuda_device)
+    x2 = x.clone()
+    ops.add_rmsnorm(x2, delta, w, 1e-5, out2, rows=idx)
+    assert torch.equal(x2, x)
+    assert (out2.double() - ref[idx.long()]).abs().max().item() < tol(dtype, 1e-5, 3e-2)
+
+
+def test_rope_partial_rotation_and_plain_append(cuda_device):
+    """rotary_dims below head_dim leaves the upper dimensions as they are (they still reach the cache);
+    with no rotation at all the kernel is a plain append."""
+    H, KV, hd, rd, theta = 2, 2, 32, 16, 10000.0
+    g = torch.Generator().manual_seed(19)
+    x = torch.randn(3, (H + 2 * KV) * hd, generator=g).to(cuda_device)
+    x0 = x.clone()
+    tok_seq = torch.zeros(3, dtype=torch.int32, device=cuda_device)
+    tok_pos = torch.tensor([62, 63, 64], dtype=torch.int32, device=cuda_device)
+    slots = torch.tensor([1], dtype=torch.int32, device=cuda_device)
+    pt = torch.tensor([[0, 0], [5, 2]], dtype=torch.int32, device=cuda_device)
+    k = torch.zeros(8, KV, 64, hd, device=cuda_device)
+    v = torch.zeros(8, KV, 64, hd, device=cuda_device)
+    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(rd)))
+    ops.rope_append(x, H + KV, hd, rd, scale, tok_pos, k_off=H * hd, v_off=(H + KV) * hd, n_kv_heads=KV,
+                    tok_seq=tok_seq, slots=slots, page_table=pt, k_cache=k, v_cache=v)
+    heads = x0.double().cpu().numpy().reshape(3, H + 2 * KV, hd)
+    rot = plain_llama.apply_rope(heads[:, : H + KV], [62, 63, 64], theta, dims=rd)
+    got = x.double().cpu().numpy().reshape(3, H + 2 * KV, hd)
+    assert np.abs(got[:, : H + KV] - rot).max() < 2e-6
+    assert np.array_equal(got[:, : H + KV, rd:], heads[:, : H + KV, rd:])
+    for t, (page, row) in enumerate([(5, 62), (5, 63), (2, 0)]):
+        assert np.array_equal(k[page, :, row].double().cpu().numpy(), got[t, H:H + KV])
+        assert np.array_equal(v[page, :, row].double().cpu().numpy(), heads[t, H + KV:])
+    k2, v2 = torch.zeros_like(k), torch.zeros_like(v)
+    ops.rope_append(x0.clone(), 0, hd, 0, 1.0, tok_pos, k_off=H * hd, v_off=(H + KV) * hd, n_kv_heads=KV,
+                    tok_seq=tok_seq, slots=slots, page_table=pt, k_cache=k2, v_cache=v2)
+    assert np.array_equal(k2[5, :, 62].double().cpu().numpy(), heads[0, H:H + KV]) and torch.equal(v2, v)
+
+
+def test_argmax_large_vocabulary(cuda_device):
+    g = torch.Generator().manual_seed(20)
+    logits = torch.randn(9, 128256, generator=g).to(cuda_device)
+    logits[0, 77] = logits[0, 100000] = 40.0
+    logits[1, 128255] = 41.0
+    logits[2, :] = -float("inf")
+    got = ops.argmax(logits).cpu().tolist()
+    ref = [int(np.argmax(r)) for r in logits.cpu().numpy()]
+    assert got == ref and got[0] == 77 and got[2] == 0
+    assert ops.argmax(logits).cpu().tolist() == ref  # the tickets were left at zero
