@@ -38,6 +38,7 @@ SOURCES: Dict[str, str] = {
     "attention_prefill": "attention_prefill.cu",
     "linear": "linear.cu",
     "linear_mma": "linear_mma.cu",
+    "linear_tc": "linear_tc.cu",
     "sampling": "sampling.cu",
 }
 

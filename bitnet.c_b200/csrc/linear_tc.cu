@@ -1,0 +1,347 @@
+// out[M, N] = x[M, K] . W[N, K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05),
+// for M <= 64: weights stream HBM -> shared memory by TMA, products accumulate in tensor memory.
+//
+// The roles are swapped so that the weight is the 128-row operand: D[128 weight rows, Mp batch
+// columns] += W_tile[128, 64] . x_tile[Mp, 64]^T, one tcgen05.mma of shape M=128, N=Mp, K=16 per 16
+// columns of k, issued by one thread.  A block of 192 threads:
+//   warp 0     one thread issues the TMA loads of W and x tiles into a ring of TC_STAGES stages and
+//              arms each stage's "full" mbarrier with the bytes to expect;
+//   warp 1     allocates tensor memory; one thread waits for "full", issues four MMAs per stage
+//              and commits them to the stage's "empty" mbarrier, and at the end to "accumulator full";
+//   warps 2-5  wait for the accumulator, read it from tensor memory (tcgen05.ld, one weight row per
+//              thread) and run the epilogue.
+// Tiles are 128-byte swizzled both by TMA and in the MMA's shared-memory descriptors.  No
+// register ever holds a weight, so the bytes in flight per SM are the ring's size.
+//
+// K may be split over gridDim.y: every block writes its float32 tile to scratch, and the block
+// that draws the last ticket of the tile adds the partial tiles in split order and runs the
+// epilogue (no block waits for another).  Epilogues: (0) store, (2) SwiGLU over weight rows that
+// alternate 8 gate and 8 up rows.
+//
+// Every wait on an mbarrier is bounded in time; when a wait gives up the block records a code
+// in *status, lets its loads drain for a bounded time, frees its tensor memory and returns.
+//
+// Reference for the operation: y = W x with float32 accumulation (src/quant/bf16_scalar.c:4-21);
+// the reference's CUDA backend reaches tensor cores only through cuBLAS (src/gpu_cuda.cu:11850-11879).
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#define TC_BM 128      // weight rows per tile (UMMA M)
+#define TC_BK 64       // k per stage: 128 bytes of bfloat16, one swizzle row
+#define TC_STAGES 4
+#define TC_THREADS 192
+#define TC_WAIT_NS 2000000000ull  // two seconds
+
+#define TC_ERR_FULL_WAIT 1
+#define TC_ERR_EMPTY_WAIT 2
+#define TC_ERR_ACC_WAIT 3
+
+struct TcArgs {
+  void* out;
+  int out_dtype;
+  int M, N, K;
+  int ldo;
+  int mode;        // 0 store, 2 swiglu
+  int k_blocks;    // ceil(K / 64)
+  float* scratch;  // [splits][tiles][128][Mp] when gridDim.y > 1
+  int* counters;   // one ticket per tile, zero before and after
+  int* status;     // 0, or the code of a wait that gave up
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and *status set) when the phase did not complete within TC_WAIT_NS.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = global_timer();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_timer() - t0 > TC_WAIT_NS) {
+      atomicExch(status, code);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// start address >> 4; leading byte offset 1 (unused for swizzled K-major); stride byte offset
+// 1024 >> 4 between groups of 8 rows; descriptor version 1; layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ unsigned long long umma_desc(unsigned addr) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned addr, float* v) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int MP>  // batch columns of the accumulator: 16, 32 or 64
+__global__ void __launch_bounds__(TC_THREADS)
+linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  constexpr int A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
+  constexpr int B_BYTES = MP * TC_BK * 2;      // 2, 4 or 8 KB
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr unsigned TMEM_COLS = MP < 32 ? 32 : MP;
+  // instruction descriptor: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both
+  // K-major, N >> 3 at bit 17, M >> 4 at bit 24
+  constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(MP >> 3) << 17) | ((TC_BM >> 4) << 24);
+
+  unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
+  __shared__ int s_last;
+  __shared__ int s_failed;
+  __shared__ int s_acc_ok;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x;
+  const int splits = gridDim.y;
+  const int kb0 = (int)((long long)blockIdx.y * a.k_blocks / splits);
+  const int kb1 = (int)((long long)(blockIdx.y + 1) * a.k_blocks / splits);
+  const int n_kb = kb1 - kb0;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES), acc_bar = smem_u32(bars + 2 * TC_STAGES);
+
+  if (tid == 0) {
+    s_failed = 0;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        int s = i % TC_STAGES, round = i / TC_STAGES;
+        if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, a.status, TC_ERR_EMPTY_WAIT)) { s_failed = 1; break; }
+        unsigned dst = smem_u32(base + s * STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(dst, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, tile * TC_BM);
+        tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        int s = i % TC_STAGES, round = i / TC_STAGES;
+        if (!mbar_wait(full0 + 8 * s, round & 1, a.status, TC_ERR_FULL_WAIT)) { s_failed = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned sa = smem_u32(base + s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 16; ++kk)
+          umma_bf16(tmem_base, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC, (i | kk) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
+      }
+      umma_commit(acc_bar);  // arrives when every MMA above has written the accumulator
+    }
+  } else {
+    // ---- epilogue warps: TMEM lane quadrant warp % 4, one weight row per thread
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const int n = tile * TC_BM + row_in_tile;
+    float v[MP];
+    // one thread waits (bounded) for the accumulator; the four warps then agree on the outcome
+    if (warp == 2 && lane == 0) {
+      s_acc_ok = mbar_wait(acc_bar, 0, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
+      if (!s_acc_ok) s_failed = 1;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = s_acc_ok != 0;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+#pragma unroll
+      for (int c = 0; c < MP; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + c, v + c);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int c = 0; c < MP; ++c) v[c] = 0.f;
+    }
+    bool run_epilogue = ok;
+    if (ok && splits > 1) {
+      const size_t tile_floats = (size_t)TC_BM * MP;
+      float* mine = a.scratch + ((size_t)blockIdx.y * gridDim.x + tile) * tile_floats + (size_t)row_in_tile * MP;
+#pragma unroll
+      for (int c = 0; c < MP; c += 4) *reinterpret_cast<float4*>(mine + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        int ticket = atomicAdd(a.counters + tile, 1);
+        s_last = (ticket == splits - 1);
+        if (s_last) a.counters[tile] = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      run_epilogue = s_last != 0;
+      if (run_epilogue) {
+        __threadfence();
+#pragma unroll
+        for (int c = 0; c < MP; ++c) v[c] = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+          const float* part = a.scratch + ((size_t)sp * gridDim.x + tile) * tile_floats + (size_t)row_in_tile * MP;
+#pragma unroll
+          for (int c = 0; c < MP; c += 4) {
+            float4 p = __ldcg(reinterpret_cast<const float4*>(part + c));
+            v[c] += p.x; v[c + 1] += p.y; v[c + 2] += p.z; v[c + 3] += p.w;
+          }
+        }
+      }
+    }
+    if (run_epilogue) {
+      if (a.mode == 0) {
+        if (n < a.N) {
+#pragma unroll
+          for (int m = 0; m < MP; ++m)
+            if (m < a.M) store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + n, v[m]);
+        }
+      } else {
+        // rows 16j..16j+7 are gate rows 8j.., rows 16j+8..16j+15 the up rows of the same indices:
+        // lane L (L % 16 < 8) holds a gate value and lane L + 8 the matching up value
+        const int i = (n >> 4) * 8 + (n & 7);
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+          float other = __shfl_xor_sync(0xffffffffu, v[m], 8);
+          if ((lane & 8) == 0 && m < a.M && n < a.N) {
+            float g = v[m];
+            store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + i, g / (1.0f + expf(-g)) * other);
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s_failed) {
+    // a wait gave up: loads that were issued may still be landing in this block's shared memory
+    unsigned long long t0 = global_timer();
+    while (global_timer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+static PFN_cuTensorMapEncodeTiled get_encode() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled)p;
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix, loaded in boxes of box_rows x 64 with 128-byte swizzle;
+// rows and columns outside the matrix read as zero.
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  PFN_cuTensorMapEncodeTiled enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MP>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+    configured = true;
+  }
+  linear_tc_kernel<MP><<<grid, TC_THREADS, smem, stream>>>(mw, mx, a);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// x [M, K], w [N, K] bfloat16, both 16-byte aligned with K a multiple of 8.  mode 0: out [M, ldo]
+// of out_dtype; mode 2: N = 2 I weight rows in blocks of 8 gate / 8 up rows, out holds
+// silu(gate) * up in I columns.  With n_splits > 1: scratch of n_splits * ceil(N/128) * 128 * Mp
+// floats (Mp = 16, 32 or 64 >= M) and ceil(N/128) zeroed ticket counters.  status: one int on the
+// device, left 0 unless a wait inside the kernel gave up.
+extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
+                            int mode, int n_splits, float* scratch, long long scratch_floats, int* counters,
+                            int n_counters, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return BN_OK;
+  if (M > 64 || K <= 0 || K % 8 || n_splits < 1 || (mode != 0 && mode != 2) || !status) return BN_ERR_BAD_ARG;
+  if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return BN_ERR_BAD_ARG;
+  int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  int tiles = (N + TC_BM - 1) / TC_BM;
+  int k_blocks = (K + TC_BK - 1) / TC_BK;
+  if (n_splits > k_blocks) n_splits = k_blocks;
+  if (n_splits > 1 && (!scratch || !counters || n_counters < tiles ||
+                       scratch_floats < (long long)n_splits * tiles * TC_BM * mp))
+    return BN_ERR_BAD_ARG;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, N, K, TC_BM) || !make_map(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
+  TcArgs a;
+  a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
+  a.k_blocks = k_blocks; a.scratch = scratch; a.counters = counters; a.status = status;
+  dim3 grid(tiles, n_splits);
+  if (mp == 16) return launch_tc<16>(mw, mx, a, grid, stream);
+  if (mp == 32) return launch_tc<32>(mw, mx, a, grid, stream);
+  return launch_tc<64>(mw, mx, a, grid, stream);
+}

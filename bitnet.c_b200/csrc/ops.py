@@ -299,6 +299,62 @@ def _mma_splits(M: int, N: int, K: int) -> int:
     return (chunks + per - 1) // per
 
 
+_tc_status = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """One int per device that the tcgen05 product sets when a wait inside it gave up (0 = fine)."""
+    key = torch.device(device).index or 0
+    got = _tc_status.get(key)
+    if got is None:
+        got = _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return got
+
+
+def check_tc_status(device) -> None:
+    """Raise if a tcgen05 product on ``device`` reported a wait that gave up (synchronises)."""
+    code = int(tc_status(device).item())
+    if code:
+        tc_status(device).zero_()
+        what = {1: "a stage never filled (TMA load)", 2: "a stage was never released (MMA commit)",
+                3: "the accumulator never completed"}.get(code, f"code {code}")
+        raise KernelError(f"linear_tc: {what}; the result of that product is not valid")
+
+
+def _tc_splits(M: int, N: int, K: int) -> int:
+    """Splits of the inner dimension so that about three blocks per SM stream weights, each over
+    at least four 64-wide pieces of K."""
+    tiles = (N + 127) // 128
+    want = 3 * N_SMS
+    if tiles >= want or tiles > _N_COUNTERS:
+        return 1
+    mp = 16 if M <= 16 else 32 if M <= 32 else 64
+    fit = _SCRATCH_FLOATS // (tiles * 128 * mp)
+    k_blocks = (K + 63) // 64
+    return max(1, min((want + tiles - 1) // tiles, k_blocks // 4, fit))
+
+
+def linear_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
+              splits: Optional[int] = None) -> torch.Tensor:
+    """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or M > MMA_MAX_ROWS or K % 8 or (swiglu and N % 16):
+        raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)} not supported")
+    out_dtype = out_dtype or x.dtype
+    cols = N // 2 if swiglu else N
+    out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
+    scratch, counters = _split_scratch(x.device)
+    splits = _tc_splits(M, N, K) if splits is None else splits
+    _check(_fn("linear_tc", "bn_linear_tc")(
+        _ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(cols),
+        c_int(2 if swiglu else 0), c_int(splits), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters),
+        c_int(counters.numel()), _ptr(tc_status(x.device)), _stream()), "linear_tc")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
            swiglu: bool = False, partial_sums: bool = False) -> torch.Tensor:
     """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
