@@ -3,20 +3,34 @@
 //
 // The roles are swapped so that the weight is the 128-row operand: D[128 weight rows, Mp batch
 // columns] += W_tile[128, 64] . x_tile[Mp, 64]^T, one tcgen05.mma of shape M=128, N=Mp, K=16 per 16
-// columns of k, issued by one thread.  A block of 192 threads:
+// columns of k, issued by one thread.
+//
+// Work is cut stream-K fashion: the tiles x k-blocks space (tile = 128 weight rows, k-block = 64
+// columns) is one line of units, and each of the (at most one per SM) persistent blocks takes a
+// contiguous stretch of it, so every block streams the same number of bytes whatever N and K
+// are.  A stretch crosses tile borders: each (block, tile) piece is a *segment* with its own
+// accumulator.  A segment that covers a whole tile runs the epilogue directly.  A tile that is
+// shared between blocks is finished through scratch: every block writes its float32 partial tile
+// and draws a ticket of the tile's counter; the one that draws the last ticket adds the partials
+// in block order and runs the epilogue.  No block ever waits for another.
+//
+// A block of 192 threads:
 //   warp 0     one thread issues the TMA loads of W and x tiles into a ring of TC_STAGES stages and
 //              arms each stage's "full" mbarrier with the bytes to expect;
-//   warp 1     allocates tensor memory; one thread waits for "full", issues four MMAs per stage
-//              and commits them to the stage's "empty" mbarrier, and at the end to "accumulator full";
-//   warps 2-5  wait for the accumulator, read it from tensor memory (tcgen05.ld, one weight row per
-//              thread) and run the epilogue.
+//   warp 1     allocates tensor memory (two accumulators); one thread waits for "full", issues four
+//              MMAs per stage, commits them to the stage's "empty" mbarrier and, at the end of a
+//              segment, to that accumulator's "full" mbarrier;
+//   warps 2-5  wait for an accumulator, read it from tensor memory (tcgen05.ld, one weight row per
+//              thread), release it, and run the partial-tile protocol and the epilogue, while the
+//              MMA thread already fills the other accumulator.
 // Tiles are 128-byte swizzled both by TMA and in the MMA's shared-memory descriptors.  No
-// register ever holds a weight, so the bytes in flight per SM are the ring's size.
+// register ever holds a weight, so the bytes in flight per SM are the ring's size (144-192 KB).
 //
-// K may be split over gridDim.y: every block writes its float32 tile to scratch, and the block
-// that draws the last ticket of the tile adds the partial tiles in split order and runs the
-// epilogue (no block waits for another).  Epilogues: (0) store, (2) SwiGLU over weight rows that
-// alternate 8 gate and 8 up rows.
+// The kernel is launched with programmatic stream serialization: the loads of its first weight
+// tiles are issued before griddepcontrol.wait, i.e. while the kernel before it in the stream is
+// still draining; everything that reads x or writes memory comes after the wait.
+//
+// Epilogues: (0) store, (2) SwiGLU over weight rows that alternate 8 gate and 8 up rows.
 //
 // Every wait on an mbarrier is bounded in time; when a wait gives up the block records a code
 // in *status, lets its loads drain for a bounded time, frees its tensor memory and returns.
@@ -29,13 +43,14 @@
 
 #define TC_BM 128      // weight rows per tile (UMMA M)
 #define TC_BK 64       // k per stage: 128 bytes of bfloat16, one swizzle row
-#define TC_STAGES 4
+#define TC_STAGES 8
 #define TC_THREADS 192
 #define TC_WAIT_NS 2000000000ull  // two seconds
 
 #define TC_ERR_FULL_WAIT 1
 #define TC_ERR_EMPTY_WAIT 2
 #define TC_ERR_ACC_WAIT 3
+#define TC_ERR_ACC_FREE_WAIT 4
 
 struct TcArgs {
   void* out;
@@ -44,7 +59,8 @@ struct TcArgs {
   int ldo;
   int mode;        // 0 store, 2 swiglu
   int k_blocks;    // ceil(K / 64)
-  float* scratch;  // [splits][tiles][128][Mp] when gridDim.y > 1
+  int tiles;       // ceil(N / 128)
+  float* scratch;  // [blocks][2][128][Mp] partial tiles of the first and last segment of a block
   int* counters;   // one ticket per tile, zero before and after
   int* status;     // 0, or the code of a wait that gave up
 };
@@ -60,6 +76,9 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
   unsigned ok;
@@ -115,32 +134,57 @@ __device__ __forceinline__ void tmem_ld16(unsigned addr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int MP>  // batch columns of the accumulator: 16, 32 or 64
+// The stretch of units of block c: [unit_start(c), unit_start(c + 1)).
+__device__ __forceinline__ long long unit_start(long long c, long long total, int blocks) { return c * total / blocks; }
+// The block whose stretch holds unit u.
+__device__ __forceinline__ int block_of(long long u, long long total, int blocks) {
+  int c = (int)(u * blocks / total);
+  while (c + 1 < blocks && unit_start(c + 1, total, blocks) <= u) ++c;
+  while (c > 0 && unit_start(c, total, blocks) > u) --c;
+  return c;
+}
+
+// Walks the segments of a block's stretch: (tile, first k-block, one past the last k-block).
+struct Segments {
+  long long u, u_end;
+  int kb;
+  __device__ Segments(long long u0, long long u1, int k_blocks) : u(u0), u_end(u1), kb(k_blocks) {}
+  __device__ bool next(int& tile, int& kb_lo, int& kb_hi) {
+    if (u >= u_end) return false;
+    tile = (int)(u / kb);
+    kb_lo = (int)(u - (long long)tile * kb);
+    long long left = u_end - u;
+    kb_hi = (int)min((long long)kb, kb_lo + left);
+    u += kb_hi - kb_lo;
+    return true;
+  }
+};
+
+template <int MP>  // batch columns of an accumulator: 16, 32 or 64
 __global__ void __launch_bounds__(TC_THREADS)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
   constexpr int B_BYTES = MP * TC_BK * 2;      // 2, 4 or 8 KB
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr unsigned TMEM_COLS = MP < 32 ? 32 : MP;
+  constexpr unsigned TMEM_COLS = 2 * MP < 32 ? 32 : 2 * MP;  // two accumulators; a power of two >= 32
   // instruction descriptor: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both
   // K-major, N >> 3 at bit 17, M >> 4 at bit 24
   constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(MP >> 3) << 17) | ((TC_BM >> 4) << 24);
 
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
-  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 4);
   __shared__ int s_last;
   __shared__ int s_failed;
   __shared__ int s_acc_ok;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tile = blockIdx.x;
-  const int splits = gridDim.y;
-  const int kb0 = (int)((long long)blockIdx.y * a.k_blocks / splits);
-  const int kb1 = (int)((long long)(blockIdx.y + 1) * a.k_blocks / splits);
-  const int n_kb = kb1 - kb0;
-  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES), acc_bar = smem_u32(bars + 2 * TC_STAGES);
+  const int blocks = gridDim.x;
+  const long long total = (long long)a.tiles * a.k_blocks;
+  const long long u0 = unit_start(blockIdx.x, total, blocks), u1 = unit_start(blockIdx.x + 1, total, blocks);
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES);
+  const unsigned acc_full0 = smem_u32(bars + 2 * TC_STAGES), acc_free0 = smem_u32(bars + 2 * TC_STAGES + 2);
 
   if (tid == 0) {
     s_failed = 0;
@@ -150,7 +194,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_free0 + 8 * b, 128);  // every epilogue thread arrives
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -162,103 +209,153 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
+  // the kernel that follows in the stream may start its own prologue now
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
-        int s = i % TC_STAGES, round = i / TC_STAGES;
-        if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, a.status, TC_ERR_EMPTY_WAIT)) { s_failed = 1; break; }
-        unsigned dst = smem_u32(base + s * STAGE_BYTES);
-        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-        tma_load_2d(dst, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, tile * TC_BM);
-        tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, 0);
+      // Weights do not depend on the kernel before this one: the first ring of W tiles is
+      // requested before the dependency wait, the matching x tiles after it.
+      int tile, kb_lo, kb_hi, it = 0;
+      {
+        Segments seg(u0, u1, a.k_blocks);
+        while (it < TC_STAGES && seg.next(tile, kb_lo, kb_hi)) {
+          for (int kb = kb_lo; kb < kb_hi && it < TC_STAGES; ++kb, ++it) {
+            mbar_expect_tx(full0 + 8 * it, STAGE_BYTES);
+            tma_load_2d(smem_u32(base + it * STAGE_BYTES), &map_w, full0 + 8 * it, kb * TC_BK, tile * TC_BM);
+          }
+          if (it >= TC_STAGES) break;
+        }
       }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      Segments seg(u0, u1, a.k_blocks);
+      it = 0;
+      bool failed = false;
+      while (!failed && seg.next(tile, kb_lo, kb_hi)) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+          int s = it % TC_STAGES, round = it / TC_STAGES;
+          unsigned dst = smem_u32(base + s * STAGE_BYTES);
+          if (round > 0) {
+            if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, a.status, TC_ERR_EMPTY_WAIT)) { failed = true; break; }
+            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_2d(dst, &map_w, full0 + 8 * s, kb * TC_BK, tile * TC_BM);
+          }
+          tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, kb * TC_BK, 0);
+        }
+      }
+      if (failed) s_failed = 1;
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
-        int s = i % TC_STAGES, round = i / TC_STAGES;
-        if (!mbar_wait(full0 + 8 * s, round & 1, a.status, TC_ERR_FULL_WAIT)) { s_failed = 1; break; }
+      Segments seg(u0, u1, a.k_blocks);
+      int tile, kb_lo, kb_hi, it = 0, j = 0;
+      bool failed = false;
+      while (!failed && seg.next(tile, kb_lo, kb_hi)) {
+        const int buf = j & 1;
+        // the epilogue must have emptied this accumulator (first use of each: passes at once)
+        if (!mbar_wait(acc_free0 + 8 * buf, ((j >> 1) & 1) ^ 1, a.status, TC_ERR_ACC_FREE_WAIT)) { failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned sa = smem_u32(base + s * STAGE_BYTES), sb = sa + A_BYTES;
+        const unsigned tmem_d = tmem_base + buf * MP;
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+          int s = it % TC_STAGES, round = it / TC_STAGES;
+          if (!mbar_wait(full0 + 8 * s, round & 1, a.status, TC_ERR_FULL_WAIT)) { failed = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned sa = smem_u32(base + s * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < TC_BK / 16; ++kk)
-          umma_bf16(tmem_base, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC, (i | kk) ? 1u : 0u);
-        umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
+          for (int kk = 0; kk < TC_BK / 16; ++kk)
+            umma_bf16(tmem_d, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC, (kb > kb_lo || kk) ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
+        }
+        if (!failed) umma_commit(acc_full0 + 8 * buf);  // arrives when the segment's MMAs are done
+        ++j;
       }
-      umma_commit(acc_bar);  // arrives when every MMA above has written the accumulator
+      if (failed) s_failed = 1;
     }
   } else {
     // ---- epilogue warps: TMEM lane quadrant warp % 4, one weight row per thread
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
-    const int n = tile * TC_BM + row_in_tile;
+    const size_t tile_floats = (size_t)TC_BM * MP;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // before any global write of this kernel
+    Segments seg(u0, u1, a.k_blocks);
+    int tile, kb_lo, kb_hi, j = 0;
     float v[MP];
-    // one thread waits (bounded) for the accumulator; the four warps then agree on the outcome
-    if (warp == 2 && lane == 0) {
-      s_acc_ok = mbar_wait(acc_bar, 0, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
-      if (!s_acc_ok) s_failed = 1;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ok = s_acc_ok != 0;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-#pragma unroll
-      for (int c = 0; c < MP; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + c, v + c);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    } else {
-#pragma unroll
-      for (int c = 0; c < MP; ++c) v[c] = 0.f;
-    }
-    bool run_epilogue = ok;
-    if (ok && splits > 1) {
-      const size_t tile_floats = (size_t)TC_BM * MP;
-      float* mine = a.scratch + ((size_t)blockIdx.y * gridDim.x + tile) * tile_floats + (size_t)row_in_tile * MP;
-#pragma unroll
-      for (int c = 0; c < MP; c += 4) *reinterpret_cast<float4*>(mine + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+    while (seg.next(tile, kb_lo, kb_hi)) {
+      const int buf = j & 1;
+      // one thread waits (bounded) for the accumulator; the four warps then agree on the outcome
       if (warp == 2 && lane == 0) {
-        int ticket = atomicAdd(a.counters + tile, 1);
-        s_last = (ticket == splits - 1);
-        if (s_last) a.counters[tile] = 0;
+        s_acc_ok = mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
+        if (!s_acc_ok) s_failed = 1;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      run_epilogue = s_last != 0;
-      if (run_epilogue) {
+      if (!s_acc_ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < MP; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + buf * MP + c, v + c);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(acc_free0 + 8 * buf);  // the MMA thread may overwrite this accumulator
+
+      const int n = tile * TC_BM + row_in_tile;
+      bool run_epilogue = true;
+      if (kb_lo != 0 || kb_hi != a.k_blocks) {
+        // a tile shared with other blocks: slot 0 holds a block's first segment, slot 1 its last
+        const long long t0 = (long long)tile * a.k_blocks;
+        const int c_first = block_of(t0, total, blocks), c_last = block_of(t0 + a.k_blocks - 1, total, blocks);
+        const int my_slot = (j == 0) ? 0 : 1;
+        float* mine = a.scratch + ((size_t)blockIdx.x * 2 + my_slot) * tile_floats + (size_t)row_in_tile * MP;
+#pragma unroll
+        for (int c = 0; c < MP; c += 4) *reinterpret_cast<float4*>(mine + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
         __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          int ticket = atomicAdd(a.counters + tile, 1);
+          s_last = (ticket == c_last - c_first);
+          if (s_last) a.counters[tile] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        run_epilogue = s_last != 0;
+        if (run_epilogue) {
+          __threadfence();
 #pragma unroll
-        for (int c = 0; c < MP; ++c) v[c] = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {
-          const float* part = a.scratch + ((size_t)sp * gridDim.x + tile) * tile_floats + (size_t)row_in_tile * MP;
+          for (int c = 0; c < MP; ++c) v[c] = 0.f;
+          for (int cb = c_first; cb <= c_last; ++cb) {
+            // block cb's piece of this tile is its first segment iff its stretch starts inside the tile
+            long long cs = unit_start(cb, total, blocks);
+            int slot = (cs >= t0) ? 0 : 1;
+            // a block whose stretch starts exactly at the tile start also uses slot 0 (j == 0)
+            const float* part = a.scratch + ((size_t)cb * 2 + slot) * tile_floats + (size_t)row_in_tile * MP;
 #pragma unroll
-          for (int c = 0; c < MP; c += 4) {
-            float4 p = __ldcg(reinterpret_cast<const float4*>(part + c));
-            v[c] += p.x; v[c + 1] += p.y; v[c + 2] += p.z; v[c + 3] += p.w;
+            for (int c = 0; c < MP; c += 4) {
+              float4 p = __ldcg(reinterpret_cast<const float4*>(part + c));
+              v[c] += p.x; v[c + 1] += p.y; v[c + 2] += p.z; v[c + 3] += p.w;
+            }
           }
         }
       }
-    }
-    if (run_epilogue) {
-      if (a.mode == 0) {
-        if (n < a.N) {
+      if (run_epilogue) {
+        if (a.mode == 0) {
+          if (n < a.N) {
 #pragma unroll
-          for (int m = 0; m < MP; ++m)
-            if (m < a.M) store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + n, v[m]);
-        }
-      } else {
-        // rows 16j..16j+7 are gate rows 8j.., rows 16j+8..16j+15 the up rows of the same indices:
-        // lane L (L % 16 < 8) holds a gate value and lane L + 8 the matching up value
-        const int i = (n >> 4) * 8 + (n & 7);
+            for (int m = 0; m < MP; ++m)
+              if (m < a.M) store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + n, v[m]);
+          }
+        } else {
+          // rows 16j..16j+7 are gate rows 8j.., rows 16j+8..16j+15 the up rows of the same indices:
+          // lane L (L % 16 < 8) holds a gate value and lane L + 8 the matching up value
+          const int i = (n >> 4) * 8 + (n & 7);
 #pragma unroll
-        for (int m = 0; m < MP; ++m) {
-          float other = __shfl_xor_sync(0xffffffffu, v[m], 8);
-          if ((lane & 8) == 0 && m < a.M && n < a.N) {
-            float g = v[m];
-            store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + i, g / (1.0f + expf(-g)) * other);
+          for (int m = 0; m < MP; ++m) {
+            float other = __shfl_xor_sync(0xffffffffu, v[m], 8);
+            if ((lane & 8) == 0 && m < a.M && n < a.N) {
+              float g = v[m];
+              store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + i, g / (1.0f + expf(-g)) * other);
+            }
           }
         }
       }
+      ++j;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps take the segments in lockstep
     }
   }
 
@@ -302,46 +399,67 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
 template <int MP>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
-  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + 1024;
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int blocks, cudaStream_t stream) {
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
-  linear_tc_kernel<MP><<<grid, TC_THREADS, smem, stream>>>(mw, mx, a);
-  BN_CHECK_LAUNCH();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_tc_kernel<MP>, mw, mx, a);
+  if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
   return BN_OK;
 }
 
 // x [M, K], w [N, K] bfloat16, both 16-byte aligned with K a multiple of 8.  mode 0: out [M, ldo]
 // of out_dtype; mode 2: N = 2 I weight rows in blocks of 8 gate / 8 up rows, out holds
-// silu(gate) * up in I columns.  With n_splits > 1: scratch of n_splits * ceil(N/128) * 128 * Mp
-// floats (Mp = 16, 32 or 64 >= M) and ceil(N/128) zeroed ticket counters.  status: one int on the
-// device, left 0 unless a wait inside the kernel gave up.
+// silu(gate) * up in I columns.  max_blocks caps the number of persistent blocks (0: one per SM).
+// scratch: blocks * 2 * 128 * Mp floats (Mp = 16, 32 or 64 >= M); counters: ceil(N/128) zeroed
+// ints; both may be shared by launches that do not overlap.  status: one int on the device, left 0
+// unless a wait inside the kernel gave up.
 extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
-                            int mode, int n_splits, float* scratch, long long scratch_floats, int* counters,
+                            int mode, int max_blocks, float* scratch, long long scratch_floats, int* counters,
                             int n_counters, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
-  if (M > 64 || K <= 0 || K % 8 || n_splits < 1 || (mode != 0 && mode != 2) || !status) return BN_ERR_BAD_ARG;
+  if (M > 64 || K <= 0 || K % 8 || max_blocks < 0 || (mode != 0 && mode != 2) || !status) return BN_ERR_BAD_ARG;
   if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return BN_ERR_BAD_ARG;
   int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   int tiles = (N + TC_BM - 1) / TC_BM;
   int k_blocks = (K + TC_BK - 1) / TC_BK;
-  if (n_splits > k_blocks) n_splits = k_blocks;
-  if (n_splits > 1 && (!scratch || !counters || n_counters < tiles ||
-                       scratch_floats < (long long)n_splits * tiles * TC_BM * mp))
+  long long total = (long long)tiles * k_blocks;
+  int blocks = max_blocks > 0 ? max_blocks : sm_count();
+  if (blocks > total) blocks = (int)total;
+  if (!scratch || !counters || n_counters < tiles || scratch_floats < (long long)blocks * 2 * TC_BM * mp)
     return BN_ERR_BAD_ARG;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, TC_BM) || !make_map(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
   TcArgs a;
   a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
-  a.k_blocks = k_blocks; a.scratch = scratch; a.counters = counters; a.status = status;
-  dim3 grid(tiles, n_splits);
-  if (mp == 16) return launch_tc<16>(mw, mx, a, grid, stream);
-  if (mp == 32) return launch_tc<32>(mw, mx, a, grid, stream);
-  return launch_tc<64>(mw, mx, a, grid, stream);
+  a.k_blocks = k_blocks; a.tiles = tiles; a.scratch = scratch; a.counters = counters; a.status = status;
+  if (mp == 16) return launch_tc<16>(mw, mx, a, blocks, stream);
+  if (mp == 32) return launch_tc<32>(mw, mx, a, blocks, stream);
+  return launch_tc<64>(mw, mx, a, blocks, stream);
 }

@@ -267,6 +267,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_seqs: 
 # ---- matrix products ----------------------------------------------------------------------
 SKINNY_MAX_ROWS = 16  # float32: warp-per-column kernel up to this many rows
 MMA_MAX_ROWS = 64  # bfloat16: tensor-core streaming kernel up to this many rows
+USE_TCGEN05 = True  # small-batch bfloat16 products run on tcgen05 (linear_tc.cu); False: mma.sync (linear_mma.cu)
 N_SMS = 148
 
 
@@ -321,37 +322,26 @@ def check_tc_status(device) -> None:
         raise KernelError(f"linear_tc: {what}; the result of that product is not valid")
 
 
-def _tc_splits(M: int, N: int, K: int) -> int:
-    """Splits of the inner dimension so that about three blocks per SM stream weights, each over
-    at least four 64-wide pieces of K."""
-    tiles = (N + 127) // 128
-    want = 3 * N_SMS
-    if tiles >= want or tiles > _N_COUNTERS:
-        return 1
-    mp = 16 if M <= 16 else 32 if M <= 32 else 64
-    fit = _SCRATCH_FLOATS // (tiles * 128 * mp)
-    k_blocks = (K + 63) // 64
-    return max(1, min((want + tiles - 1) // tiles, k_blocks // 4, fit))
-
-
 def linear_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-              splits: Optional[int] = None) -> torch.Tensor:
-    """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands."""
+              max_blocks: int = 0) -> torch.Tensor:
+    """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands.
+    ``max_blocks`` caps the persistent blocks that share the work (0: one per SM)."""
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or M > MMA_MAX_ROWS or K % 8 or (swiglu and N % 16):
         raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)} not supported")
+    if (N + 127) // 128 > _N_COUNTERS:
+        raise KernelError(f"linear_tc: {N} output columns exceed the {_N_COUNTERS * 128} the ticket counters cover")
     out_dtype = out_dtype or x.dtype
     cols = N // 2 if swiglu else N
     out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
     scratch, counters = _split_scratch(x.device)
-    splits = _tc_splits(M, N, K) if splits is None else splits
     _check(_fn("linear_tc", "bn_linear_tc")(
         _ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(cols),
-        c_int(2 if swiglu else 0), c_int(splits), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters),
-        c_int(counters.numel()), _ptr(tc_status(x.device)), _stream()), "linear_tc")
+        c_int(2 if swiglu else 0), c_int(max_blocks), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
+        _ptr(counters), c_int(counters.numel()), _ptr(tc_status(x.device)), _stream()), "linear_tc")
     return out
 
 
@@ -375,7 +365,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         x = x.to(w.dtype)
     M, K = x.shape
     N = w.shape[0]
-    if w.dtype == torch.bfloat16 and M <= MMA_MAX_ROWS and K % 8 == 0 and (not swiglu or N % 16 == 0):
+    small = w.dtype == torch.bfloat16 and M <= MMA_MAX_ROWS and K % 8 == 0 and (not swiglu or N % 16 == 0)
+    if small and not partial_sums and USE_TCGEN05:
+        return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
+    if small:
         fn = _fn("linear_mma", "bn_linear_mma")
         splits = _mma_splits(M, N, K)
         scratch, counters = _split_scratch(x.device)

@@ -14,7 +14,7 @@ from .registry import register_ffn
 class GatedMlp(FeedForward):
     """y = W_down (silu(W_gate h) * (W_up h))   (src/transformer/cpu.c:1247-1303)."""
 
-    kernels = ("linear", "linear_mma", "act")
+    kernels = ("linear", "linear_mma", "linear_tc", "act")
     graph_safe = True
 
     def __init__(self, spec, build):
