@@ -8,6 +8,8 @@
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ h, T* __restrict__ out, int inter, size_t total) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   size_t t = idx / inter;
@@ -25,9 +27,9 @@ extern "C" int bn_silu_mul(const void* h, void* out, int dtype, int n_rows, int 
   size_t total = (size_t)n_rows * inter;
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == BN_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)h, (float*)out, inter, total);
+    BN_LAUNCH((silu_mul_kernel<float>), blocks, 256, 0, stream, (const float*)h, (float*)out, inter, total);
   else if (dtype == BN_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)h, (__nv_bfloat16*)out, inter, total);
+    BN_LAUNCH((silu_mul_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)out, inter, total);
   else
     return BN_ERR_BAD_ARG;
   BN_CHECK_LAUNCH();

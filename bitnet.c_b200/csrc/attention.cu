@@ -45,6 +45,8 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
                                          const int* __restrict__ tok_pos, const int* __restrict__ slots,
                                          const int* __restrict__ page_table, int pt_stride,
                                          const T* __restrict__ k_cache, const T* __restrict__ v_cache) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ float sm[];
   float* qs = sm;                    // head_dim
   float* ps = qs + head_dim;         // ATT_CHUNK scores, then probabilities
@@ -125,11 +127,11 @@ extern "C" int bn_attention_general(const void* q, int q_stride, void* out, int 
   dim3 grid(n_tokens, n_heads);
   size_t smem = (head_dim + ATT_CHUNK + 32) * sizeof(float);
   if (dtype == BN_F32)
-    attention_general_kernel<float><<<grid, ATT_THREADS, smem, stream>>>(
+    BN_LAUNCH((attention_general_kernel<float>), grid, ATT_THREADS, smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window,
         tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache);
   else if (dtype == BN_BF16)
-    attention_general_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
+    BN_LAUNCH((attention_general_kernel<__nv_bfloat16>), grid, ATT_THREADS, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim,
         scale, window, tok_seq, tok_pos, slots, page_table, pt_stride,
         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);

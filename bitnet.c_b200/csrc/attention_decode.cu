@@ -36,6 +36,8 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
                                 const int* __restrict__ slots, const int* __restrict__ page_table, int pt_stride,
                                 const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                                 float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   __shared__ float q_s[DEC_GB * 256];
   __shared__ float p_s[DEC_GB * DEC_CHUNK];
   __shared__ float red[DEC_THREADS * DEC_GB * 8];
@@ -176,6 +178,8 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
                                                 int n_splits, int head_dim, int window,
                                                 const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
                                                 int out_stride, int n_heads) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const int pos = tok_pos[b];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -210,12 +214,12 @@ extern "C" int bn_attention_decode(const void* q, int q_stride, void* out, int o
   int gblocks = (group + DEC_GB - 1) / DEC_GB;
   if ((long long)n_kv_heads * gblocks > 65535 || n_splits > 65535 || n_heads > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits);
-  attention_decode_partial_kernel<<<grid, DEC_THREADS, 0, stream>>>(
+  BN_LAUNCH(attention_decode_partial_kernel, grid, DEC_THREADS, 0, stream, 
       (const __nv_bfloat16*)q, q_stride, n_heads, n_kv_heads, head_dim, scale, window, tok_pos, slots, page_table,
       pt_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_o, part_ml, n_splits);
   BN_CHECK_LAUNCH();
   int threads = ((head_dim + 31) / 32) * 32;
-  attention_decode_combine_kernel<<<dim3(n_seqs, n_heads), threads, 0, stream>>>(
+  BN_LAUNCH(attention_decode_combine_kernel, dim3(n_seqs, n_heads), threads, 0, stream, 
       part_o, part_ml, n_splits, head_dim, window, tok_pos, (__nv_bfloat16*)out, out_stride, n_heads);
   BN_CHECK_LAUNCH();
   return BN_OK;

@@ -62,6 +62,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                          const int* __restrict__ slots, const int* __restrict__ page_table, int pt_stride,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE_BYTES = PF_N * HD * 2;
   constexpr int CHUNKS = HD / 8;   // 16-byte chunks per row
@@ -258,7 +260,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
     configured = true;
   }
   dim3 grid(n_tiles, n_heads);
-  attention_prefill_kernel<HD><<<grid, PF_THREADS, smem, stream>>>(
+  BN_LAUNCH((attention_prefill_kernel<HD>), grid, PF_THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim,
       scale * 1.4426950408889634f, window, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
       (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);

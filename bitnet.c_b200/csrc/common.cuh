@@ -21,6 +21,46 @@
 #define BN_ERR_BAD_ARG 1
 #define BN_ERR_LAUNCH 2
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// Every kernel of this library is launched with programmatic stream serialization: it may start
+// while the kernel before it in the stream is still running, and calls pdl_wait() before its
+// first access to global memory that another kernel may write (or, for writes, read).  Kernels
+// call pdl_launch_dependents() early so that their successor's prologue overlaps them.  What a
+// kernel does before pdl_wait() touches only read-only weights, shared and tensor memory.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+#include <utility>
+static inline bool bn_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("BN_NO_PDL");  // set to serialise kernels completely (for comparison)
+    on = (e && e[0] && e[0] != '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t bn_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = bn_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#define BN_LAUNCH(kernel, grid, block, smem, stream, ...)                                  \
+  do {                                                                                     \
+    cudaError_t e__ = bn_launch(kernel, grid, block, smem, stream, __VA_ARGS__);           \
+    if (e__ != cudaSuccess) return BN_ERR_LAUNCH + (int)e__;                               \
+  } while (0)
+
 #define BN_CHECK_LAUNCH()                                    \
   do {                                                       \
     cudaError_t e__ = cudaGetLastError();                    \

@@ -7,6 +7,8 @@ template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ out, int width, int vocab, float scale,
                                     int* __restrict__ bad_token) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   int t = blockIdx.x;
   int id = tokens[t];
   float* o = out + (size_t)t * width;
@@ -27,9 +29,9 @@ extern "C" int bn_embed_gather(const void* table, int table_dtype, const int* to
   if (width <= 0 || vocab <= 0) return BN_ERR_BAD_ARG;
   int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == BN_F32)
-    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, tokens, out, width, vocab, scale, bad_token);
+    BN_LAUNCH((embed_gather_kernel<float>), n_tokens, threads, 0, stream, (const float*)table, tokens, out, width, vocab, scale, bad_token);
   else if (table_dtype == BN_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, width, vocab, scale, bad_token);
+    BN_LAUNCH((embed_gather_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, width, vocab, scale, bad_token);
   else
     return BN_ERR_BAD_ARG;
   BN_CHECK_LAUNCH();

@@ -35,6 +35,8 @@ struct VecLd<__nv_bfloat16> {
 template <typename T>
 __global__ void linear_skinny_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ out,
                                      int out_dtype, int M, int N, int K, int ldo) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int n = blockIdx.x * SK_WARPS + warp;
   if (n >= N) return;
@@ -75,10 +77,10 @@ extern "C" int bn_linear_skinny(const void* x, const void* w, int dtype, void* o
   if (K <= 0 || K % 8 || ldo < N) return BN_ERR_BAD_ARG;
   unsigned blocks = (unsigned)((N + SK_WARPS - 1) / SK_WARPS);
   if (dtype == BN_F32)
-    linear_skinny_kernel<float><<<blocks, SK_WARPS * 32, 0, stream>>>((const float*)x, (const float*)w, out,
+    BN_LAUNCH((linear_skinny_kernel<float>), blocks, SK_WARPS * 32, 0, stream, (const float*)x, (const float*)w, out,
                                                                     out_dtype, M, N, K, ldo);
   else if (dtype == BN_BF16)
-    linear_skinny_kernel<__nv_bfloat16><<<blocks, SK_WARPS * 32, 0, stream>>>(
+    BN_LAUNCH((linear_skinny_kernel<__nv_bfloat16>), blocks, SK_WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, out_dtype, M, N, K, ldo);
   else
     return BN_ERR_BAD_ARG;

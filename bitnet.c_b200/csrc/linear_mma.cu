@@ -68,6 +68,8 @@ struct LmArgs {
 
 template <int NT>
 __global__ void __launch_bounds__(128) linear_mma_kernel(LmArgs a) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][NT*8][LM_XS_STRIDE]
   constexpr int MP = NT * 8;

@@ -47,6 +47,8 @@ add_rmsnorm_cluster_kernel(float* __restrict__ x, const void* __restrict__ delta
                            size_t part_stride, const void* __restrict__ w, int w_dtype, void* __restrict__ out,
                            int out_dtype, const int* __restrict__ rows, int width, int cols_per_block, float eps,
                            int write_x) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   __shared__ float scratch[32];
   __shared__ float block_ss;
   cg::cluster_group cluster = cg::this_cluster();
@@ -95,6 +97,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
                                    int n_parts, size_t part_stride, const void* __restrict__ w, int w_dtype, void* __restrict__ out,
                                    int out_dtype, const int* __restrict__ rows, int width, float eps,
                                    int write_x) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ float v[];  // width floats, then 32 for the reduction
   float* scratch = v + width;
   int r = blockIdx.x;
@@ -130,7 +134,7 @@ extern "C" int bn_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
   bool aligned = width % 8 == 0 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w | (uintptr_t)delta) & 15) == 0 &&
                  (part_stride % 8) == 0;
   if (n_rows <= 256 && width >= 1024 && aligned && cols <= NORM_CL_THREADS * NORM_CL_VEC * 4) {
-    add_rmsnorm_cluster_kernel<<<dim3(n_rows, NORM_CLUSTER), NORM_CL_THREADS, 0, stream>>>(
+    BN_LAUNCH(add_rmsnorm_cluster_kernel, dim3(n_rows, NORM_CLUSTER), NORM_CL_THREADS, 0, stream, 
         x, delta, delta_dtype, n_parts, (size_t)part_stride, w, w_dtype, out, out_dtype, rows, width, cols, eps,
         write_x);
     BN_CHECK_LAUNCH();
@@ -147,7 +151,7 @@ extern "C" int bn_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
     }
   }
   int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<<<n_rows, threads, smem, stream>>>(x, delta, delta_dtype, n_parts, (size_t)part_stride, w,
+  BN_LAUNCH(add_rmsnorm_kernel, n_rows, threads, smem, stream, x, delta, delta_dtype, n_parts, (size_t)part_stride, w,
                                                        w_dtype, out, out_dtype,
                                                        rows, width, eps, write_x);
   BN_CHECK_LAUNCH();

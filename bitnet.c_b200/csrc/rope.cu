@@ -20,6 +20,8 @@ __global__ void rope_append_kernel(T* __restrict__ x, int row_stride, int n_rot_
                                    int k_off, int v_off, int n_kv_heads, const int* __restrict__ tok_seq,
                                    const int* __restrict__ slots, const int* __restrict__ page_table,
                                    int pt_stride, T* __restrict__ k_cache, T* __restrict__ v_cache) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   T* row = x + (size_t)t * row_stride;
@@ -73,11 +75,11 @@ extern "C" int bn_rope_append(void* x, int dtype, int n_tokens, int row_stride, 
   dim3 grid(n_tokens, (items + ROPE_THREADS - 1) / ROPE_THREADS);
   const int threads = ROPE_THREADS;
   if (dtype == BN_F32)
-    rope_append_kernel<float><<<grid, threads, 0, stream>>>(
+    BN_LAUNCH((rope_append_kernel<float>), grid, threads, 0, stream, 
         (float*)x, row_stride, n_rot_heads, head_dim, rotary_dims, theta_scale, tok_pos, k_off, v_off,
         n_kv_heads, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache);
   else if (dtype == BN_BF16)
-    rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+    BN_LAUNCH((rope_append_kernel<__nv_bfloat16>), grid, threads, 0, stream, 
         (__nv_bfloat16*)x, row_stride, n_rot_heads, head_dim, rotary_dims, theta_scale, tok_pos, k_off, v_off,
         n_kv_heads, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache);

@@ -26,6 +26,8 @@ __global__ void repeat_penalty_kernel(float* __restrict__ logits, int ld, int vo
                                       const int* __restrict__ recent, int recent_stride,
                                       const int* __restrict__ recent_len, const int* __restrict__ index,
                                       float penalty) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   int r = blockIdx.x;
   int sr = index ? index[r] : r;
   const int* ids = recent + (size_t)sr * recent_stride;
@@ -47,7 +49,7 @@ extern "C" int bn_repeat_penalty(float* logits, int ld, int n_rows, int vocab, c
                                  int recent_stride, const int* recent_len, const int* index, float penalty,
                                  cudaStream_t stream) {
   if (n_rows <= 0 || recent_stride <= 0) return BN_OK;
-  repeat_penalty_kernel<<<n_rows, 64, 0, stream>>>(logits, ld, vocab, recent, recent_stride, recent_len, index,
+  BN_LAUNCH(repeat_penalty_kernel, n_rows, 64, 0, stream, logits, ld, vocab, recent, recent_stride, recent_len, index,
                                                   penalty);
   BN_CHECK_LAUNCH();
   return BN_OK;
@@ -58,6 +60,8 @@ extern "C" int bn_repeat_penalty(float* logits, int ld, int n_rows, int vocab, c
 __global__ void accept_kernel(int* __restrict__ recent, int recent_stride, int* __restrict__ recent_len,
                               int* __restrict__ recent_pos, const int* __restrict__ index,
                               const int* __restrict__ tokens, int n_rows) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n_rows) return;
   int sr = index ? index[r] : r;
@@ -70,7 +74,7 @@ __global__ void accept_kernel(int* __restrict__ recent, int recent_stride, int* 
 extern "C" int bn_sampler_accept(int* recent, int recent_stride, int* recent_len, int* recent_pos,
                                  const int* index, const int* tokens, int n_rows, cudaStream_t stream) {
   if (n_rows <= 0 || recent_stride <= 0) return BN_OK;
-  accept_kernel<<<(n_rows + 127) / 128, 128, 0, stream>>>(recent, recent_stride, recent_len, recent_pos, index,
+  BN_LAUNCH(accept_kernel, (n_rows + 127) / 128, 128, 0, stream, recent, recent_stride, recent_len, recent_pos, index,
                                                          tokens, n_rows);
   BN_CHECK_LAUNCH();
   return BN_OK;
@@ -87,6 +91,8 @@ __device__ __forceinline__ bool argmax_better(float v, int i, float best, int bi
 // draws the last ticket of the row reduces the row's slices and writes the result.
 __global__ void argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
                               float* __restrict__ part_v, int* __restrict__ part_i, int* __restrict__ tickets) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int s_last;
@@ -149,7 +155,7 @@ extern "C" int bn_argmax(const float* logits, int ld, int n_rows, int vocab, int
   if (n_rows <= 0) return BN_OK;
   if (vocab <= 0 || !part_v || !part_i || !tickets) return BN_ERR_BAD_ARG;
   int nb = vocab >= 8192 ? ARGMAX_BLOCKS : 1;
-  argmax_kernel<<<dim3(n_rows, nb), 256, 0, stream>>>(logits, ld, vocab, out, part_v, part_i, tickets);
+  BN_LAUNCH(argmax_kernel, dim3(n_rows, nb), 256, 0, stream, logits, ld, vocab, out, part_v, part_i, tickets);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
@@ -159,6 +165,8 @@ extern "C" int bn_argmax(const float* logits, int ld, int n_rows, int vocab, int
 __global__ void sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
                                           unsigned long long* __restrict__ rng, const int* __restrict__ index,
                                           int* __restrict__ out) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   __shared__ float scratch[32];
   __shared__ float tsum[SAMPLE_THREADS];
   __shared__ float r_shared;
@@ -205,7 +213,7 @@ extern "C" int bn_sample_temperature(const float* logits, int ld, int n_rows, in
                                      unsigned long long* rng, const int* index, int* out, cudaStream_t stream) {
   if (n_rows <= 0) return BN_OK;
   if (vocab <= 0 || !(temperature > 0.f)) return BN_ERR_BAD_ARG;
-  sample_temperature_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, rng, index, out);
+  BN_LAUNCH(sample_temperature_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, temperature, rng, index, out);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
@@ -339,6 +347,8 @@ __device__ int nucleus_first_exceeding(const float* p, int n, unsigned cutoff_bi
 __global__ void sample_topp_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
                                    float topp, unsigned long long* __restrict__ rng, const int* __restrict__ index,
                                    float* __restrict__ probs, int* __restrict__ out) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  pdl_wait();               // the kernels before this one have completed and their writes are visible
   __shared__ float scratch[32];
   __shared__ double dscratch[32];
   __shared__ int iscratch[SAMPLE_THREADS];
@@ -381,7 +391,7 @@ extern "C" int bn_sample_topp(const float* logits, int ld, int n_rows, int vocab
                               cudaStream_t stream) {
   if (n_rows <= 0) return BN_OK;
   if (vocab <= 0 || !(temperature > 0.f) || !(topp > 0.f && topp < 1.f) || !probs) return BN_ERR_BAD_ARG;
-  sample_topp_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, topp, rng, index, probs,
+  BN_LAUNCH(sample_topp_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, temperature, topp, rng, index, probs,
                                                            out);
   BN_CHECK_LAUNCH();
   return BN_OK;
