@@ -24,7 +24,7 @@
 //              thread), release it, and run the partial-tile protocol and the epilogue, while the
 //              MMA thread already fills the other accumulator.
 // Tiles are 128-byte swizzled both by TMA and in the MMA's shared-memory descriptors.  No
-// register ever holds a weight, so the bytes in flight per SM are the ring's size (144-192 KB).
+// register ever holds a weight, so the bytes in flight per SM are the ring's size (about 100 KB).
 //
 // The kernel is launched with programmatic stream serialization: the loads of its first weight
 // tiles are issued before griddepcontrol.wait, i.e. while the kernel before it in the stream is
@@ -43,7 +43,10 @@
 
 #define TC_BM 128      // weight rows per tile (UMMA M)
 #define TC_BK 64       // k per stage: 128 bytes of bfloat16, one swizzle row
-#define TC_STAGES 8
+// Ring depth by accumulator width: at most ~110 KB of shared memory per block, so that a block of
+// the next kernel in the stream fits on the same SM and fetches its first weight tiles while this
+// kernel's blocks are finishing (programmatic dependent launch).
+#define TC_STAGES_FOR(MP) ((MP) == 16 ? 6 : ((MP) == 32 ? 5 : 4))
 #define TC_THREADS 192
 #define TC_WAIT_NS 2000000000ull  // two seconds
 
@@ -167,6 +170,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   constexpr int A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
   constexpr int B_BYTES = MP * TC_BK * 2;      // 2, 4 or 8 KB
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TC_STAGES = TC_STAGES_FOR(MP);
   constexpr unsigned TMEM_COLS = 2 * MP < 32 ? 32 : 2 * MP;  // two accumulators; a power of two >= 32
   // instruction descriptor: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both
   // K-major, N >> 3 at bit 17, M >> 4 at bit 24
@@ -411,6 +415,7 @@ static int sm_count() {
 
 template <int MP>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int blocks, cudaStream_t stream) {
+  constexpr int TC_STAGES = TC_STAGES_FOR(MP);
   size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {

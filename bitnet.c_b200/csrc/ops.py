@@ -264,6 +264,43 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_seqs: 
     return out
 
 
+def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch.Tensor, n_seqs: int, n_heads: int,
+                           n_kv_heads: int, head_dim: int, scale: float, window: int, rotary_dims: int,
+                           theta_scale: float, tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                           k_cache: torch.Tensor, v_cache: torch.Tensor, max_len: int) -> torch.Tensor:
+    """The decode step's attention in one launch: rotary encoding of the raw queries and of the new
+    key (``rotary_dims`` = 0: none), the new key and value written into the cache at ``tok_pos``,
+    attention split over the keys, and the combination of the splits.  ``qkv`` holds one raw
+    q|k|v row per sequence with the key heads at element ``k_off`` and the value heads at ``v_off``."""
+    _need(qkv, "qkv", torch.bfloat16, 2)
+    _need(out, "out", torch.bfloat16, 2)
+    for t, nm in ((tok_pos, "tok_pos"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_decode_fused: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+    if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads or rotary_dims % 2 or rotary_dims > head_dim:
+        raise KernelError(f"attention_decode_fused: head_dim={head_dim}, heads {n_heads}/{n_kv_heads}, "
+                          f"rotary_dims={rotary_dims} not supported")
+    if max(k_off, v_off) + n_kv_heads * head_dim > qkv.shape[1] or n_heads * head_dim > qkv.shape[1]:
+        raise KernelError("attention_decode_fused: offsets run past the row")
+    if out.shape[0] < n_seqs or out.shape[1] != n_heads * head_dim or tok_pos.shape[0] < n_seqs or qkv.shape[0] < n_seqs:
+        raise KernelError("attention_decode_fused: out, qkv or tok_pos does not fit")
+    n_splits = max(1, (max_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+    part_o = torch.empty((n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
+    part_ml = torch.empty((n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+    _scr, counters = _split_scratch(qkv.device)
+    _check(_fn("attention_decode", "bn_attention_decode_fused")(
+        _ptr(qkv), c_int(qkv.shape[1]), c_int(k_off), c_int(v_off), _ptr(out), c_int(out.shape[1]), c_int(n_seqs),
+        c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(rotary_dims),
+        c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
+        _ptr(v_cache), _ptr(part_o), _ptr(part_ml), c_int(n_splits), _ptr(counters), c_int(counters.numel()),
+        _stream()), "attention_decode_fused")
+    return out
+
+
 # ---- matrix products ----------------------------------------------------------------------
 SKINNY_MAX_ROWS = 16  # float32: warp-per-column kernel up to this many rows
 MMA_MAX_ROWS = 64  # bfloat16: tensor-core streaming kernel up to this many rows

@@ -52,6 +52,17 @@ class Attention(Mixer):
     def forward(self, h, ctx, kv, state):
         s = self.spec
         n = h.shape[0]
+        fusable = getattr(self.position, "rotary_params", None)
+        if kv.owner and ctx.decode and self.build.dtype == torch.bfloat16 and fusable is not None:
+            # one token per sequence: position encoding, cache write, attention over the splits of
+            # the keys and their combination are one kernel
+            qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)
+            out = torch.empty((n, s.q_dim), dtype=self.build.dtype, device=h.device)
+            rotary_dims, theta_scale = fusable()
+            ops.attention_decode_fused(qkv, s.q_dim, s.q_dim + s.kv_dim, out, n, s.n_heads, s.n_kv_heads, s.head_dim,
+                                       s.softmax_scale, s.window, rotary_dims, theta_scale, ctx.tok_pos, ctx.slots,
+                                       kv.page_table, kv.k, kv.v, ctx.max_len)
+            return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True)
         if kv.owner:
             qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)
             n_rot = s.n_heads + s.n_kv_heads

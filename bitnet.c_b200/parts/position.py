@@ -24,6 +24,10 @@ class Rotary(Position):
         # powf(theta, -2/dims) in float32, the factor between consecutive angles.
         self.theta_scale = float(np.power(np.float32(spec.theta), np.float32(-2.0) / np.float32(dims)))
 
+    def rotary_params(self):
+        """(rotary_dims, theta_scale): lets a mixer's decode kernel apply this encoding itself."""
+        return self.spec.dims, self.theta_scale
+
     def rotate(self, x, n_heads, head_dim, ctx):
         ops.rope_append(x, n_heads, head_dim, self.spec.dims, self.theta_scale, ctx.tok_pos)
 
@@ -36,6 +40,9 @@ class Rotary(Position):
 @register_position("none")
 class NoPosition(Position):
     graph_safe = True
+
+    def rotary_params(self):
+        return 0, 1.0
 
     def rotate(self, x, n_heads, head_dim, ctx):
         return None

@@ -419,3 +419,52 @@ def test_argmax_large_vocabulary(cuda_device):
     ref = [int(np.argmax(r)) for r in logits.cpu().numpy()]
     assert got == ref and got[0] == 77 and got[2] == 0
     assert ops.argmax(logits).cpu().tolist() == ref  # the tickets were left at zero
+
+
+@pytest.mark.parametrize("H,KV,hd,rd,lens,window", [
+    (4, 2, 16, 16, [1, 5, 64, 130], 0), (3, 1, 48, 48, [200, 129, 128], 0), (32, 8, 128, 128, [700, 3, 513], 0),
+    (2, 2, 256, 64, [257], 0), (40, 40, 64, 0, [100, 300], 0), (12, 1, 32, 32, [150, 40, 260], 17),
+])
+def test_attention_decode_fused(cuda_device, H, KV, hd, rd, lens, window):
+    """The one-launch decode attention against plain rotary + attention: the new key and value must land
+    in the cache (rotated / as they are) and the result must see them."""
+    g = torch.Generator().manual_seed(23)
+    theta = 10000.0
+    n_seq, n_pages, per_seq = len(lens), 80, 16
+    perm = torch.randperm(n_pages, generator=g)[: n_seq * per_seq].reshape(n_seq, per_seq).to(torch.int32)
+    k, v = _paged_cache(cuda_device, "bfloat16", n_pages, KV, hd, 24)
+    ks = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]  # already rotated, cached
+    vs = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]
+    raw = (torch.randn(n_seq, H + 2 * KV, hd, generator=g) * 0.7).to(torch.bfloat16)  # the new token's q|k|v
+    slots = list(range(n_seq))[::-1]
+    for s, L in enumerate(lens):
+        for p in range(L - 1):  # the last position is written by the kernel
+            page = perm[slots[s], p // 64].item()
+            k[page, :, p % 64] = ks[s][p].to(cuda_device)
+            v[page, :, p % 64] = vs[s][p].to(cuda_device)
+    k_before, v_before = k.clone(), v.clone()
+    out = torch.empty(n_seq, H * hd, dtype=torch.bfloat16, device=cuda_device)
+    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(rd))) if rd else 1.0
+    pos = [L - 1 for L in lens]
+    ops.attention_decode_fused(raw.reshape(n_seq, -1).contiguous().to(cuda_device), H * hd, (H + KV) * hd, out, n_seq,
+                               H, KV, hd, hd ** -0.5, window, rd, scale,
+                               torch.tensor(pos, dtype=torch.int32, device=cuda_device),
+                               torch.tensor(slots, dtype=torch.int32, device=cuda_device), perm.to(cuda_device), k, v,
+                               max(lens))
+    got = out.double().cpu().numpy().reshape(n_seq, H, hd)
+    touched = torch.zeros_like(k, dtype=torch.bool)
+    for s, L in enumerate(lens):
+        r = raw[s].double().numpy()
+        rot = plain_llama.apply_rope(r[None, : H + KV], [pos[s]], theta, dims=rd)[0] if rd else r[: H + KV]
+        rot = plain_llama.to_bf16(rot)
+        page, row = perm[slots[s], pos[s] // 64].item(), pos[s] % 64
+        assert np.abs(k[page, :, row].double().cpu().numpy() - rot[H:]).max() < 2e-2
+        assert np.array_equal(v[page, :, row].double().cpu().numpy(), r[H + KV:])
+        touched[page, :, row] = True
+        kfull = np.concatenate([ks[s][: L - 1].double().numpy(), rot[None, H:]])
+        vfull = np.concatenate([vs[s][: L - 1].double().numpy(), r[None, H + KV:]])
+        qfull = np.zeros((L, H, hd))
+        qfull[L - 1] = rot[:H]
+        ref = plain_llama.attention(qfull, kfull, vfull, hd ** -0.5, window)[L - 1]
+        assert np.abs(got[s] - ref).max() < 2e-2, f"sequence {s}"
+    assert torch.equal(k[~touched], k_before[~touched]) and torch.equal(v[~touched], v_before[~touched])
