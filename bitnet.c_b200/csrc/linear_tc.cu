@@ -66,6 +66,8 @@ struct TcArgs {
   float* scratch;  // [blocks][2][128][Mp] partial tiles of the first and last segment of a block
   int* counters;   // one ticket per tile, zero before and after
   int* status;     // 0, or the code of a wait that gave up
+  int l2_prefetch; // k-blocks of W, beyond the ring, that a block asks into L2 before the dependency wait
+  unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -103,6 +105,9 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* st
     }
   }
   return true;
+}
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1) {
   asm volatile(
@@ -213,6 +218,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
+  const bool tracing = a.trace != nullptr && blockIdx.x == 0;
+  if (tracing && tid == 0) a.trace[0] = global_timer();
   // the kernel that follows in the stream may start its own prologue now
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -220,18 +227,26 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (lane == 0) {
       // Weights do not depend on the kernel before this one: the first ring of W tiles is
       // requested before the dependency wait, the matching x tiles after it.
+      // Further W tiles of the stretch are only asked into L2: the requests are served while this
+      // block sits in the wait, so that the kernel before this one ends with HBM still busy.
       int tile, kb_lo, kb_hi, it = 0;
       {
         Segments seg(u0, u1, a.k_blocks);
-        while (it < TC_STAGES && seg.next(tile, kb_lo, kb_hi)) {
-          for (int kb = kb_lo; kb < kb_hi && it < TC_STAGES; ++kb, ++it) {
-            mbar_expect_tx(full0 + 8 * it, STAGE_BYTES);
-            tma_load_2d(smem_u32(base + it * STAGE_BYTES), &map_w, full0 + 8 * it, kb * TC_BK, tile * TC_BM);
+        const int ahead = TC_STAGES + a.l2_prefetch;
+        while (it < ahead && seg.next(tile, kb_lo, kb_hi)) {
+          for (int kb = kb_lo; kb < kb_hi && it < ahead; ++kb, ++it) {
+            if (it < TC_STAGES) {
+              mbar_expect_tx(full0 + 8 * it, STAGE_BYTES);
+              tma_load_2d(smem_u32(base + it * STAGE_BYTES), &map_w, full0 + 8 * it, kb * TC_BK, tile * TC_BM);
+            } else {
+              tma_prefetch_l2_2d(&map_w, kb * TC_BK, tile * TC_BM);
+            }
           }
-          if (it >= TC_STAGES) break;
         }
       }
+      if (tracing) a.trace[1] = global_timer();
       asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (tracing) a.trace[2] = global_timer();
       Segments seg(u0, u1, a.k_blocks);
       it = 0;
       bool failed = false;
@@ -248,6 +263,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
       }
       if (failed) s_failed = 1;
+      if (tracing) a.trace[3] = global_timer();  // all loads issued
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -274,6 +290,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         ++j;
       }
       if (failed) s_failed = 1;
+      if (tracing) a.trace[4] = global_timer();  // all MMAs issued
     }
   } else {
     // ---- epilogue warps: TMEM lane quadrant warp % 4, one weight row per thread
@@ -361,6 +378,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       ++j;
       asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps take the segments in lockstep
     }
+    if (tracing && warp == 2 && lane == 0) a.trace[5] = global_timer();  // epilogues done
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -375,6 +393,25 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
+  if (tracing && tid == 32) a.trace[6] = global_timer();
+}
+
+// Debugging aid: bn_linear_tc_trace(n) makes the next n launches record timestamps of block 0
+// (device buffer allocated here; not used on the product path).
+static unsigned long long* g_trace = nullptr;
+static int g_trace_n = 0, g_trace_cap = 0;
+extern "C" int bn_linear_tc_trace(int n) {
+  if (g_trace) cudaFree(g_trace);
+  g_trace = nullptr; g_trace_n = 0; g_trace_cap = 0;
+  if (n <= 0) return 0;
+  if (cudaMalloc(&g_trace, (size_t)n * 64) != cudaSuccess) return 1;
+  cudaMemset(g_trace, 0, (size_t)n * 64);
+  g_trace_cap = n;
+  return 0;
+}
+extern "C" int bn_linear_tc_trace_read(unsigned long long* host, int n) {
+  if (!g_trace || n > g_trace_cap) return 1;
+  return cudaMemcpy(host, g_trace, (size_t)n * 64, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
 
 static PFN_cuTensorMapEncodeTiled get_encode() {
@@ -464,6 +501,15 @@ extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dty
   TcArgs a;
   a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
   a.k_blocks = k_blocks; a.tiles = tiles; a.scratch = scratch; a.counters = counters; a.status = status;
+  static int l2_prefetch = -1;
+  if (l2_prefetch < 0) {
+    const char* e = getenv("BN_TC_L2_PREFETCH");  // tuning knob: k-blocks per block, 0 = off
+    l2_prefetch = e ? atoi(e) : 16;
+    if (l2_prefetch < 0) l2_prefetch = 0;
+  }
+  a.l2_prefetch = l2_prefetch;
+  a.trace = nullptr;
+  if (g_trace && g_trace_n < g_trace_cap) a.trace = g_trace + 8 * (g_trace_n++);
   if (mp == 16) return launch_tc<16>(mw, mx, a, blocks, stream);
   if (mp == 32) return launch_tc<32>(mw, mx, a, blocks, stream);
   return launch_tc<64>(mw, mx, a, blocks, stream);
