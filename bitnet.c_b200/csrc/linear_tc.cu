@@ -5,26 +5,25 @@
 // columns] += W_tile[128, 64] . x_tile[Mp, 64]^T, one tcgen05.mma of shape M=128, N=Mp, K=16 per 16
 // columns of k, issued by one thread.
 //
-// Work is cut stream-K fashion: the tiles x k-blocks space (tile = 128 weight rows, k-block = 64
-// columns) is one line of units, and each of the (at most one per SM) persistent blocks takes a
-// contiguous stretch of it, so every block streams the same number of bytes whatever N and K
-// are.  A stretch crosses tile borders: each (block, tile) piece is a *segment* with its own
-// accumulator.  A segment that covers a whole tile runs the epilogue directly.  A tile that is
-// shared between blocks is finished through scratch: every block writes its float32 partial tile
-// and draws a ticket of the tile's counter; the one that draws the last ticket adds the partials
-// in block order and runs the epilogue.  No block ever waits for another.
+// A tile is 128 weight rows.  Weights with few rows have fewer tiles than the GPU has SMs, so the
+// inner dimension of a tile is split over a thread-block cluster of C blocks (C x tiles is about
+// the number of SMs): block r of the cluster multiplies k-blocks [r KB/C, (r+1) KB/C).  Each block
+// leaves its float32 partial tile in its own shared memory; after a cluster barrier every block
+// adds up, in rank order, a slice of the tile's rows read from all C blocks through distributed
+// shared memory and runs the epilogue on that slice.  Nothing goes through global memory, all
+// blocks of a tile finish together, and the order of the additions is fixed.
 //
 // A block of 192 threads:
-//   warp 0     one thread issues the TMA loads of W and x tiles into a ring of TC_STAGES stages and
-//              arms each stage's "full" mbarrier with the bytes to expect;
-//   warp 1     allocates tensor memory (two accumulators); one thread waits for "full", issues four
-//              MMAs per stage, commits them to the stage's "empty" mbarrier and, at the end of a
-//              segment, to that accumulator's "full" mbarrier;
-//   warps 2-5  wait for an accumulator, read it from tensor memory (tcgen05.ld, one weight row per
-//              thread), release it, and run the partial-tile protocol and the epilogue, while the
-//              MMA thread already fills the other accumulator.
-// Tiles are 128-byte swizzled both by TMA and in the MMA's shared-memory descriptors.  No
-// register ever holds a weight, so the bytes in flight per SM are the ring's size (about 100 KB).
+//   warp 0     one thread issues the TMA loads of W and x tiles into a ring of stages and arms each
+//              stage's "full" mbarrier with the bytes to expect;
+//   warp 1     allocates tensor memory; one thread waits for "full", issues four MMAs per stage,
+//              commits them to the stage's "empty" mbarrier and at the end to "accumulator full";
+//   warps 2-5  wait for the accumulator, move it from tensor memory to shared memory
+//              (tcgen05.ld, one weight row per thread) and, after the cluster barrier, reduce and
+//              store with consecutive threads on consecutive output columns.
+// Tiles are 128-byte swizzled both by TMA and in the MMA's shared-memory descriptors.  No register
+// ever holds a weight, so the bytes in flight per SM are the ring's size (about 100 KB); a block
+// uses less than half of an SM's shared memory so that a block of the next kernel fits beside it.
 //
 // The kernel is launched with programmatic stream serialization: the loads of its first weight
 // tiles are issued before griddepcontrol.wait, i.e. while the kernel before it in the stream is
@@ -33,7 +32,8 @@
 // Epilogues: (0) store, (2) SwiGLU over weight rows that alternate 8 gate and 8 up rows.
 //
 // Every wait on an mbarrier is bounded in time; when a wait gives up the block records a code
-// in *status, lets its loads drain for a bounded time, frees its tensor memory and returns.
+// in *status, still takes part in the cluster barriers, lets its loads drain for a bounded time,
+// frees its tensor memory and returns.
 //
 // Reference for the operation: y = W x with float32 accumulation (src/quant/bf16_scalar.c:4-21);
 // the reference's CUDA backend reaches tensor cores only through cuBLAS (src/gpu_cuda.cu:11850-11879).
@@ -53,7 +53,6 @@
 #define TC_ERR_FULL_WAIT 1
 #define TC_ERR_EMPTY_WAIT 2
 #define TC_ERR_ACC_WAIT 3
-#define TC_ERR_ACC_FREE_WAIT 4
 
 struct TcArgs {
   void* out;
@@ -62,11 +61,7 @@ struct TcArgs {
   int ldo;
   int mode;        // 0 store, 2 swiglu
   int k_blocks;    // ceil(K / 64)
-  int tiles;       // ceil(N / 128)
-  float* scratch;  // [blocks][2][128][Mp] partial tiles of the first and last segment of a block
-  int* counters;   // one ticket per tile, zero before and after
   int* status;     // 0, or the code of a wait that gave up
-  int l2_prefetch; // k-blocks of W, beyond the ring, that a block asks into L2 before the dependency wait
   unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
 };
 
@@ -142,33 +137,51 @@ __device__ __forceinline__ void tmem_ld16(unsigned addr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// The stretch of units of block c: [unit_start(c), unit_start(c + 1)).
-__device__ __forceinline__ long long unit_start(long long c, long long total, int blocks) { return c * total / blocks; }
-// The block whose stretch holds unit u.
-__device__ __forceinline__ int block_of(long long u, long long total, int blocks) {
-  int c = (int)(u * blocks / total);
-  while (c + 1 < blocks && unit_start(c + 1, total, blocks) <= u) ++c;
-  while (c > 0 && unit_start(c, total, blocks) > u) --c;
-  return c;
+// First row (of 128) of the slice that cluster rank r reduces and stores: multiples of 16 so that
+// a gate row and its up row (8 apart) stay in one slice.
+__device__ __forceinline__ int slice_start(int r, int c) { return 16 * ((8 * r) / c); }
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Four consecutive floats of block `rank`'s shared memory, at the address that `local_addr` has here.
+__device__ __forceinline__ float4 ld_dsmem4(unsigned local_addr, unsigned rank) {
+  unsigned remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+// The sum over the cluster, in rank order, of such a group of four: all loads are issued before
+// the first is used.
+__device__ __forceinline__ float4 sum_dsmem4(unsigned local_addr, int C) {
+  float4 p[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) p[q] = q < C ? ld_dsmem4(local_addr, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 s = p[0];
+#pragma unroll
+  for (int q = 1; q < 8; ++q) { s.x += p[q].x; s.y += p[q].y; s.z += p[q].z; s.w += p[q].w; }
+  return s;
+}
+__device__ __forceinline__ void store4(void* out, int out_dtype, size_t idx, float4 v, int valid) {
+  // idx..idx+3 are consecutive elements; `valid` of them exist
+  if (valid == 4 && out_dtype == BN_BF16 && (idx & 3) == 0) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&a);
+    raw.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>((__nv_bfloat16*)out + idx) = raw;
+  } else if (valid == 4 && out_dtype == BN_F32 && (idx & 3) == 0) {
+    *reinterpret_cast<float4*>((float*)out + idx) = v;
+  } else {
+    float e[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < valid; ++i) store_from_f32(out, out_dtype, idx + i, e[i]);
+  }
 }
 
-// Walks the segments of a block's stretch: (tile, first k-block, one past the last k-block).
-struct Segments {
-  long long u, u_end;
-  int kb;
-  __device__ Segments(long long u0, long long u1, int k_blocks) : u(u0), u_end(u1), kb(k_blocks) {}
-  __device__ bool next(int& tile, int& kb_lo, int& kb_hi) {
-    if (u >= u_end) return false;
-    tile = (int)(u / kb);
-    kb_lo = (int)(u - (long long)tile * kb);
-    long long left = u_end - u;
-    kb_hi = (int)min((long long)kb, kb_lo + left);
-    u += kb_hi - kb_lo;
-    return true;
-  }
-};
-
-template <int MP>  // batch columns of an accumulator: 16, 32 or 64
+template <int MP>  // batch columns of the accumulator: 16, 32 or 64
 __global__ void __launch_bounds__(TC_THREADS)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -176,37 +189,37 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   constexpr int B_BYTES = MP * TC_BK * 2;      // 2, 4 or 8 KB
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
-  constexpr unsigned TMEM_COLS = 2 * MP < 32 ? 32 : 2 * MP;  // two accumulators; a power of two >= 32
+  constexpr int PSTRIDE = TC_BM + 4;           // floats per batch column of the partial tile in shared memory
+  static_assert(MP * PSTRIDE * 4 <= TC_STAGES * STAGE_BYTES, "the partial tile reuses the ring");
+  constexpr unsigned TMEM_COLS = MP < 32 ? 32 : MP;
   // instruction descriptor: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both
   // K-major, N >> 3 at bit 17, M >> 4 at bit 24
   constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(MP >> 3) << 17) | ((TC_BM >> 4) << 24);
 
+  // the same offset in every block of the cluster (dynamic shared memory starts at the same address)
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
-  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 4);
-  __shared__ int s_last;
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
+  float* partial = (float*)base;  // [MP][PSTRIDE]: partial[m][row], valid once all MMAs have read the ring
   __shared__ int s_failed;
   __shared__ int s_acc_ok;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int blocks = gridDim.x;
-  const long long total = (long long)a.tiles * a.k_blocks;
-  const long long u0 = unit_start(blockIdx.x, total, blocks), u1 = unit_start(blockIdx.x + 1, total, blocks);
-  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES);
-  const unsigned acc_full0 = smem_u32(bars + 2 * TC_STAGES), acc_free0 = smem_u32(bars + 2 * TC_STAGES + 2);
+  const int C = gridDim.x, rank = blockIdx.x, tile = blockIdx.y;  // the cluster spans gridDim.x
+  const int kb0 = (int)((long long)rank * a.k_blocks / C), kb1 = (int)((long long)(rank + 1) * a.k_blocks / C);
+  const int n_kb = kb1 - kb0;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES), acc_bar = smem_u32(bars + 2 * TC_STAGES);
 
   if (tid == 0) {
     s_failed = 0;
+    s_acc_ok = 0;
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full0 + 8 * b, 1);
-      mbar_init(acc_free0 + 8 * b, 128);  // every epilogue thread arrives
-    }
+    mbar_init(acc_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -218,7 +231,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
-  const bool tracing = a.trace != nullptr && blockIdx.x == 0;
+  const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
   if (tracing && tid == 0) a.trace[0] = global_timer();
   // the kernel that follows in the stream may start its own prologue now
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -227,160 +240,117 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (lane == 0) {
       // Weights do not depend on the kernel before this one: the first ring of W tiles is
       // requested before the dependency wait, the matching x tiles after it.
-      // Further W tiles of the stretch are only asked into L2: the requests are served while this
-      // block sits in the wait, so that the kernel before this one ends with HBM still busy.
-      int tile, kb_lo, kb_hi, it = 0;
-      {
-        Segments seg(u0, u1, a.k_blocks);
-        const int ahead = TC_STAGES + a.l2_prefetch;
-        while (it < ahead && seg.next(tile, kb_lo, kb_hi)) {
-          for (int kb = kb_lo; kb < kb_hi && it < ahead; ++kb, ++it) {
-            if (it < TC_STAGES) {
-              mbar_expect_tx(full0 + 8 * it, STAGE_BYTES);
-              tma_load_2d(smem_u32(base + it * STAGE_BYTES), &map_w, full0 + 8 * it, kb * TC_BK, tile * TC_BM);
-            } else {
-              tma_prefetch_l2_2d(&map_w, kb * TC_BK, tile * TC_BM);
-            }
-          }
-        }
+      const int pre = min(n_kb, TC_STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+        tma_load_2d(smem_u32(base + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, tile * TC_BM);
       }
       if (tracing) a.trace[1] = global_timer();
       asm volatile("griddepcontrol.wait;" ::: "memory");
       if (tracing) a.trace[2] = global_timer();
-      Segments seg(u0, u1, a.k_blocks);
-      it = 0;
       bool failed = false;
-      while (!failed && seg.next(tile, kb_lo, kb_hi)) {
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-          int s = it % TC_STAGES, round = it / TC_STAGES;
-          unsigned dst = smem_u32(base + s * STAGE_BYTES);
-          if (round > 0) {
-            if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, a.status, TC_ERR_EMPTY_WAIT)) { failed = true; break; }
-            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_2d(dst, &map_w, full0 + 8 * s, kb * TC_BK, tile * TC_BM);
-          }
-          tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, kb * TC_BK, 0);
+      for (int i = 0; i < n_kb; ++i) {
+        int s = i % TC_STAGES, round = i / TC_STAGES;
+        unsigned dst = smem_u32(base + s * STAGE_BYTES);
+        if (round > 0) {
+          if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, a.status, TC_ERR_EMPTY_WAIT)) { failed = true; break; }
+          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          tma_load_2d(dst, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, tile * TC_BM);
         }
+        tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, 0);
       }
       if (failed) s_failed = 1;
       if (tracing) a.trace[3] = global_timer();  // all loads issued
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      Segments seg(u0, u1, a.k_blocks);
-      int tile, kb_lo, kb_hi, it = 0, j = 0;
       bool failed = false;
-      while (!failed && seg.next(tile, kb_lo, kb_hi)) {
-        const int buf = j & 1;
-        // the epilogue must have emptied this accumulator (first use of each: passes at once)
-        if (!mbar_wait(acc_free0 + 8 * buf, ((j >> 1) & 1) ^ 1, a.status, TC_ERR_ACC_FREE_WAIT)) { failed = true; break; }
+      for (int i = 0; i < n_kb; ++i) {
+        int s = i % TC_STAGES, round = i / TC_STAGES;
+        if (!mbar_wait(full0 + 8 * s, round & 1, a.status, TC_ERR_FULL_WAIT)) { failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned tmem_d = tmem_base + buf * MP;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-          int s = it % TC_STAGES, round = it / TC_STAGES;
-          if (!mbar_wait(full0 + 8 * s, round & 1, a.status, TC_ERR_FULL_WAIT)) { failed = true; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          unsigned sa = smem_u32(base + s * STAGE_BYTES), sb = sa + A_BYTES;
+        unsigned sa = smem_u32(base + s * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < TC_BK / 16; ++kk)
-            umma_bf16(tmem_d, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC, (kb > kb_lo || kk) ? 1u : 0u);
-          umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
-        }
-        if (!failed) umma_commit(acc_full0 + 8 * buf);  // arrives when the segment's MMAs are done
-        ++j;
+        for (int kk = 0; kk < TC_BK / 16; ++kk)
+          umma_bf16(tmem_base, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC, (i | kk) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
       }
+      if (!failed) umma_commit(acc_bar);  // arrives when every MMA above is done
       if (failed) s_failed = 1;
       if (tracing) a.trace[4] = global_timer();  // all MMAs issued
     }
   } else {
-    // ---- epilogue warps: TMEM lane quadrant warp % 4, one weight row per thread
+    // ---- epilogue warps, part one: accumulator -> shared memory (TMEM lane quadrant warp % 4)
     const int quad = warp & 3;
-    const int row_in_tile = quad * 32 + lane;
-    const size_t tile_floats = (size_t)TC_BM * MP;
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // before any global write of this kernel
-    Segments seg(u0, u1, a.k_blocks);
-    int tile, kb_lo, kb_hi, j = 0;
-    float v[MP];
-    while (seg.next(tile, kb_lo, kb_hi)) {
-      const int buf = j & 1;
-      // one thread waits (bounded) for the accumulator; the four warps then agree on the outcome
-      if (warp == 2 && lane == 0) {
-        s_acc_ok = mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
-        if (!s_acc_ok) s_failed = 1;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!s_acc_ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < MP; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + buf * MP + c, v + c);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(acc_free0 + 8 * buf);  // the MMA thread may overwrite this accumulator
-
-      const int n = tile * TC_BM + row_in_tile;
-      bool run_epilogue = true;
-      if (kb_lo != 0 || kb_hi != a.k_blocks) {
-        // a tile shared with other blocks: slot 0 holds a block's first segment, slot 1 its last
-        const long long t0 = (long long)tile * a.k_blocks;
-        const int c_first = block_of(t0, total, blocks), c_last = block_of(t0 + a.k_blocks - 1, total, blocks);
-        const int my_slot = (j == 0) ? 0 : 1;
-        float* mine = a.scratch + ((size_t)blockIdx.x * 2 + my_slot) * tile_floats + (size_t)row_in_tile * MP;
-#pragma unroll
-        for (int c = 0; c < MP; c += 4) *reinterpret_cast<float4*>(mine + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          int ticket = atomicAdd(a.counters + tile, 1);
-          s_last = (ticket == c_last - c_first);
-          if (s_last) a.counters[tile] = 0;  // ready for the next launch
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        run_epilogue = s_last != 0;
-        if (run_epilogue) {
-          __threadfence();
-#pragma unroll
-          for (int c = 0; c < MP; ++c) v[c] = 0.f;
-          for (int cb = c_first; cb <= c_last; ++cb) {
-            // block cb's piece of this tile is its first segment iff its stretch starts inside the tile
-            long long cs = unit_start(cb, total, blocks);
-            int slot = (cs >= t0) ? 0 : 1;
-            // a block whose stretch starts exactly at the tile start also uses slot 0 (j == 0)
-            const float* part = a.scratch + ((size_t)cb * 2 + slot) * tile_floats + (size_t)row_in_tile * MP;
-#pragma unroll
-            for (int c = 0; c < MP; c += 4) {
-              float4 p = __ldcg(reinterpret_cast<const float4*>(part + c));
-              v[c] += p.x; v[c + 1] += p.y; v[c + 2] += p.z; v[c + 3] += p.w;
-            }
-          }
-        }
-      }
-      if (run_epilogue) {
-        if (a.mode == 0) {
-          if (n < a.N) {
-#pragma unroll
-            for (int m = 0; m < MP; ++m)
-              if (m < a.M) store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + n, v[m]);
-          }
-        } else {
-          // rows 16j..16j+7 are gate rows 8j.., rows 16j+8..16j+15 the up rows of the same indices:
-          // lane L (L % 16 < 8) holds a gate value and lane L + 8 the matching up value
-          const int i = (n >> 4) * 8 + (n & 7);
-#pragma unroll
-          for (int m = 0; m < MP; ++m) {
-            float other = __shfl_xor_sync(0xffffffffu, v[m], 8);
-            if ((lane & 8) == 0 && m < a.M && n < a.N) {
-              float g = v[m];
-              store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + i, g / (1.0f + expf(-g)) * other);
-            }
-          }
-        }
-      }
-      ++j;
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps take the segments in lockstep
+    const int row = quad * 32 + lane;
+    if (warp == 2 && lane == 0) {
+      int ok = mbar_wait(acc_bar, 0, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
+      if (!ok) s_failed = 1;
+      s_acc_ok = ok;
     }
-    if (tracing && warp == 2 && lane == 0) a.trace[5] = global_timer();  // epilogues done
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float v[MP];
+    if (s_acc_ok) {
+#pragma unroll
+      for (int c = 0; c < MP; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + c, v + c);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int c = 0; c < MP; ++c) v[c] = 0.f;
+    }
+    // every MMA has completed, so nothing reads the ring any more: it now holds the partial tile,
+    // batch column by batch column (consecutive threads write consecutive addresses)
+#pragma unroll
+    for (int c = 0; c < MP; ++c) partial[c * PSTRIDE + row] = v[c];
   }
 
+  // ---- all blocks of the cluster have their partial tiles in shared memory
+  __syncwarp();
+  cluster_sync_all();
+
+  if (warp >= 2) {
+    // part two: this block's slice of the rows, summed over the cluster in rank order, then stored.
+    // Consecutive threads take consecutive rows (output columns), so stores coalesce.
+    pdl_wait();  // before the first global write of this thread
+    const int t = tid - 64;
+    const int r0 = slice_start(rank, C), rows = slice_start(rank + 1, C) - r0;
+    const unsigned pbase = smem_u32(partial);
+    if (a.mode == 0) {
+      // item = (batch row m, group of four weight rows): four consecutive output columns
+      const int groups = rows / 4;
+      for (int e = t; e < groups * a.M; e += 128) {
+        int m = e / groups, rl = (e - m * groups) * 4;
+        int n = tile * TC_BM + r0 + rl;
+        if (n >= a.N) continue;
+        float4 sum = sum_dsmem4(pbase + (unsigned)((m * PSTRIDE + r0 + rl) * 4), C);
+        store4(a.out, a.out_dtype, (size_t)m * a.ldo + n, sum, min(4, a.N - n));
+      }
+    } else {
+      // rows 16j..16j+7 of a tile are gate rows, rows 16j+8..16j+15 the up rows of the same indices;
+      // item = (batch row m, four gate rows and their up rows): four consecutive activations
+      const int groups = rows / 8;
+      for (int e = t; e < groups * a.M; e += 128) {
+        int m = e / groups, gq = e - m * groups;
+        int rg = r0 + (gq >> 1) * 16 + (gq & 1) * 4;  // first of the four gate rows within the tile
+        int n = tile * TC_BM + rg;
+        if (n >= a.N) continue;
+        unsigned ag = pbase + (unsigned)((m * PSTRIDE + rg) * 4);
+        float4 g = sum_dsmem4(ag, C), u = sum_dsmem4(ag + 8 * 4, C);
+        float4 act;
+        act.x = g.x / (1.0f + expf(-g.x)) * u.x;
+        act.y = g.y / (1.0f + expf(-g.y)) * u.y;
+        act.z = g.z / (1.0f + expf(-g.z)) * u.z;
+        act.w = g.w / (1.0f + expf(-g.w)) * u.w;
+        int i = (n >> 4) * 8 + (n & 7);
+        store4(a.out, a.out_dtype, (size_t)m * a.ldo + i, act, 4);  // N is a multiple of 16: all four exist
+      }
+    }
+    if (tracing && warp == 2 && lane == 0) a.trace[5] = global_timer();  // epilogue done
+  }
+
+  __syncwarp();
+  cluster_sync_all();  // no block leaves while another still reads its partial tile
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (s_failed) {
@@ -451,9 +421,10 @@ static int sm_count() {
 }
 
 template <int MP>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int blocks, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int cluster, int tiles,
+                     cudaStream_t stream) {
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
-  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 4) * 8 + 16 + 1024;
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -461,15 +432,19 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs&
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(blocks);
+  cfg.gridDim = dim3(cluster, tiles);
   cfg.blockDim = dim3(TC_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = bn_pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_tc_kernel<MP>, mw, mx, a);
   if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
   return BN_OK;
@@ -477,40 +452,36 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs&
 
 // x [M, K], w [N, K] bfloat16, both 16-byte aligned with K a multiple of 8.  mode 0: out [M, ldo]
 // of out_dtype; mode 2: N = 2 I weight rows in blocks of 8 gate / 8 up rows, out holds
-// silu(gate) * up in I columns.  max_blocks caps the number of persistent blocks (0: one per SM).
-// scratch: blocks * 2 * 128 * Mp floats (Mp = 16, 32 or 64 >= M); counters: ceil(N/128) zeroed
-// ints; both may be shared by launches that do not overlap.  status: one int on the device, left 0
-// unless a wait inside the kernel gave up.
+// silu(gate) * up in I columns.  cluster: blocks that share a tile's inner dimension, 1 to 8
+// (0: chosen so that cluster x tiles is about the number of SMs).  status: one int on the device,
+// left 0 unless a wait inside the kernel gave up.
 extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
-                            int mode, int max_blocks, float* scratch, long long scratch_floats, int* counters,
-                            int n_counters, int* status, cudaStream_t stream) {
+                            int mode, int cluster, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
-  if (M > 64 || K <= 0 || K % 8 || max_blocks < 0 || (mode != 0 && mode != 2) || !status) return BN_ERR_BAD_ARG;
+  if (M > 64 || K <= 0 || K % 8 || cluster < 0 || cluster > 8 || (mode != 0 && mode != 2) || !status)
+    return BN_ERR_BAD_ARG;
   if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return BN_ERR_BAD_ARG;
   int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   int tiles = (N + TC_BM - 1) / TC_BM;
   int k_blocks = (K + TC_BK - 1) / TC_BK;
-  long long total = (long long)tiles * k_blocks;
-  int blocks = max_blocks > 0 ? max_blocks : sm_count();
-  if (blocks > total) blocks = (int)total;
-  if (!scratch || !counters || n_counters < tiles || scratch_floats < (long long)blocks * 2 * TC_BM * mp)
-    return BN_ERR_BAD_ARG;
+  if (tiles > 65535) return BN_ERR_BAD_ARG;
+  if (cluster == 0) {
+    cluster = sm_count() / tiles;
+    int by_k = k_blocks / 4;  // at least four k-blocks per block
+    if (cluster > by_k) cluster = by_k;
+    if (cluster > 8) cluster = 8;
+    if (cluster < 1) cluster = 1;
+  }
+  if (cluster > k_blocks) cluster = k_blocks;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, TC_BM) || !make_map(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
   TcArgs a;
   a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
-  a.k_blocks = k_blocks; a.tiles = tiles; a.scratch = scratch; a.counters = counters; a.status = status;
-  static int l2_prefetch = -1;
-  if (l2_prefetch < 0) {
-    const char* e = getenv("BN_TC_L2_PREFETCH");  // tuning knob: k-blocks per block, 0 = off
-    l2_prefetch = e ? atoi(e) : 16;
-    if (l2_prefetch < 0) l2_prefetch = 0;
-  }
-  a.l2_prefetch = l2_prefetch;
+  a.k_blocks = k_blocks; a.status = status;
   a.trace = nullptr;
   if (g_trace && g_trace_n < g_trace_cap) a.trace = g_trace + 8 * (g_trace_n++);
-  if (mp == 16) return launch_tc<16>(mw, mx, a, blocks, stream);
-  if (mp == 32) return launch_tc<32>(mw, mx, a, blocks, stream);
-  return launch_tc<64>(mw, mx, a, blocks, stream);
+  if (mp == 16) return launch_tc<16>(mw, mx, a, cluster, tiles, stream);
+  if (mp == 32) return launch_tc<32>(mw, mx, a, cluster, tiles, stream);
+  return launch_tc<64>(mw, mx, a, cluster, tiles, stream);
 }

@@ -360,25 +360,22 @@ def check_tc_status(device) -> None:
 
 
 def linear_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-              max_blocks: int = 0) -> torch.Tensor:
+              cluster: int = 0) -> torch.Tensor:
     """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands.
-    ``max_blocks`` caps the persistent blocks that share the work (0: one per SM)."""
+    ``cluster`` blocks (1 to 8) share the inner dimension of each 128-row tile of w and add their
+    parts up through distributed shared memory (0: chosen from the number of tiles)."""
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or M > MMA_MAX_ROWS or K % 8 or (swiglu and N % 16):
-        raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)} not supported")
-    if (N + 127) // 128 > _N_COUNTERS:
-        raise KernelError(f"linear_tc: {N} output columns exceed the {_N_COUNTERS * 128} the ticket counters cover")
+    if w.shape[1] != K or M > MMA_MAX_ROWS or K % 8 or (swiglu and N % 16) or not 0 <= cluster <= 8:
+        raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, cluster {cluster} not supported")
     out_dtype = out_dtype or x.dtype
     cols = N // 2 if swiglu else N
     out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
-    scratch, counters = _split_scratch(x.device)
     _check(_fn("linear_tc", "bn_linear_tc")(
         _ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(cols),
-        c_int(2 if swiglu else 0), c_int(max_blocks), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
-        _ptr(counters), c_int(counters.numel()), _ptr(tc_status(x.device)), _stream()), "linear_tc")
+        c_int(2 if swiglu else 0), c_int(cluster), _ptr(tc_status(x.device)), _stream()), "linear_tc")
     return out
 
 
