@@ -40,6 +40,7 @@ SOURCES: Dict[str, str] = {
     "linear_mma": "linear_mma.cu",
     "linear_tc": "linear_tc.cu",
     "sampling": "sampling.cu",
+    "argmax_noalloc": "argmax_noalloc.cu",
 }
 
 NVCC_FLAGS = [
@@ -93,10 +94,11 @@ def _digest(family: str) -> str:
     for fn in (SOURCES[family], "common.cuh"):
         with open(os.path.join(_HERE, fn), "rb") as f:
             h.update(f.read())
-    extra = os.path.join(_HERE, SOURCES[family].replace(".cu", ".cuh"))
-    if os.path.isfile(extra):
-        with open(extra, "rb") as f:
-            h.update(f.read())
+    for ext in (".cuh", ".h"):
+        extra = os.path.join(_HERE, SOURCES[family].replace(".cu", ext))
+        if os.path.isfile(extra):
+            with open(extra, "rb") as f:
+                h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()[:12]
 
