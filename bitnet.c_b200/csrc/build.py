@@ -35,6 +35,7 @@ SOURCES: Dict[str, str] = {
     "act": "act.cu",
     "attention": "attention.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_decode_tc": "attention_decode_tc.cu",
     "attention_prefill": "attention_prefill.cu",
     "linear": "linear.cu",
     "linear_mma": "linear_mma.cu",

@@ -268,9 +268,10 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
                            n_kv_heads: int, head_dim: int, scale: float, window: int, rotary_dims: int,
                            theta_scale: float, tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                            k_cache: torch.Tensor, v_cache: torch.Tensor, max_len: int) -> torch.Tensor:
-    """The decode step's attention in one launch: rotary encoding of the raw queries and of the new
-    key (``rotary_dims`` = 0: none), the new key and value written into the cache at ``tok_pos``,
-    attention split over the keys, and the combination of the splits.  ``qkv`` holds one raw
+    """The decode step's attention in one launch on tensor cores (attention_decode_tc.cu): rotary
+    encoding of the raw queries and of the new key (``rotary_dims`` = 0: none), the new key and value
+    written into the cache at ``tok_pos``, attention split over the keys, and the combination of
+    the splits.  ``qkv`` holds one raw
     q|k|v row per sequence with the key heads at element ``k_off`` and the value heads at ``v_off``."""
     _need(qkv, "qkv", torch.bfloat16, 2)
     _need(out, "out", torch.bfloat16, 2)
@@ -292,7 +293,7 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
     part_o = torch.empty((n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
     _scr, counters = _split_scratch(qkv.device)
-    _check(_fn("attention_decode", "bn_attention_decode_fused")(
+    _check(_fn("attention_decode_tc", "bn_attention_decode_tc")(
         _ptr(qkv), c_int(qkv.shape[1]), c_int(k_off), c_int(v_off), _ptr(out), c_int(out.shape[1]), c_int(n_seqs),
         c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(rotary_dims),
         c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
