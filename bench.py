@@ -215,6 +215,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64 and the prefill (quick runs)")
+    ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -234,23 +235,24 @@ def main():
     pk = peaks()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
 
-    main_run = run_decode(bn, model, cfg, 8, args.steps, warmup, clock=ClockSampler())
+    B = args.batch
+    main_run = run_decode(bn, model, cfg, B, args.steps, warmup, clock=ClockSampler())
     ms_per_step = main_run["dev_ms"] / args.steps
-    value = 8 * args.steps / (main_run["dev_ms"] / 1e3)
-    e2e_run = run_decode(bn, model, cfg, 8, args.steps, warmup)
-    e2e_value = 8 * args.steps / (e2e_run["wall_ms"] / 1e3)
-    read_bytes = decode_read_bytes(model, cfg, 8, main_run["context"])
+    value = B * args.steps / (main_run["dev_ms"] / 1e3)
+    e2e_run = run_decode(bn, model, cfg, B, args.steps, warmup)
+    e2e_value = B * args.steps / (e2e_run["wall_ms"] / 1e3)
+    read_bytes = decode_read_bytes(model, cfg, B, main_run["context"])
     achieved = read_bytes / (ms_per_step / 1e3) / 1e9
 
     out = {
-        "metric": "decode tokens/s at batch 8 (Llama-3.1-8B sizes, bf16)", "value": round(value, 2), "unit": "tokens/s",
+        "metric": f"decode tokens/s at batch {B} (Llama-3.1-8B sizes, bf16)", "value": round(value, 2), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {"model": "llama-3.1-8b-sizes-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "global_batch": 8, "seq_len": cfg["max_position_embeddings"], "prompt_len": PROMPT_LEN,
+                   "global_batch": B, "seq_len": cfg["max_position_embeddings"], "prompt_len": PROMPT_LEN,
                    "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied": False,
                    "parallelism": "single-gpu", "l2": "inputs larger than L2 (15 GB of weights per step)",
                    "peaks": pk["source"]},

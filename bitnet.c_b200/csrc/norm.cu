@@ -96,29 +96,54 @@ add_rmsnorm_cluster_kernel(float* __restrict__ x, const void* __restrict__ delta
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta, int delta_dtype,
                                    int n_parts, size_t part_stride, const void* __restrict__ w, int w_dtype, void* __restrict__ out,
                                    int out_dtype, const int* __restrict__ rows, int width, float eps,
-                                   int write_x) {
+                                   int write_x, int vec4) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
-  extern __shared__ float v[];  // width floats, then 32 for the reduction
+  extern __shared__ __align__(16) float v[];  // width floats, then 32 for the reduction
   float* scratch = v + width;
   int r = blockIdx.x;
   size_t row = rows ? (size_t)rows[r] : (size_t)r;
   float* xr = x + row * width;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float a = xr[i];
-    if (delta) {
-      for (int p = 0; p < n_parts; ++p) a += load_as_f32(delta, delta_dtype, p * part_stride + row * width + i);
+  if (vec4) {
+    // groups of four columns, whole 8- or 16-byte pieces (the launcher checked the alignment)
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(xr + i);
+      if (delta) {
+        for (int p = 0; p < n_parts; ++p) {
+          float4 d = load4_as_f32(delta, delta_dtype, p * part_stride + row * width + i);
+          a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        }
+      }
+      *reinterpret_cast<float4*>(v + i) = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
     }
-    v[i] = a;
-    ss += a * a;
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float a = xr[i];
+      if (delta) {
+        for (int p = 0; p < n_parts; ++p) a += load_as_f32(delta, delta_dtype, p * part_stride + row * width + i);
+      }
+      v[i] = a;
+      ss += a * a;
+    }
   }
   ss = block_sum(ss, scratch);
   float scale = 1.0f / sqrtf(ss / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float a = v[i];
-    if (write_x) xr[i] = a;
-    store_from_f32(out, out_dtype, (size_t)r * width + i, a * scale * load_as_f32(w, w_dtype, i));
+  if (vec4) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(v + i);
+      if (write_x) *reinterpret_cast<float4*>(xr + i) = a;
+      float4 g = load4_as_f32(w, w_dtype, i);
+      store4_from_f32(out, out_dtype, (size_t)r * width + i,
+                      make_float4(a.x * scale * g.x, a.y * scale * g.y, a.z * scale * g.z, a.w * scale * g.w));
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float a = v[i];
+      if (write_x) xr[i] = a;
+      store_from_f32(out, out_dtype, (size_t)r * width + i, a * scale * load_as_f32(w, w_dtype, i));
+    }
   }
 }
 
@@ -153,7 +178,7 @@ extern "C" int bn_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
   int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   BN_LAUNCH(add_rmsnorm_kernel, n_rows, threads, smem, stream, x, delta, delta_dtype, n_parts, (size_t)part_stride, w,
                                                        w_dtype, out, out_dtype,
-                                                       rows, width, eps, write_x);
+                                                       rows, width, eps, write_x, aligned ? 1 : 0);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }

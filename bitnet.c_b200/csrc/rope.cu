@@ -10,7 +10,8 @@
 
 #define ROPE_THREADS 256
 
-// Work items of one token, spread over the blocks of gridDim.y:
+// One block per token.  The cosines and sines of the token's position are computed once into
+// shared memory; then the block walks the token's work items:
 //   [0, n_rot_heads * half)           one rotation pair (head, i); a pair of a key head also goes to the cache
 //   [.., + n_kv_heads * head_dim)     one value element -> cache, and the key element at the same place if
 //                                     no rotation touched it (dimensions past rotary_dims, or no rotation at all)
@@ -22,40 +23,44 @@ __global__ void rope_append_kernel(T* __restrict__ x, int row_stride, int n_rot_
                                    int pt_stride, T* __restrict__ k_cache, T* __restrict__ v_cache) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
+  __shared__ float cs[128], sn[128];  // rotary_dims <= head_dim <= 256
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   T* row = x + (size_t)t * row_stride;
   const int half = rotary_dims >> 1;
-  const int n_pairs = n_rot_heads * half;
-  const int n_copy = k_cache ? n_kv_heads * head_dim : 0;
-  const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
-  if (item >= n_pairs + n_copy) return;
-  const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
-  if (item < n_pairs) {
-    int h = item / half, i = item - h * half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float angle = (float)pos;
     for (int k = 0; k < i; ++k) angle *= theta_scale;
-    float s, c;
-    sincosf(angle, &s, &c);
-    T* hd = row + (size_t)h * head_dim;
-    float a = to_f32<T>(hd[i]), b = to_f32<T>(hd[i + half]);
-    T lo = from_f32<T>(a * c - b * s), hi = from_f32<T>(a * s + b * c);
-    hd[i] = lo;
-    hd[i + half] = hi;
-    int e = h * head_dim - k_off;  // element offset of this head among the key heads
-    if (k_cache && e >= 0 && e < n_kv_heads * head_dim) {
-      size_t off = cache_row_offset(pt, pos, n_kv_heads, e / head_dim, head_dim);
-      k_cache[off + i] = lo;
-      k_cache[off + i + half] = hi;
-    }
-    return;
+    sincosf(angle, &sn[i], &cs[i]);
   }
-  int e = item - n_pairs;
-  int kvh = e / head_dim, d = e - kvh * head_dim;
-  size_t off = cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d;
-  v_cache[off] = row[v_off + e];
-  bool rotated = d < rotary_dims && (k_off + kvh * head_dim) < n_rot_heads * head_dim;
-  if (!rotated) k_cache[off] = row[k_off + e];
+  __syncthreads();
+  const int n_pairs = n_rot_heads * half;
+  const int n_copy = k_cache ? n_kv_heads * head_dim : 0;
+  const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
+  for (int item = threadIdx.x; item < n_pairs + n_copy; item += blockDim.x) {
+    if (item < n_pairs) {
+      int h = item / half, i = item - h * half;
+      float s = sn[i], c = cs[i];
+      T* hd = row + (size_t)h * head_dim;
+      float a = to_f32<T>(hd[i]), b = to_f32<T>(hd[i + half]);
+      T lo = from_f32<T>(a * c - b * s), hi = from_f32<T>(a * s + b * c);
+      hd[i] = lo;
+      hd[i + half] = hi;
+      int e = h * head_dim - k_off;  // element offset of this head among the key heads
+      if (k_cache && e >= 0 && e < n_kv_heads * head_dim) {
+        size_t off = cache_row_offset(pt, pos, n_kv_heads, e / head_dim, head_dim);
+        k_cache[off + i] = lo;
+        k_cache[off + i + half] = hi;
+      }
+    } else {
+      int e = item - n_pairs;
+      int kvh = e / head_dim, d = e - kvh * head_dim;
+      size_t off = cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d;
+      v_cache[off] = row[v_off + e];
+      bool rotated = d < rotary_dims && (k_off + kvh * head_dim) < n_rot_heads * head_dim;
+      if (!rotated) k_cache[off] = row[k_off + e];
+    }
+  }
 }
 
 // x: [n_tokens, row_stride] with the heads to rotate first in each row.  When k_cache is
@@ -72,7 +77,7 @@ extern "C" int bn_rope_append(void* x, int dtype, int n_tokens, int row_stride, 
   if (k_cache && (k_off % head_dim)) return BN_ERR_BAD_ARG;  // key heads start at a head border
   int items = n_rot_heads * (rotary_dims / 2) + (k_cache ? n_kv_heads * head_dim : 0);
   if (items <= 0) return BN_OK;
-  dim3 grid(n_tokens, (items + ROPE_THREADS - 1) / ROPE_THREADS);
+  dim3 grid(n_tokens);
   const int threads = ROPE_THREADS;
   if (dtype == BN_F32)
     BN_LAUNCH((rope_append_kernel<float>), grid, threads, 0, stream, 

@@ -10,7 +10,9 @@ The reference does the same for its single sequence: it records its decode op li
 CUDA graph and patches position and length in a device struct (src/gpu_cuda.cu:186-310).
 
 Page tables are brought up to date before each replay, outside the graph.  Attention splits
-its keys for the cache's full context, so one graph serves every length.
+its keys into chunks and launches one block per possible chunk, so a graph is recorded for a
+*bucket* of lengths (1024, 2048, 4096, ... positions): a longer sequence moves the step to the
+next bucket's graph instead of every step paying for the chunks of the full context.
 """
 from __future__ import annotations
 
@@ -37,7 +39,7 @@ class DecodeRunner:
                                slots=self.slots, seq_start=ar, seq_pos0=self.tok_pos, rows=ar[:B], max_new=1,
                                max_len=cache.max_positions, decode=True)
         self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.graphs = {}  # length bucket -> recorded graph
         self.pool = pool
         self.warmed = False
         self.host_slots: Optional[List[int]] = None
@@ -65,6 +67,10 @@ class DecodeRunner:
             self.uploads += 1
         self.host_slots, self.host_rows = slots, rows
         from ..csrc import ops
+        bucket = 1024
+        while bucket < max(positions) + 1:
+            bucket *= 2
+        self.ctx.max_len = min(bucket, self.cache.max_positions)
         if not self.warmed:
             # the first step runs directly: kernels and libraries finish their lazy set-up,
             # which must not happen under capture
@@ -73,14 +79,15 @@ class DecodeRunner:
             self.launches_per_step = ops.LAUNCHES - before
             self.warmed = True
         else:
-            if self.graph is None:
+            g = self.graphs.get(self.ctx.max_len)
+            if g is None:
                 g = torch.cuda.CUDAGraph()
                 before = ops.LAUNCHES
                 with torch.cuda.graph(g, pool=self.pool):
                     self._body()
                 ops.LAUNCHES = before  # recording launches nothing
-                self.graph = g
-            self.graph.replay()
+                self.graphs[self.ctx.max_len] = g
+            g.replay()
             ops.LAUNCHES += self.launches_per_step  # the replay launches every recorded kernel
         self.host_pos = [p + 1 for p in positions]
         self.expect_tokens = None  # known once the caller has read ``sampled``
