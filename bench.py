@@ -215,6 +215,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64 and the prefill (quick runs)")
+    ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill and print its record (profiling)")
     ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -235,6 +236,13 @@ def main():
     pk = peaks()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
 
+    if args.only_prefill:
+        pre_ms = run_prefill(bn, model, cfg, warmup=2, iters=3)
+        fl = prefill_flops(cfg, PREFILL_TOKENS)
+        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                                      "ms": round(pre_ms, 3), "layers": cfg["num_hidden_layers"],
+                                      "frac": round(fl / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
     B = args.batch
     main_run = run_decode(bn, model, cfg, B, args.steps, warmup, clock=ClockSampler())
     ms_per_step = main_run["dev_ms"] / args.steps

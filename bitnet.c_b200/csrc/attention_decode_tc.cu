@@ -1,18 +1,21 @@
 // Decode attention in bfloat16 on tensor cores: one new token per sequence over its paged cache,
 // position encoding, cache write, attention and the combination of the key chunks in one launch.
 //
-// grid = (sequences, key/value heads x groups of 16 query heads, chunks of 128 positions).
-// A block first asks for its whole chunk of keys and values (two pages each, up to 64 KB) with
-// cp.async, so a step that reads hundreds of megabytes of cache has them all in flight at once;
-// while they travel it rotates the queries of its head group into a 16-row tile (the query heads
-// that share the key/value head are the rows).  The block whose chunk holds the new position
-// also rotates the new key, writes key and value to the cache and puts them into its tiles
-// directly.  Each of the four warps then takes 32 keys: scores on m16n8k16 MMAs, float32 softmax
-// statistics, the weighted value sum on MMAs again; the warps' results are merged in shared
-// memory, written as an unnormalised partial with maximum and sum, and the block that draws the
-// last ticket of its (sequence, head group) merges the chunks and writes the output.
-// Chunk borders are multiples of 128 in position, so a row's arithmetic depends on its own
-// position only.  Head sizes in steps of 16 run on the instantiation for 64, 128 or 256 with the
+// grid = (sequences, key/value heads x groups of 16 query heads, splits).  A block walks a run of
+// the sequence's cache pages (64 positions each) through a ring of three shared-memory stages fed
+// by cp.async, so the next pages are in flight while one is being used.  The query heads that
+// share the key/value head are the 16 rows of an MMA tile; the block rotates them itself.  The
+// block whose run holds the new position also rotates the new key, writes key and value to the
+// cache and puts them into its stage directly.  Each of the four warps owns 16 of a page's 64
+// keys and keeps its own running maximum, sum and output (scores and the weighted value sum on
+// m16n8k16 MMAs, statistics in float32), so the loop needs no exchange between warps; at the end
+// the four are merged in shared memory.  With more than one split per sequence the merged result
+// is written as an unnormalised partial with maximum and sum, and the block that draws the last
+// ticket of its (sequence, head group) merges the splits and writes the output.  How many pages a
+// block walks is chosen by the host from the batch (few sequences: many splits; many sequences:
+// one block per sequence and head group, no partials at all).
+// Page borders are fixed in position, so a row's arithmetic depends on its own position and the
+// split size only.  Head sizes in steps of 16 run on the instantiation for 64, 128 or 256 with the
 // missing dimensions zero in shared memory.
 //
 // Reference: scores = q.k * scale over the causal range, softmax with the maximum subtracted,
@@ -25,7 +28,7 @@
 #include "common.cuh"
 
 #define DT_THREADS 128
-#define DT_CHUNK 128
+#define DT_STAGES 3
 #define DT_ROWS 16  // query heads per block (the MMA's 16 rows)
 
 __device__ __forceinline__ void dt_cp_async16(unsigned smem, const void* gmem, bool valid) {
@@ -75,9 +78,9 @@ struct DtArgs {
   int pt_stride;
   __nv_bfloat16* k_cache;
   __nv_bfloat16* v_cache;
-  float* part_o;   // [n_seqs][n_heads][n_splits][head_dim]
-  float* part_ml;  // [n_seqs][n_heads][n_splits][2]: maximum (in the scaled log2 domain) and sum
-  int n_splits;
+  float* part_o;   // [n_seqs][n_heads][splits][head_dim]
+  float* part_ml;  // [n_seqs][n_heads][splits][2]: maximum (in the scaled log2 domain) and sum
+  int pages_per_block;
   int* tickets;    // [n_seqs][gridDim.y], zero before and after
   __nv_bfloat16* out;
   int out_stride;
@@ -89,19 +92,20 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int CHUNKS = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8;
-  constexpr int TILE_BYTES = DT_CHUNK * HD * 2;
+  constexpr int PAGE_BYTES = BN_PAGE * HD * 2;       // one page of keys (or values) of one head
+  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
   const unsigned s_q = (unsigned)__cvta_generic_to_shared(smem);
-  const unsigned s_k = s_q + DT_ROWS * HD * 2;
-  const unsigned s_v = s_k + TILE_BYTES;
+  const unsigned s_st = s_q + DT_ROWS * HD * 2;
   unsigned char* q_tile = smem;
-  unsigned char* k_tile = smem + DT_ROWS * HD * 2;
-  unsigned char* v_tile = k_tile + TILE_BYTES;
-  float* o_part = reinterpret_cast<float*>(k_tile);               // [4 warps][16][HD], after the scores
-  float* ml_part = reinterpret_cast<float*>(v_tile + TILE_BYTES);  // [4 warps][16][2]
-  float* ml_fin = ml_part + 4 * DT_ROWS * 2;                       // [16][2]
+  unsigned char* stages = smem + DT_ROWS * HD * 2;
+  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(stages + DT_STAGES * STAGE_BYTES);  // [2][HD]
+  float* ml_part = reinterpret_cast<float*>(new_kv + 2 * HD);  // [4 warps][16][2]
+  float* ml_fin = ml_part + 4 * DT_ROWS * 2;                   // [16][2]
+  float* o_part = reinterpret_cast<float*>(stages);            // [4 warps][16][HD], after the loop
+  static_assert(4 * DT_ROWS * HD * 4 <= DT_STAGES * STAGE_BYTES, "the warps' outputs reuse the stages");
   __shared__ int s_last;
 
-  const int b = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g4 = lane >> 2, t4 = lane & 3;
   const int head_dim = a.head_dim, n_kv_heads = a.n_kv_heads, n_heads = a.n_heads;
   const int group = n_heads / n_kv_heads;
@@ -111,29 +115,37 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   const int G = min(DT_ROWS, group - gb * DT_ROWS);
   const int pos = a.tok_pos[b];
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int c0 = split * DT_CHUNK;
-  if (c0 > pos || c0 + DT_CHUNK <= lo) return;  // no key of this chunk is visible
+  // pages that hold a visible key, and this block's run of them
+  const int p_lo = lo / BN_PAGE, p_hi = pos / BN_PAGE;
+  const int my_lo = max(p_lo, (int)blockIdx.z * a.pages_per_block);
+  const int my_hi = min(p_hi, (int)(blockIdx.z + 1) * a.pages_per_block - 1);
+  if (my_lo > my_hi) return;
+  const int n_pages = my_hi - my_lo + 1;
+  const int n_splits = gridDim.z;
   const int* pt = a.page_table + (size_t)a.slots[b] * a.pt_stride;
-  const int page_a = pt[c0 / BN_PAGE];
-  const int page_b = (c0 + BN_PAGE <= pos) ? pt[c0 / BN_PAGE + 1] : page_a;
-  auto row_off = [&](int j) -> size_t {  // cache row of key/value j of this chunk (0 <= j < 128)
-    int page = j < BN_PAGE ? page_a : page_b;
-    return (((size_t)page * n_kv_heads + kvh) * BN_PAGE + (j & (BN_PAGE - 1))) * (size_t)head_dim;
-  };
   const int real_chunks = head_dim / 8;
-  const int new_row = (pos / DT_CHUNK == split) ? pos - c0 : -1;  // the new token's row, if it is in this chunk
-  const int j_lo = max(0, lo - c0), j_hi = min(DT_CHUNK, pos - c0 + 1);  // visible rows [j_lo, j_hi)
+  const bool has_new = (p_hi >= my_lo && p_hi <= my_hi);  // the new token's page is in this run
+  const int new_row = pos - p_hi * BN_PAGE;
 
-  // ---- ask for the chunk's keys and values (rows outside the range and padding dimensions are zero)
-  for (int p = tid; p < DT_CHUNK * CHUNKS; p += DT_THREADS) {
-    int r = p / CHUNKS, c = p - r * CHUNKS;
-    if (r == new_row) continue;  // written below from the new token's row
-    bool ok = r >= j_lo && r < j_hi && c < real_chunks;
-    size_t off = ok ? row_off(r) + (size_t)c * 8 : 0;
-    dt_cp_async16(s_k + dt_off<HD>(r, c), a.k_cache + off, ok);
-    dt_cp_async16(s_v + dt_off<HD>(r, c), a.v_cache + off, ok);
+  auto load_page = [&](int page_idx, int stage) {  // rows outside [lo, pos] and padding dimensions are zero
+    const int page = pt[page_idx];
+    const size_t base = ((size_t)page * n_kv_heads + kvh) * BN_PAGE * (size_t)head_dim;
+    const int first = page_idx * BN_PAGE;
+    const unsigned sk = s_st + stage * STAGE_BYTES, sv = sk + PAGE_BYTES;
+    for (int p = tid; p < BN_PAGE * CHUNKS; p += DT_THREADS) {
+      int r = p / CHUNKS, c = p - r * CHUNKS;
+      if (has_new && page_idx == p_hi && r == new_row) continue;  // placed from the new token's row
+      bool ok = first + r >= lo && first + r <= pos && c < real_chunks;
+      size_t off = ok ? base + (size_t)r * head_dim + (size_t)c * 8 : 0;
+      dt_cp_async16(sk + dt_off<HD>(r, c), a.k_cache + off, ok);
+      dt_cp_async16(sv + dt_off<HD>(r, c), a.v_cache + off, ok);
+    }
+  };
+#pragma unroll
+  for (int st = 0; st < DT_STAGES - 1; ++st) {
+    if (st < n_pages) load_page(my_lo + st, st);
+    asm volatile("cp.async.commit_group;");
   }
-  asm volatile("cp.async.commit_group;");
 
   // ---- queries of this head group: rotate, round to bfloat16, place as rows of the 16-row tile
   const __nv_bfloat16* qrow = a.qkv + (size_t)b * a.q_stride;
@@ -147,12 +159,12 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   }
   for (int p = tid; p < G * half; p += DT_THREADS) {
     int g = p / half, i = p - g * half;
-    float s, c;
-    sincosf(dt_angle(pos, i, a.theta_scale), &s, &c);
+    float sn, cs;
+    sincosf(dt_angle(pos, i, a.theta_scale), &sn, &cs);
     const __nv_bfloat16* hd = qrow + (size_t)(h0 + g) * head_dim;
     float x = __bfloat162float(hd[i]), y = __bfloat162float(hd[i + half]);
-    *q_at(g, i) = __float2bfloat16_rn(x * c - y * s);
-    *q_at(g, i + half) = __float2bfloat16_rn(x * s + y * c);
+    *q_at(g, i) = __float2bfloat16_rn(x * cs - y * sn);
+    *q_at(g, i + half) = __float2bfloat16_rn(x * sn + y * cs);
   }
   {
     const int rest = head_dim - a.rotary_dims;
@@ -161,117 +173,133 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
       *q_at(g, d) = qrow[(size_t)(h0 + g) * head_dim + d];
     }
   }
-  // ---- the new token's key (rotated) and value: to the cache and into this block's tiles
-  if (new_row >= 0) {
-    const size_t off = row_off(new_row);
+  // ---- the new token's key (rotated) and value: to the cache, and kept for this block's stage
+  if (has_new) {
+    const size_t off = (((size_t)pt[p_hi] * n_kv_heads + kvh) * BN_PAGE + new_row) * (size_t)head_dim;
     const __nv_bfloat16* kraw = qrow + a.k_off + (size_t)kvh * head_dim;
     const __nv_bfloat16* vraw = qrow + a.v_off + (size_t)kvh * head_dim;
-    auto tile_at = [&](unsigned char* tile, int d) -> __nv_bfloat16* {
-      return reinterpret_cast<__nv_bfloat16*>(tile + dt_off<HD>(new_row, d >> 3)) + (d & 7);
-    };
     for (int i = tid; i < half; i += DT_THREADS) {
-      float s, c;
-      sincosf(dt_angle(pos, i, a.theta_scale), &s, &c);
+      float sn, cs;
+      sincosf(dt_angle(pos, i, a.theta_scale), &sn, &cs);
       float x = __bfloat162float(kraw[i]), y = __bfloat162float(kraw[i + half]);
-      __nv_bfloat16 k0 = __float2bfloat16_rn(x * c - y * s), k1 = __float2bfloat16_rn(x * s + y * c);
+      __nv_bfloat16 k0 = __float2bfloat16_rn(x * cs - y * sn), k1 = __float2bfloat16_rn(x * sn + y * cs);
       a.k_cache[off + i] = k0;
       a.k_cache[off + i + half] = k1;
-      *tile_at(k_tile, i) = k0;
-      *tile_at(k_tile, i + half) = k1;
+      new_kv[i] = k0;
+      new_kv[i + half] = k1;
     }
     for (int d = a.rotary_dims + tid; d < head_dim; d += DT_THREADS) {
       a.k_cache[off + d] = kraw[d];
-      *tile_at(k_tile, d) = kraw[d];
+      new_kv[d] = kraw[d];
     }
     for (int d = tid; d < head_dim; d += DT_THREADS) {
       a.v_cache[off + d] = vraw[d];
-      *tile_at(v_tile, d) = vraw[d];
+      new_kv[HD + d] = vraw[d];
     }
-    for (int d = head_dim + tid; d < HD; d += DT_THREADS) {  // padding dimensions of the new row
-      *tile_at(k_tile, d) = __float2bfloat16_rn(0.f);
-      *tile_at(v_tile, d) = __float2bfloat16_rn(0.f);
+    for (int d = head_dim + tid; d < HD; d += DT_THREADS) {
+      new_kv[d] = __float2bfloat16_rn(0.f);
+      new_kv[HD + d] = __float2bfloat16_rn(0.f);
     }
   }
-  asm volatile("cp.async.wait_group 0;");
-  __syncthreads();
 
-  // ---- this warp's 32 keys: S = Q K^T
-  float s[4][4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-  const int krow0 = warp * 32;
-#pragma unroll
-  for (int ks = 0; ks < KSTEPS; ++ks) {
-    unsigned a0, a1, a2, a3;
-    const int mi = lane >> 3, r = lane & 7;
-    dt_ldsm_x4(s_q + dt_off<HD>(r + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
-#pragma unroll
-    for (int j = 0; j < 4; j += 2) {
-      unsigned b0, b1, b2, b3;
-      dt_ldsm_x4(s_k + dt_off<HD>(krow0 + (j + (mi >> 1)) * 8 + r, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-      dt_mma(s[j], a0, a1, a2, a3, b0, b1);
-      dt_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
-    }
-  }
-  // mask, maximum, exponentials, sum; rows g4 and g4 + 8 of the head tile
-  float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.f, 0.f};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      int jr = krow0 + j * 8 + 2 * t4 + (c & 1);
-      bool ok = jr >= j_lo && jr < j_hi;
-      float v = ok ? s[j][c] * a.scale_log2e : -INFINITY;
-      s[j][c] = v;
-      m_w[c >> 1] = fmaxf(m_w[c >> 1], v);
-    }
-  }
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 1));
-    m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 2));
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      int e = c >> 1;
-      float p = (m_w[e] == -INFINITY) ? 0.f : exp2f(s[j][c] - m_w[e]);
-      s[j][c] = p;
-      l_w[e] += p;
-    }
-  }
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    l_w[e] += __shfl_xor_sync(0xffffffffu, l_w[e], 1);
-    l_w[e] += __shfl_xor_sync(0xffffffffu, l_w[e], 2);
-  }
-  // ---- O = P V over this warp's 32 keys
+  // ---- the loop over this block's pages; warp w owns keys 16w..16w+15 of every page
   float o[NT_O][4];
 #pragma unroll
   for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int mi = lane >> 3, r8 = lane & 7;
+  for (int i = 0; i < n_pages; ++i) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(DT_STAGES - 2));
+    __syncthreads();  // stage i has landed for everyone; stage i-1 is free again; q and new_kv are written
+    if (i + DT_STAGES - 1 < n_pages) load_page(my_lo + i + DT_STAGES - 1, (i + DT_STAGES - 1) % DT_STAGES);
+    asm volatile("cp.async.commit_group;");
+    const int page_idx = my_lo + i;
+    const unsigned sk = s_st + (i % DT_STAGES) * STAGE_BYTES, sv = sk + PAGE_BYTES;
+    if (has_new && page_idx == p_hi) {
+      // put the new token's row into the stage (the copies above left it out)
+      unsigned char* kt = stages + (i % DT_STAGES) * STAGE_BYTES;
+      for (int c = tid; c < 2 * CHUNKS; c += DT_THREADS) {
+        int which = c / CHUNKS, cc = c - which * CHUNKS;
+        *reinterpret_cast<uint4*>(kt + which * PAGE_BYTES + dt_off<HD>(new_row, cc)) =
+            *reinterpret_cast<const uint4*>(new_kv + which * HD + cc * 8);
+      }
+      __syncthreads();
+    }
+    // S = Q K^T for this warp's 16 keys
+    float s[2][4];
+    s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+    const int krow0 = warp * 16;
 #pragma unroll
-  for (int ks = 0; ks < 2; ++ks) {
-    unsigned a0 = dt_pack(s[2 * ks][0], s[2 * ks][1]);
-    unsigned a1 = dt_pack(s[2 * ks][2], s[2 * ks][3]);
-    unsigned a2 = dt_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-    unsigned a3 = dt_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-    const int mi = lane >> 3, r = lane & 7;
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      unsigned a0, a1, a2, a3, b0, b1, b2, b3;
+      dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
+      dt_ldsm_x4(sk + dt_off<HD>(krow0 + (mi >> 1) * 8 + r8, ks * 2 + (mi & 1)), b0, b1, b2, b3);
+      dt_mma(s[0], a0, a1, a2, a3, b0, b1);
+      dt_mma(s[1], a0, a1, a2, a3, b2, b3);
+    }
+    // mask, running maximum, exponentials; rows g4 and g4 + 8 of the head tile
+    float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-    for (int j = 0; j < NT_O; j += 2) {
-      unsigned b0, b1, b2, b3;
-      dt_ldsm_x4_trans(s_v + dt_off<HD>(krow0 + ks * 16 + (mi & 1) * 8 + r, j + (mi >> 1)), b0, b1, b2, b3);
-      dt_mma(o[j], a0, a1, a2, a3, b0, b1);
-      dt_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        int kpos = page_idx * BN_PAGE + krow0 + j * 8 + 2 * t4 + (c & 1);
+        bool ok = kpos >= lo && kpos <= pos;
+        float v = ok ? s[j][c] * a.scale_log2e : -INFINITY;
+        s[j][c] = v;
+        m_new[c >> 1] = fmaxf(m_new[c >> 1], v);
+      }
+    }
+    float alpha[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 1));
+      m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 2));
+      alpha[e] = (m_run[e] == -INFINITY) ? 0.f : exp2f(m_run[e] - m_new[e]);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        int e = c >> 1;
+        float p = (m_new[e] == -INFINITY) ? 0.f : exp2f(s[j][c] - m_new[e]);
+        s[j][c] = p;
+        l_add[e] += p;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      l_run[e] = l_run[e] * alpha[e] + l_add[e];  // per-thread partial sums; quads are combined at the end
+      m_run[e] = m_new[e];
+    }
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
+    // O += P V over the 16 keys
+    {
+      unsigned a0 = dt_pack(s[0][0], s[0][1]), a1 = dt_pack(s[0][2], s[0][3]);
+      unsigned a2 = dt_pack(s[1][0], s[1][1]), a3 = dt_pack(s[1][2], s[1][3]);
+#pragma unroll
+      for (int j = 0; j < NT_O; j += 2) {
+        unsigned b0, b1, b2, b3;
+        dt_ldsm_x4_trans(sv + dt_off<HD>(krow0 + (mi & 1) * 8 + r8, j + (mi >> 1)), b0, b1, b2, b3);
+        dt_mma(o[j], a0, a1, a2, a3, b0, b1);
+        dt_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+      }
     }
   }
-  __syncthreads();  // every warp has read the key tile: it now holds the warps' partial outputs
+  asm volatile("cp.async.wait_group 0;");
+  __syncthreads();  // every warp is done with the stages: they now hold the warps' outputs
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
     int row = g4 + e * 8;
     if (t4 == 0) {
-      ml_part[(warp * DT_ROWS + row) * 2] = m_w[e];
-      ml_part[(warp * DT_ROWS + row) * 2 + 1] = l_w[e];
+      ml_part[(warp * DT_ROWS + row) * 2] = m_run[e];
+      ml_part[(warp * DT_ROWS + row) * 2 + 1] = l_run[e];
     }
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
@@ -280,7 +308,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
     }
   }
   __syncthreads();
-  // ---- merge the four warps: this chunk's unnormalised partial, its maximum and its sum
+  // ---- merge the four warps
   if (tid < G) {
     float m = -INFINITY;
     for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_part[(w * DT_ROWS + tid) * 2]);
@@ -291,11 +319,10 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
     }
     ml_fin[tid * 2] = m;
     ml_fin[tid * 2 + 1] = l;
-    size_t oo = (((size_t)b * n_heads + h0 + tid) * a.n_splits + split) * 2;
-    a.part_ml[oo] = m;
-    a.part_ml[oo + 1] = l;
   }
   __syncthreads();
+  const int z_lo = p_lo / a.pages_per_block, z_hi = p_hi / a.pages_per_block;  // splits with a visible page
+  const bool alone = (z_lo == z_hi);
   for (int i = tid; i < G * head_dim; i += DT_THREADS) {
     int g = i / head_dim, d = i - g * head_dim;
     float m = ml_fin[g * 2], acc = 0.f;
@@ -303,45 +330,54 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
       float mw = ml_part[(w * DT_ROWS + g) * 2];
       if (mw != -INFINITY) acc += exp2f(mw - m) * o_part[(size_t)(w * DT_ROWS + g) * HD + d];
     }
-    a.part_o[(((size_t)b * n_heads + h0 + g) * a.n_splits + split) * head_dim + d] = acc;
+    if (alone)  // the only split of this sequence: normalise and store, no partials
+      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(acc / ml_fin[g * 2 + 1]);
+    else
+      a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + blockIdx.z) * head_dim + d] = acc;
+  }
+  if (alone) return;
+  if (tid < G) {
+    size_t oo = (((size_t)b * n_heads + h0 + tid) * n_splits + blockIdx.z) * 2;
+    a.part_ml[oo] = ml_fin[tid * 2];
+    a.part_ml[oo + 1] = ml_fin[tid * 2 + 1];
   }
 
-  // ---- the block that draws the last ticket of this (sequence, head group) merges the chunks
-  const int s0 = lo / DT_CHUNK, s1 = pos / DT_CHUNK;
+  // ---- the block that draws the last ticket of this (sequence, head group) merges the splits
   __threadfence();
   __syncthreads();
   if (tid == 0) {
     int* t = a.tickets + (size_t)b * gridDim.y + blockIdx.y;
     int ticket = atomicAdd(t, 1);
-    s_last = (ticket == s1 - s0);
+    s_last = (ticket == z_hi - z_lo);
     if (s_last) *t = 0;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
   if (tid < G) {
-    const float* ml = a.part_ml + ((size_t)b * n_heads + h0 + tid) * a.n_splits * 2;
+    const float* ml = a.part_ml + ((size_t)b * n_heads + h0 + tid) * n_splits * 2;
     float m = -INFINITY;
-    for (int s_ = s0; s_ <= s1; ++s_) m = fmaxf(m, __ldcg(ml + 2 * s_));
+    for (int z = z_lo; z <= z_hi; ++z) m = fmaxf(m, __ldcg(ml + 2 * z));
     float den = 0.f;
-    for (int s_ = s0; s_ <= s1; ++s_) den += exp2f(__ldcg(ml + 2 * s_) - m) * __ldcg(ml + 2 * s_ + 1);
+    for (int z = z_lo; z <= z_hi; ++z) den += exp2f(__ldcg(ml + 2 * z) - m) * __ldcg(ml + 2 * z + 1);
     ml_fin[tid * 2] = m;
     ml_fin[tid * 2 + 1] = den;
   }
   __syncthreads();
   for (int i = tid; i < G * head_dim; i += DT_THREADS) {
     int g = i / head_dim, d = i - g * head_dim;
-    const float* ml = a.part_ml + ((size_t)b * n_heads + h0 + g) * a.n_splits * 2;
-    const float* po = a.part_o + ((size_t)b * n_heads + h0 + g) * a.n_splits * head_dim;
+    const float* ml = a.part_ml + ((size_t)b * n_heads + h0 + g) * n_splits * 2;
+    const float* po = a.part_o + ((size_t)b * n_heads + h0 + g) * n_splits * head_dim;
     float m = ml_fin[g * 2], num = 0.f;
-    for (int s_ = s0; s_ <= s1; ++s_) num += exp2f(__ldcg(ml + 2 * s_) - m) * __ldcg(po + (size_t)s_ * head_dim + d);
+    for (int z = z_lo; z <= z_hi; ++z) num += exp2f(__ldcg(ml + 2 * z) - m) * __ldcg(po + (size_t)z * head_dim + d);
     a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num / ml_fin[g * 2 + 1]);
   }
 }
 
 template <int HD>
 static int launch_dt(const DtArgs& a, dim3 grid, cudaStream_t stream) {
-  size_t smem = (size_t)DT_ROWS * HD * 2 + 2 * (size_t)DT_CHUNK * HD * 2 + (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float);
+  size_t smem = (size_t)DT_ROWS * HD * 2 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + 2 * HD * 2 +
+                (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -355,18 +391,20 @@ static int launch_dt(const DtArgs& a, dim3 grid, cudaStream_t stream) {
 // qkv: [n_seqs, q_stride] bfloat16 rows with the raw query heads first, the key heads at element
 // k_off and the value heads at v_off (all multiples of 8 elements).  The kernel rotates queries and
 // the new key (rotary_dims = 0: none), writes the new key and value into the cache at tok_pos[b],
-// attends and combines.  part_o / part_ml: scratch of n_seqs * n_heads * n_splits * head_dim and
-// n_seqs * n_heads * n_splits * 2 floats, n_splits * 128 covering the longest sequence;
-// tickets: n_seqs * n_kv_heads * ceil(group / 16) ints, zero before and after.
+// attends and combines.  A block walks pages_per_block pages of 64 positions; n_splits blocks cover
+// a sequence, so n_splits * pages_per_block * 64 must cover the longest sequence.  part_o / part_ml:
+// scratch of n_seqs * n_heads * n_splits * head_dim and n_seqs * n_heads * n_splits * 2 floats (unused
+// when n_splits is 1); tickets: n_seqs * n_kv_heads * ceil(group / 16) ints, zero before and after.
 extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, int v_off, void* out, int out_stride,
                                       int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                       int rotary_dims, float theta_scale, const int* tok_pos, const int* slots,
                                       const int* page_table, int pt_stride, void* k_cache, void* v_cache,
-                                      float* part_o, float* part_ml, int n_splits, int* tickets, int n_tickets,
-                                      cudaStream_t stream) {
+                                      float* part_o, float* part_ml, int n_splits, int pages_per_block, int* tickets,
+                                      int n_tickets, cudaStream_t stream) {
   if (n_seqs <= 0) return BN_OK;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || n_splits <= 0 ||
-      window < 0 || !part_o || !part_ml || !tickets || rotary_dims < 0 || rotary_dims > head_dim || (rotary_dims & 1))
+      pages_per_block <= 0 || window < 0 || !part_o || !part_ml || !tickets || rotary_dims < 0 ||
+      rotary_dims > head_dim || (rotary_dims & 1))
     return BN_ERR_BAD_ARG;
   int group = n_heads / n_kv_heads;
   int gblocks = (group + DT_ROWS - 1) / DT_ROWS;
@@ -379,7 +417,7 @@ extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, 
   a.scale_log2e = scale * 1.4426950408889634f; a.window = window; a.rotary_dims = rotary_dims;
   a.theta_scale = theta_scale; a.tok_pos = tok_pos; a.slots = slots; a.page_table = page_table; a.pt_stride = pt_stride;
   a.k_cache = (__nv_bfloat16*)k_cache; a.v_cache = (__nv_bfloat16*)v_cache; a.part_o = part_o; a.part_ml = part_ml;
-  a.n_splits = n_splits; a.tickets = tickets; a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
+  a.pages_per_block = pages_per_block; a.tickets = tickets; a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
   dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits);
   if (head_dim <= 64) return launch_dt<64>(a, grid, stream);
   if (head_dim <= 128) return launch_dt<128>(a, grid, stream);

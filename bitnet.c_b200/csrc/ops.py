@@ -289,7 +289,16 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         raise KernelError("attention_decode_fused: offsets run past the row")
     if out.shape[0] < n_seqs or out.shape[1] != n_heads * head_dim or tok_pos.shape[0] < n_seqs or qkv.shape[0] < n_seqs:
         raise KernelError("attention_decode_fused: out, qkv or tok_pos does not fit")
-    n_splits = max(1, (max_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+    # few sequences: many blocks per sequence so that all SMs read the cache; many sequences: one
+    # block per (sequence, head group) walks all its pages and no partial results are needed
+    pages = max(1, (max_len + PAGE - 1) // PAGE)
+    blocks_per_split = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
+    if blocks_per_split >= 2 * N_SMS:
+        want_splits = 1
+    else:
+        want_splits = max(1, min(pages, (4 * N_SMS + blocks_per_split - 1) // blocks_per_split))
+    pages_per_block = (pages + want_splits - 1) // want_splits
+    n_splits = (pages + pages_per_block - 1) // pages_per_block
     part_o = torch.empty((n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
     _scr, counters = _split_scratch(qkv.device)
@@ -297,8 +306,8 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         _ptr(qkv), c_int(qkv.shape[1]), c_int(k_off), c_int(v_off), _ptr(out), c_int(out.shape[1]), c_int(n_seqs),
         c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(rotary_dims),
         c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
-        _ptr(v_cache), _ptr(part_o), _ptr(part_ml), c_int(n_splits), _ptr(counters), c_int(counters.numel()),
-        _stream()), "attention_decode_fused")
+        _ptr(v_cache), _ptr(part_o), _ptr(part_ml), c_int(n_splits), c_int(pages_per_block), _ptr(counters),
+        c_int(counters.numel()), _stream()), "attention_decode_fused")
     return out
 
 
