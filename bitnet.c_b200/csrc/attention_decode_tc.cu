@@ -2,8 +2,8 @@
 // position encoding, cache write, attention and the combination of the key chunks in one launch.
 //
 // grid = (sequences, key/value heads x groups of 16 query heads, splits).  A block walks a run of
-// the sequence's cache pages (64 positions each) through a ring of three shared-memory stages fed
-// by cp.async, so the next pages are in flight while one is being used.  The query heads that
+// the sequence's cache pages (64 positions each) through a ring of two or three shared-memory stages
+// fed by cp.async, filled completely at the start, so the next pages are in flight while one is used.  The query heads that
 // share the key/value head are the 16 rows of an MMA tile; the block rotates them itself.  The
 // block whose run holds the new position also rotates the new key, writes key and value to the
 // cache and puts them into its stage directly.  Each of the four warps owns 16 of a page's 64
@@ -28,7 +28,6 @@
 #include "common.cuh"
 
 #define DT_THREADS 128
-#define DT_STAGES 3
 #define DT_ROWS 16  // query heads per block (the MMA's 16 rows)
 
 __device__ __forceinline__ void dt_cp_async16(unsigned smem, const void* gmem, bool valid) {
@@ -86,7 +85,7 @@ struct DtArgs {
   int out_stride;
 };
 
-template <int HD>
+template <int HD, int DT_STAGES>
 __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs a) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
@@ -142,7 +141,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
     }
   };
 #pragma unroll
-  for (int st = 0; st < DT_STAGES - 1; ++st) {
+  for (int st = 0; st < DT_STAGES; ++st) {  // the whole ring is filled at once
     if (st < n_pages) load_page(my_lo + st, st);
     asm volatile("cp.async.commit_group;");
   }
@@ -208,11 +207,23 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int mi = lane >> 3, r8 = lane & 7;
+  // Q as MMA operand fragments, kept in registers when the head is small enough
+  constexpr bool Q_IN_REGS = HD <= 128;
+  unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
   for (int i = 0; i < n_pages; ++i) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(DT_STAGES - 2));
-    __syncthreads();  // stage i has landed for everyone; stage i-1 is free again; q and new_kv are written
-    if (i + DT_STAGES - 1 < n_pages) load_page(my_lo + i + DT_STAGES - 1, (i + DT_STAGES - 1) % DT_STAGES);
-    asm volatile("cp.async.commit_group;");
+    // groups committed so far: the ring (DT_STAGES) plus one per earlier iteration but the first
+    if (i == 0) asm volatile("cp.async.wait_group %0;" ::"n"(DT_STAGES - 1));
+    else asm volatile("cp.async.wait_group %0;" ::"n"(DT_STAGES - 2));
+    __syncthreads();  // page i has landed for everyone; the stage of page i-1 is free; q and new_kv are written
+    if (i >= 1) {
+      if (i - 1 + DT_STAGES < n_pages) load_page(my_lo + i - 1 + DT_STAGES, (i - 1) % DT_STAGES);
+      asm volatile("cp.async.commit_group;");
+    }
+    if (Q_IN_REGS && i == 0) {
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks)
+        dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
     const int page_idx = my_lo + i;
     const unsigned sk = s_st + (i % DT_STAGES) * STAGE_BYTES, sv = sk + PAGE_BYTES;
     if (has_new && page_idx == p_hi) {
@@ -232,7 +243,11 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       unsigned a0, a1, a2, a3, b0, b1, b2, b3;
-      dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
+      if (Q_IN_REGS) {
+        a0 = qf[ks][0]; a1 = qf[ks][1]; a2 = qf[ks][2]; a3 = qf[ks][3];
+      } else {
+        dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
+      }
       dt_ldsm_x4(sk + dt_off<HD>(krow0 + (mi >> 1) * 8 + r8, ks * 2 + (mi & 1)), b0, b1, b2, b3);
       dt_mma(s[0], a0, a1, a2, a3, b0, b1);
       dt_mma(s[1], a0, a1, a2, a3, b2, b3);
@@ -374,18 +389,26 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   }
 }
 
-template <int HD>
-static int launch_dt(const DtArgs& a, dim3 grid, cudaStream_t stream) {
+template <int HD, int DT_STAGES>
+static int launch_dt2(const DtArgs& a, dim3 grid, cudaStream_t stream) {
   size_t smem = (size_t)DT_ROWS * HD * 2 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + 2 * HD * 2 +
                 (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<HD, DT_STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
-  BN_LAUNCH(attention_decode_tc_kernel<HD>, grid, DT_THREADS, smem, stream, a);
+  BN_LAUNCH((attention_decode_tc_kernel<HD, DT_STAGES>), grid, DT_THREADS, smem, stream, a);
   return BN_OK;
+}
+// Short runs (at most two pages per block) take the two-stage ring: less shared memory, more
+// blocks per SM, and both pages are requested at once anyway.
+template <int HD>
+static int launch_dt(const DtArgs& a, dim3 grid, cudaStream_t stream) {
+  if (a.pages_per_block <= 2) return launch_dt2<HD, 2>(a, grid, stream);
+  return launch_dt2<HD, 3>(a, grid, stream);
 }
 
 // qkv: [n_seqs, q_stride] bfloat16 rows with the raw query heads first, the key heads at element
