@@ -2,11 +2,16 @@
 // position encoding, cache write, attention and the combination of the key chunks in one launch.
 //
 // grid = (sequences, key/value heads x groups of 16 query heads, splits).  A block walks a run of
-// the sequence's cache pages (64 positions each) through a ring of two or three shared-memory stages
-// fed by cp.async, filled completely at the start, so the next pages are in flight while one is used.  The query heads that
-// share the key/value head are the 16 rows of an MMA tile; the block rotates them itself.  The
-// block whose run holds the new position also rotates the new key, writes key and value to the
-// cache and puts them into its stage directly.  Each of the four warps owns 16 of a page's 64
+// the sequence's cache pages (64 positions each) through a ring of two or three shared-memory
+// stages.  One thread requests whole pages by TMA (a page of one head's keys is HD/64 boxes of
+// 64 rows x 128 bytes, 128-byte swizzled, completing on the stage's mbarrier); the ring is filled
+// at the start, before the dependency wait of the programmatic launch: page table, positions and
+// the cached rows of earlier positions were written by kernels that completed before the kernel in
+// front of this one, which only produces the new token's q|k|v row.  The query heads that share
+// the key/value head are the 16 rows of an MMA tile; the block rotates them itself.  The block
+// whose run holds the new position also rotates the new key, writes key and value to the cache
+// and puts them into its stage directly (rows of that page behind the new position are cleared
+// in shared memory, whatever the cache holds there).  Each of the four warps owns 16 of a page's 64
 // keys and keeps its own running maximum, sum and output (scores and the weighted value sum on
 // m16n8k16 MMAs, statistics in float32), so the loop needs no exchange between warps; at the end
 // the four are merged in shared memory.  With more than one split per sequence the merged result
@@ -25,15 +30,11 @@
 // (src/transformer/cpu_backend.c:283-296, src/model_arch.c:322-338).  The reference's CUDA decode
 // attention is one block per head on CUDA cores without a split over the keys, with a variant
 // that fuses the rotary encoding of q (src/gpu_cuda.cu:9718, 9989).
-#include "common.cuh"
+#include "tma.cuh"
 
 #define DT_THREADS 128
 #define DT_ROWS 16  // query heads per block (the MMA's 16 rows)
 
-__device__ __forceinline__ void dt_cp_async16(unsigned smem, const void* gmem, bool valid) {
-  int bytes = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem), "l"(gmem), "r"(bytes));
-}
 __device__ __forceinline__ void dt_ldsm_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -52,11 +53,18 @@ __device__ __forceinline__ unsigned dt_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
-// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold HD bfloat16 (XOR swizzle).
+// Byte offset of 16-byte chunk `chunk` of row `row` in the query tile, whose rows hold HD bfloat16 (XOR swizzle).
 template <int HD>
 __device__ __forceinline__ unsigned dt_off(int row, int chunk) {
   return (unsigned)(row * HD * 2 + ((chunk ^ (row & 7)) << 4));
 }
+// The same for a page of keys or values as TMA leaves it: boxes of 64 rows x 128 bytes (64
+// dimensions), box after box, the chunk index within a row XORed with the row's low three bits.
+#define DT_BOX_BYTES (BN_PAGE * 128)
+__device__ __forceinline__ unsigned dt_koff(int row, int chunk) {
+  return (unsigned)((chunk >> 3) * DT_BOX_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+#define DT_ERR_PAGE_WAIT 4
 __device__ __forceinline__ float dt_angle(int pos, int i, float theta_scale) {
   float angle = (float)pos;
   for (int k = 0; k < i; ++k) angle *= theta_scale;
@@ -77,6 +85,7 @@ struct DtArgs {
   int pt_stride;
   __nv_bfloat16* k_cache;
   __nv_bfloat16* v_cache;
+  int* status;     // 0, or DT_ERR_PAGE_WAIT when a page never arrived
   float* part_o;   // [n_seqs][n_heads][splits][head_dim]
   float* part_ml;  // [n_seqs][n_heads][splits][2]: maximum (in the scaled log2 domain) and sum
   int pages_per_block;
@@ -86,22 +95,25 @@ struct DtArgs {
 };
 
 template <int HD, int DT_STAGES>
-__global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs a) {
+__global__ void __launch_bounds__(DT_THREADS)
+attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DtArgs a) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
-  pdl_wait();               // the kernels before this one have completed and their writes are visible
-  extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int CHUNKS = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  constexpr int CHUNKS = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, BOXES = HD / 64;
   constexpr int PAGE_BYTES = BN_PAGE * HD * 2;       // one page of keys (or values) of one head
   constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
-  const unsigned s_q = (unsigned)__cvta_generic_to_shared(smem);
-  const unsigned s_st = s_q + DT_ROWS * HD * 2;
-  unsigned char* q_tile = smem;
-  unsigned char* stages = smem + DT_ROWS * HD * 2;
-  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(stages + DT_STAGES * STAGE_BYTES);  // [2][HD]
+  constexpr int OSTRIDE = HD + 8;                    // floats per row of a warp's output (padded against bank conflicts)
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* stages = smem;                      // 1024-byte aligned: the swizzle is a function of the address
+  unsigned char* q_tile = stages + DT_STAGES * STAGE_BYTES;
+  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(q_tile + DT_ROWS * HD * 2);  // [2][HD]
   float* ml_part = reinterpret_cast<float*>(new_kv + 2 * HD);  // [4 warps][16][2]
   float* ml_fin = ml_part + 4 * DT_ROWS * 2;                   // [16][2]
-  float* o_part = reinterpret_cast<float*>(stages);            // [4 warps][16][HD], after the loop
-  static_assert(4 * DT_ROWS * HD * 4 <= DT_STAGES * STAGE_BYTES, "the warps' outputs reuse the stages");
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(ml_fin + DT_ROWS * 2);  // [DT_STAGES]
+  float* cs_tab = reinterpret_cast<float*>(bars + DT_STAGES);  // [rotary_dims / 2][2]: cosine, sine of this position's angles
+  float* o_part = reinterpret_cast<float*>(stages);            // [4 warps][16][OSTRIDE], after the loop
+  static_assert(4 * DT_ROWS * OSTRIDE * 4 <= DT_STAGES * STAGE_BYTES, "the warps' outputs reuse the stages");
+  const unsigned s_q = smem_u32(q_tile), s_st = smem_u32(stages), full0 = smem_u32(bars);
   __shared__ int s_last;
 
   const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -118,37 +130,47 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   const int p_lo = lo / BN_PAGE, p_hi = pos / BN_PAGE;
   const int my_lo = max(p_lo, (int)blockIdx.z * a.pages_per_block);
   const int my_hi = min(p_hi, (int)(blockIdx.z + 1) * a.pages_per_block - 1);
-  if (my_lo > my_hi) return;
+  if (my_lo > my_hi) {
+    pdl_wait();  // no block of this grid ends before the grids in front of it have
+    return;
+  }
   const int n_pages = my_hi - my_lo + 1;
   const int n_splits = gridDim.z;
   const int* pt = a.page_table + (size_t)a.slots[b] * a.pt_stride;
-  const int real_chunks = head_dim / 8;
   const bool has_new = (p_hi >= my_lo && p_hi <= my_hi);  // the new token's page is in this run
   const int new_row = pos - p_hi * BN_PAGE;
 
-  auto load_page = [&](int page_idx, int stage) {  // rows outside [lo, pos] and padding dimensions are zero
+  auto request_page = [&](int page_idx, int stage) {  // one thread: the whole page of this head, keys and values
     const int page = pt[page_idx];
-    const size_t base = ((size_t)page * n_kv_heads + kvh) * BN_PAGE * (size_t)head_dim;
-    const int first = page_idx * BN_PAGE;
-    const unsigned sk = s_st + stage * STAGE_BYTES, sv = sk + PAGE_BYTES;
-    for (int p = tid; p < BN_PAGE * CHUNKS; p += DT_THREADS) {
-      int r = p / CHUNKS, c = p - r * CHUNKS;
-      if (has_new && page_idx == p_hi && r == new_row) continue;  // placed from the new token's row
-      bool ok = first + r >= lo && first + r <= pos && c < real_chunks;
-      size_t off = ok ? base + (size_t)r * head_dim + (size_t)c * 8 : 0;
-      dt_cp_async16(sk + dt_off<HD>(r, c), a.k_cache + off, ok);
-      dt_cp_async16(sv + dt_off<HD>(r, c), a.v_cache + off, ok);
+    const unsigned bar = full0 + 8 * stage, sk = s_st + stage * STAGE_BYTES, sv = sk + PAGE_BYTES;
+    mbar_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+    for (int bx = 0; bx < BOXES; ++bx) {
+      tma_load_3d(sk + bx * DT_BOX_BYTES, &map_k, bar, bx * 64, kvh * BN_PAGE, page);
+      tma_load_3d(sv + bx * DT_BOX_BYTES, &map_v, bar, bx * 64, kvh * BN_PAGE, page);
     }
   };
-#pragma unroll
-  for (int st = 0; st < DT_STAGES; ++st) {  // the whole ring is filled at once
-    if (st < n_pages) load_page(my_lo + st, st);
-    asm volatile("cp.async.commit_group;");
+  if (tid == 0) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+    for (int st = 0; st < DT_STAGES; ++st) mbar_init(full0 + 8 * st, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int st = 0; st < DT_STAGES; ++st)  // the whole ring is requested at once
+      if (st < n_pages) request_page(my_lo + st, st);
   }
+  // the rotation of this position, also before the wait: it depends on the position only
+  const int half = a.rotary_dims >> 1;
+  for (int i = tid; i < half; i += DT_THREADS) {
+    float sn, cs;
+    sincosf(dt_angle(pos, i, a.theta_scale), &sn, &cs);
+    cs_tab[2 * i] = cs;
+    cs_tab[2 * i + 1] = sn;
+  }
+  pdl_wait();  // the kernel before this one has completed: the q|k|v rows are there
+  __syncthreads();
 
   // ---- queries of this head group: rotate, round to bfloat16, place as rows of the 16-row tile
   const __nv_bfloat16* qrow = a.qkv + (size_t)b * a.q_stride;
-  const int half = a.rotary_dims >> 1;
   auto q_at = [&](int g, int d) -> __nv_bfloat16* {
     return reinterpret_cast<__nv_bfloat16*>(q_tile + dt_off<HD>(g, d >> 3)) + (d & 7);
   };
@@ -158,8 +180,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   }
   for (int p = tid; p < G * half; p += DT_THREADS) {
     int g = p / half, i = p - g * half;
-    float sn, cs;
-    sincosf(dt_angle(pos, i, a.theta_scale), &sn, &cs);
+    const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
     const __nv_bfloat16* hd = qrow + (size_t)(h0 + g) * head_dim;
     float x = __bfloat162float(hd[i]), y = __bfloat162float(hd[i + half]);
     *q_at(g, i) = __float2bfloat16_rn(x * cs - y * sn);
@@ -178,8 +199,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
     const __nv_bfloat16* kraw = qrow + a.k_off + (size_t)kvh * head_dim;
     const __nv_bfloat16* vraw = qrow + a.v_off + (size_t)kvh * head_dim;
     for (int i = tid; i < half; i += DT_THREADS) {
-      float sn, cs;
-      sincosf(dt_angle(pos, i, a.theta_scale), &sn, &cs);
+      const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
       float x = __bfloat162float(kraw[i]), y = __bfloat162float(kraw[i + half]);
       __nv_bfloat16 k0 = __float2bfloat16_rn(x * cs - y * sn), k1 = __float2bfloat16_rn(x * sn + y * cs);
       a.k_cache[off + i] = k0;
@@ -210,29 +230,32 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
   // Q as MMA operand fragments, kept in registers when the head is small enough
   constexpr bool Q_IN_REGS = HD <= 128;
   unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
+  bool failed = false;
   for (int i = 0; i < n_pages; ++i) {
-    // groups committed so far: the ring (DT_STAGES) plus one per earlier iteration but the first
-    if (i == 0) asm volatile("cp.async.wait_group %0;" ::"n"(DT_STAGES - 1));
-    else asm volatile("cp.async.wait_group %0;" ::"n"(DT_STAGES - 2));
-    __syncthreads();  // page i has landed for everyone; the stage of page i-1 is free; q and new_kv are written
-    if (i >= 1) {
-      if (i - 1 + DT_STAGES < n_pages) load_page(my_lo + i - 1 + DT_STAGES, (i - 1) % DT_STAGES);
-      asm volatile("cp.async.commit_group;");
-    }
+    const int stage = i % DT_STAGES;
+    const bool arrived = mbar_wait(full0 + 8 * stage, (unsigned)(i / DT_STAGES) & 1u, a.status, DT_ERR_PAGE_WAIT);
+    // page i has landed for everyone; the stage of page i-1 is free; q and new_kv are written
+    if (__syncthreads_or(arrived ? 0 : 1)) { failed = true; break; }
+    if (tid == 0 && i >= 1 && i - 1 + DT_STAGES < n_pages) request_page(my_lo + i - 1 + DT_STAGES, (i - 1) % DT_STAGES);
     if (Q_IN_REGS && i == 0) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
         dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
     }
     const int page_idx = my_lo + i;
-    const unsigned sk = s_st + (i % DT_STAGES) * STAGE_BYTES, sv = sk + PAGE_BYTES;
+    const unsigned sk = s_st + stage * STAGE_BYTES, sv = sk + PAGE_BYTES;
     if (has_new && page_idx == p_hi) {
-      // put the new token's row into the stage (the copies above left it out)
-      unsigned char* kt = stages + (i % DT_STAGES) * STAGE_BYTES;
+      // put the new token's row into the stage (the page came with what the cache held there) and
+      // clear the value rows behind it: their weights are zero, but zero times anything must be zero
+      unsigned char* kt = stages + stage * STAGE_BYTES;
       for (int c = tid; c < 2 * CHUNKS; c += DT_THREADS) {
         int which = c / CHUNKS, cc = c - which * CHUNKS;
-        *reinterpret_cast<uint4*>(kt + which * PAGE_BYTES + dt_off<HD>(new_row, cc)) =
+        *reinterpret_cast<uint4*>(kt + which * PAGE_BYTES + dt_koff(new_row, cc)) =
             *reinterpret_cast<const uint4*>(new_kv + which * HD + cc * 8);
+      }
+      for (int c = tid; c < (BN_PAGE - 1 - new_row) * CHUNKS; c += DT_THREADS) {
+        int r = new_row + 1 + c / CHUNKS, cc = c % CHUNKS;
+        *reinterpret_cast<uint4*>(kt + PAGE_BYTES + dt_koff(r, cc)) = make_uint4(0u, 0u, 0u, 0u);
       }
       __syncthreads();
     }
@@ -248,7 +271,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
       } else {
         dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
       }
-      dt_ldsm_x4(sk + dt_off<HD>(krow0 + (mi >> 1) * 8 + r8, ks * 2 + (mi & 1)), b0, b1, b2, b3);
+      dt_ldsm_x4(sk + dt_koff(krow0 + (mi >> 1) * 8 + r8, ks * 2 + (mi & 1)), b0, b1, b2, b3);
       dt_mma(s[0], a0, a1, a2, a3, b0, b1);
       dt_mma(s[1], a0, a1, a2, a3, b2, b3);
     }
@@ -299,13 +322,19 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
 #pragma unroll
       for (int j = 0; j < NT_O; j += 2) {
         unsigned b0, b1, b2, b3;
-        dt_ldsm_x4_trans(sv + dt_off<HD>(krow0 + (mi & 1) * 8 + r8, j + (mi >> 1)), b0, b1, b2, b3);
+        dt_ldsm_x4_trans(sv + dt_koff(krow0 + (mi & 1) * 8 + r8, j + (mi >> 1)), b0, b1, b2, b3);
         dt_mma(o[j], a0, a1, a2, a3, b0, b1);
         dt_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
       }
     }
   }
-  asm volatile("cp.async.wait_group 0;");
+  if (failed) {
+    // a page never arrived: loads that were requested may still be landing in this block's shared
+    // memory, so give them a bounded time and leave without a result (the status word says so)
+    unsigned long long t0 = global_timer();
+    while (global_timer() - t0 < 200000ull) __nanosleep(1000);
+    return;
+  }
   __syncthreads();  // every warp is done with the stages: they now hold the warps' outputs
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -319,7 +348,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
       float2 v = make_float2(o[j][2 * e], o[j][2 * e + 1]);
-      *reinterpret_cast<float2*>(o_part + ((size_t)(warp * DT_ROWS + row)) * HD + j * 8 + 2 * t4) = v;
+      *reinterpret_cast<float2*>(o_part + ((size_t)(warp * DT_ROWS + row)) * OSTRIDE + j * 8 + 2 * t4) = v;
     }
   }
   __syncthreads();
@@ -343,7 +372,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
     float m = ml_fin[g * 2], acc = 0.f;
     for (int w = 0; w < 4; ++w) {
       float mw = ml_part[(w * DT_ROWS + g) * 2];
-      if (mw != -INFINITY) acc += exp2f(mw - m) * o_part[(size_t)(w * DT_ROWS + g) * HD + d];
+      if (mw != -INFINITY) acc += exp2f(mw - m) * o_part[(size_t)(w * DT_ROWS + g) * OSTRIDE + d];
     }
     if (alone)  // the only split of this sequence: normalise and store, no partials
       a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(acc / ml_fin[g * 2 + 1]);
@@ -390,9 +419,9 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tc_kernel(DtArgs 
 }
 
 template <int HD, int DT_STAGES>
-static int launch_dt2(const DtArgs& a, dim3 grid, cudaStream_t stream) {
-  size_t smem = (size_t)DT_ROWS * HD * 2 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + 2 * HD * 2 +
-                (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float);
+static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
+  size_t smem = 1024 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + (size_t)DT_ROWS * HD * 2 + 2 * HD * 2 +
+                (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float) + DT_STAGES * 8 + HD * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<HD, DT_STAGES>,
@@ -400,15 +429,15 @@ static int launch_dt2(const DtArgs& a, dim3 grid, cudaStream_t stream) {
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
-  BN_LAUNCH((attention_decode_tc_kernel<HD, DT_STAGES>), grid, DT_THREADS, smem, stream, a);
+  BN_LAUNCH((attention_decode_tc_kernel<HD, DT_STAGES>), grid, DT_THREADS, smem, stream, mk, mv, a);
   return BN_OK;
 }
 // Short runs (at most two pages per block) take the two-stage ring: less shared memory, more
 // blocks per SM, and both pages are requested at once anyway.
 template <int HD>
-static int launch_dt(const DtArgs& a, dim3 grid, cudaStream_t stream) {
-  if (a.pages_per_block <= 2) return launch_dt2<HD, 2>(a, grid, stream);
-  return launch_dt2<HD, 3>(a, grid, stream);
+static int launch_dt(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
+  if (a.pages_per_block <= 2) return launch_dt2<HD, 2>(mk, mv, a, grid, stream);
+  return launch_dt2<HD, 3>(mk, mv, a, grid, stream);
 }
 
 // qkv: [n_seqs, q_stride] bfloat16 rows with the raw query heads first, the key heads at element
@@ -418,15 +447,19 @@ static int launch_dt(const DtArgs& a, dim3 grid, cudaStream_t stream) {
 // a sequence, so n_splits * pages_per_block * 64 must cover the longest sequence.  part_o / part_ml:
 // scratch of n_seqs * n_heads * n_splits * head_dim and n_seqs * n_heads * n_splits * 2 floats (unused
 // when n_splits is 1); tickets: n_seqs * n_kv_heads * ceil(group / 16) ints, zero before and after.
+// The caches are [n_cache_pages, n_kv_heads, 64, head_dim], contiguous and 16-byte aligned.  status:
+// one int on the device, left as it is unless a page load never completed (then 4, and the output
+// of that launch is not valid).
 extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, int v_off, void* out, int out_stride,
                                       int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                       int rotary_dims, float theta_scale, const int* tok_pos, const int* slots,
                                       const int* page_table, int pt_stride, void* k_cache, void* v_cache,
-                                      float* part_o, float* part_ml, int n_splits, int pages_per_block, int* tickets,
+                                      int n_cache_pages, int* status, float* part_o, float* part_ml, int n_splits, int pages_per_block, int* tickets,
                                       int n_tickets, cudaStream_t stream) {
   if (n_seqs <= 0) return BN_OK;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || n_splits <= 0 ||
-      pages_per_block <= 0 || window < 0 || !part_o || !part_ml || !tickets || rotary_dims < 0 ||
+      pages_per_block <= 0 || window < 0 || !part_o || !part_ml || !tickets || !status || n_cache_pages <= 0 ||
+      (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) || rotary_dims < 0 ||
       rotary_dims > head_dim || (rotary_dims & 1))
     return BN_ERR_BAD_ARG;
   int group = n_heads / n_kv_heads;
@@ -440,9 +473,14 @@ extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, 
   a.scale_log2e = scale * 1.4426950408889634f; a.window = window; a.rotary_dims = rotary_dims;
   a.theta_scale = theta_scale; a.tok_pos = tok_pos; a.slots = slots; a.page_table = page_table; a.pt_stride = pt_stride;
   a.k_cache = (__nv_bfloat16*)k_cache; a.v_cache = (__nv_bfloat16*)v_cache; a.part_o = part_o; a.part_ml = part_ml;
+  a.status = status;
   a.pages_per_block = pages_per_block; a.tickets = tickets; a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
   dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits);
-  if (head_dim <= 64) return launch_dt<64>(a, grid, stream);
-  if (head_dim <= 128) return launch_dt<128>(a, grid, stream);
-  return launch_dt<256>(a, grid, stream);
+  CUtensorMap mk, mv;
+  if (!tma_map_bf16_pages(&mk, k_cache, n_cache_pages, (unsigned long long)n_kv_heads * BN_PAGE, head_dim, BN_PAGE) ||
+      !tma_map_bf16_pages(&mv, v_cache, n_cache_pages, (unsigned long long)n_kv_heads * BN_PAGE, head_dim, BN_PAGE))
+    return BN_ERR_BAD_ARG;
+  if (head_dim <= 64) return launch_dt<64>(mk, mv, a, grid, stream);
+  if (head_dim <= 128) return launch_dt<128>(mk, mv, a, grid, stream);
+  return launch_dt<256>(mk, mv, a, grid, stream);
 }

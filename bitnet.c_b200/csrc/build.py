@@ -4,7 +4,7 @@ Each ``.cu`` file is one kernel family and becomes one shared library with
 ``extern "C"`` entry points, loaded through ``ctypes``.  A family is compiled the
 first time something asks for it (or all at once by ``build_all``); a model asks
 only for the families its parts use.  Libraries are kept beside the sources in
-``_build/`` under a name that carries a hash of the source, the shared header and
+``_build/`` under a name that carries a hash of the source, the headers of this folder and
 the compiler flags, so an edited source is recompiled and an old library is never
 picked up.  If that folder cannot be written, a per-user folder under the system's
 temporary directory is used instead.
@@ -92,14 +92,10 @@ def build_dir() -> str:
 
 def _digest(family: str) -> str:
     h = hashlib.sha256()
-    for fn in (SOURCES[family], "common.cuh"):
+    headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith((".cuh", ".h")))
+    for fn in [SOURCES[family]] + headers:
         with open(os.path.join(_HERE, fn), "rb") as f:
             h.update(f.read())
-    for ext in (".cuh", ".h"):
-        extra = os.path.join(_HERE, SOURCES[family].replace(".cu", ext))
-        if os.path.isfile(extra):
-            with open(extra, "rb") as f:
-                h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()[:12]
 

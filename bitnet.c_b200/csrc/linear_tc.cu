@@ -33,13 +33,11 @@
 //
 // Every wait on an mbarrier is bounded in time; when a wait gives up the block records a code
 // in *status, still takes part in the cluster barriers, lets its loads drain for a bounded time,
-// frees its tensor memory and returns.
+// frees its tensor memory and returns (tma.cuh).
 //
 // Reference for the operation: y = W x with float32 accumulation (src/quant/bf16_scalar.c:4-21);
 // the reference's CUDA backend reaches tensor cores only through cuBLAS (src/gpu_cuda.cu:11850-11879).
-#include "common.cuh"
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include "tma.cuh"
 
 #define TC_BM 128      // weight rows per tile (UMMA M)
 #define TC_BK 64       // k per stage: 128 bytes of bfloat16, one swizzle row
@@ -48,7 +46,6 @@
 // kernel's blocks are finishing (programmatic dependent launch).
 #define TC_STAGES_FOR(MP) ((MP) == 16 ? 6 : ((MP) == 32 ? 5 : 4))
 #define TC_THREADS 192
-#define TC_WAIT_NS 2000000000ull  // two seconds
 
 #define TC_ERR_FULL_WAIT 1
 #define TC_ERR_EMPTY_WAIT 2
@@ -65,50 +62,6 @@ struct TcArgs {
   unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long global_timer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false (and *status set) when the phase did not complete within TC_WAIT_NS.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = global_timer();
-  while (!mbar_try_wait(bar, parity)) {
-    if (global_timer() - t0 > TC_WAIT_NS) {
-      atomicExch(status, code);
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
 // start address >> 4; leading byte offset 1 (unused for swizzled K-major); stride byte offset
 // 1024 >> 4 between groups of 8 rows; descriptor version 1; layout type 2 = SWIZZLE_128B.
@@ -213,8 +166,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (tid == 0) {
     s_failed = 0;
     s_acc_ok = 0;
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    tma_prefetch_map(&map_w);
+    tma_prefetch_map(&map_x);
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
@@ -384,32 +337,6 @@ extern "C" int bn_linear_tc_trace_read(unsigned long long* host, int n) {
   return cudaMemcpy(host, g_trace, (size_t)n * 64, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
 
-static PFN_cuTensorMapEncodeTiled get_encode() {
-  static PFN_cuTensorMapEncodeTiled fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (PFN_cuTensorMapEncodeTiled)p;
-  }
-  return fn;
-}
-
-// A [rows, K] bfloat16 row-major matrix, loaded in boxes of box_rows x 64 with 128-byte swizzle;
-// rows and columns outside the matrix read as zero.
-static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-  PFN_cuTensorMapEncodeTiled enc = get_encode();
-  if (!enc) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -475,7 +402,7 @@ extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dty
   }
   if (cluster > k_blocks) cluster = k_blocks;
   CUtensorMap mw, mx;
-  if (!make_map(&mw, w, N, K, TC_BM) || !make_map(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
+  if (!tma_map_bf16_rows(&mw, w, N, K, TC_BM) || !tma_map_bf16_rows(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
   TcArgs a;
   a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
   a.k_blocks = k_blocks; a.status = status;

@@ -306,7 +306,8 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         _ptr(qkv), c_int(qkv.shape[1]), c_int(k_off), c_int(v_off), _ptr(out), c_int(out.shape[1]), c_int(n_seqs),
         c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(rotary_dims),
         c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
-        _ptr(v_cache), _ptr(part_o), _ptr(part_ml), c_int(n_splits), c_int(pages_per_block), _ptr(counters),
+        _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(tc_status(qkv.device)), _ptr(part_o), _ptr(part_ml), c_int(n_splits),
+        c_int(pages_per_block), _ptr(counters),
         c_int(counters.numel()), _stream()), "attention_decode_fused")
     return out
 
@@ -351,7 +352,8 @@ _tc_status = {}
 
 
 def tc_status(device) -> torch.Tensor:
-    """One int per device that the tcgen05 product sets when a wait inside it gave up (0 = fine)."""
+    """One int per device that a TMA-fed kernel (the tcgen05 product, the tensor-core decode
+    attention) sets when a wait inside it gave up (0 = fine)."""
     key = torch.device(device).index or 0
     got = _tc_status.get(key)
     if got is None:
@@ -360,13 +362,15 @@ def tc_status(device) -> torch.Tensor:
 
 
 def check_tc_status(device) -> None:
-    """Raise if a tcgen05 product on ``device`` reported a wait that gave up (synchronises)."""
+    """Raise if a TMA-fed kernel on ``device`` reported a wait that gave up (synchronises)."""
     code = int(tc_status(device).item())
     if code:
         tc_status(device).zero_()
-        what = {1: "a stage never filled (TMA load)", 2: "a stage was never released (MMA commit)",
-                3: "the accumulator never completed"}.get(code, f"code {code}")
-        raise KernelError(f"linear_tc: {what}; the result of that product is not valid")
+        _split_scratch(device)[1].zero_()  # tickets of the launch that gave up may be left over
+        what = {1: "linear_tc: a stage never filled (TMA load)", 2: "linear_tc: a stage was never released (MMA commit)",
+                3: "linear_tc: the accumulator never completed",
+                4: "attention_decode_tc: a cache page never arrived (TMA load)"}.get(code, f"code {code}")
+        raise KernelError(f"{what}; the result of that launch is not valid")
 
 
 def linear_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,

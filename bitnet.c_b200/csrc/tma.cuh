@@ -1,0 +1,110 @@
+// Tensor-memory-accelerator loads and the mbarriers they complete on, shared by the kernels that
+// stream tiles from global memory (linear_tc.cu, attention_decode_tc.cu).
+//
+// Every wait is bounded in time: a wait that gives up records a code in a status word of the
+// caller and returns false, so that the kernel can drain and return instead of spinning.
+#pragma once
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#define TMA_WAIT_NS 2000000000ull  // two seconds
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and *status set to code) when the phase did not complete within TMA_WAIT_NS.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = global_timer();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_timer() - t0 > TMA_WAIT_NS) {
+      atomicExch(status, code);
+      return false;
+    }
+  }
+  return true;
+}
+// One box of a two-dimensional tensor map into shared memory; c0 is the coordinate along the
+// contiguous dimension (c0 x element size must be a multiple of 16 bytes), c1 the row.
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+static PFN_cuTensorMapEncodeTiled tma_encoder() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled)p;
+  }
+  return fn;
+}
+
+// A [rows, cols] bfloat16 row-major matrix (row stride `cols` elements, a multiple of 8; base
+// 16-byte aligned), loaded in boxes of box_rows x 64 elements with 128-byte swizzle: in shared
+// memory a box is box_rows rows of 128 bytes, and the 16-byte chunk c of row r lies at chunk
+// c ^ (r & 7) (the box must start on a 1024-byte boundary).  Rows and columns outside the matrix
+// read as zero.
+static bool tma_map_bf16_rows(CUtensorMap* map, const void* ptr, unsigned long long rows, unsigned long long cols,
+                              int box_rows) {
+  PFN_cuTensorMapEncodeTiled enc = tma_encoder();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// A paged bfloat16 tensor [pages, rows_per_page, cols] (contiguous; cols a multiple of 8; base
+// 16-byte aligned), loaded in boxes of box_rows x 64 elements of one page with 128-byte swizzle
+// (layout in shared memory as for tma_map_bf16_rows).  Coordinates: (column, row in page, page).
+static bool tma_map_bf16_pages(CUtensorMap* map, const void* ptr, unsigned long long pages,
+                               unsigned long long rows_per_page, unsigned long long cols, int box_rows) {
+  PFN_cuTensorMapEncodeTiled enc = tma_encoder();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows_per_page, (cuuint64_t)pages};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows_per_page * cols * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}

@@ -157,6 +157,13 @@ class Model:
                      self.device, max_seqs=max_seqs, allocate=allocate)
 
     # ---- the step -------------------------------------------------------------------------
+    def check_kernels(self) -> None:
+        """Raise if a kernel with bounded waits reported that a wait gave up since the last call
+        (the results of that launch are not valid).  Synchronises with the device."""
+        if self.device is not None and self.device.type == "cuda":
+            from ..csrc import ops
+            ops.check_tc_status(self.device)
+
     def check_step(self, cache: Cache, seqs: Sequence[SeqStep]) -> List[int]:
         if not seqs:
             raise StepError("a step needs at least one sequence")

@@ -24,6 +24,15 @@ class ModelEngine(Engine):
         self.use_graphs = use_graphs and model.graph_safe()
         self.runners = {}
         self.pool = None
+        self._steps_unchecked = 0
+
+    def _check_kernels(self, every: int = 1) -> None:
+        """Kernels with bounded waits report a wait that gave up in a status word; look at it now
+        and then (every ``every`` steps) and when a sequence ends."""
+        self._steps_unchecked += 1
+        if self._steps_unchecked >= every:
+            self._steps_unchecked = 0
+            self.model.check_kernels()
 
     def free_tokens(self) -> int:
         return self.cache.tokens_free()
@@ -35,6 +44,7 @@ class ModelEngine(Engine):
         return self.cache.open()
 
     def close(self, slot: int) -> None:
+        self._check_kernels()
         self.cache.close(slot)
 
     def start_batch(self, first_index: int, prompts: Sequence[Sequence[int]]) -> None:
@@ -52,7 +62,9 @@ class ModelEngine(Engine):
             return self._decode_step(seqs, rows)
         logits = self.model.step(self.cache, seqs)
         out = self.sampler.sample(logits, self._index(rows, self.sampler.n_rows))
-        return out.cpu().tolist()
+        toks = out.cpu().tolist()
+        self._check_kernels()
+        return toks
 
     def _decode_step(self, seqs: Sequence[SeqStep], rows: Sequence[int]) -> List[int]:
         """One token per sequence through the recorded graph of this batch size."""
@@ -78,6 +90,7 @@ class ModelEngine(Engine):
             self.cache.advance(s.slot, 1)
         toks = out.cpu().tolist()
         runner.note_sampled(toks)
+        self._check_kernels(every=32)
         return toks
 
     def accept(self, tokens: Sequence[int], rows: Sequence[int]) -> None:

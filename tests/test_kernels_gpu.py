@@ -442,6 +442,10 @@ def test_attention_decode_fused(cuda_device, H, KV, hd, rd, lens, window):
             page = perm[slots[s], p // 64].item()
             k[page, :, p % 64] = ks[s][p].to(cuda_device)
             v[page, :, p % 64] = vs[s][p].to(cuda_device)
+        # whatever lies behind the new position in its page must not reach the result
+        page, row = perm[slots[s], (L - 1) // 64].item(), (L - 1) % 64
+        k[page, :, row + 1:] = float("nan")
+        v[page, :, row + 1:] = float("inf")
     k_before, v_before = k.clone(), v.clone()
     out = torch.empty(n_seq, H * hd, dtype=torch.bfloat16, device=cuda_device)
     scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(rd))) if rd else 1.0
@@ -467,4 +471,6 @@ def test_attention_decode_fused(cuda_device, H, KV, hd, rd, lens, window):
         qfull[L - 1] = rot[:H]
         ref = plain_llama.attention(qfull, kfull, vfull, hd ** -0.5, window)[L - 1]
         assert np.abs(got[s] - ref).max() < 2e-2, f"sequence {s}"
-    assert torch.equal(k[~touched], k_before[~touched]) and torch.equal(v[~touched], v_before[~touched])
+    bits = lambda t: t.view(torch.int16)
+    assert torch.equal(bits(k)[~touched], bits(k_before)[~touched]) and torch.equal(bits(v)[~touched], bits(v_before)[~touched])
+    ops.check_tc_status(cuda_device)
