@@ -233,7 +233,9 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   bool failed = false;
   for (int i = 0; i < n_pages; ++i) {
     const int stage = i % DT_STAGES;
-    const bool arrived = mbar_wait(full0 + 8 * stage, (unsigned)(i / DT_STAGES) & 1u, a.status, DT_ERR_PAGE_WAIT);
+    // one thread watches the stage's mbarrier, the others sleep at the block's barrier
+    bool arrived = true;
+    if (tid == 0) arrived = mbar_wait(full0 + 8 * stage, (unsigned)(i / DT_STAGES) & 1u, a.status, DT_ERR_PAGE_WAIT);
     // page i has landed for everyone; the stage of page i-1 is free; q and new_kv are written
     if (__syncthreads_or(arrived ? 0 : 1)) { failed = true; break; }
     if (tid == 0 && i >= 1 && i - 1 + DT_STAGES < n_pages) request_page(my_lo + i - 1 + DT_STAGES, (i - 1) % DT_STAGES);

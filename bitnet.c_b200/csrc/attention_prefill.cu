@@ -80,6 +80,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const int* pt = page_table + (size_t)slots[seq] * pt_stride;
   const int real_chunks = head_dim / 8;
   const int rows_here = min(PF_M, n_new - row0);
+  const int seq_last = pos0 + n_new - 1;  // the last position of this sequence that the cache holds
 
   // visible key range of this block
   const int q_first = pos0 + row0, q_last = pos0 + row0 + rows_here - 1;
@@ -100,9 +101,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     for (int p = tid; p < PF_N * CHUNKS; p += PF_THREADS) {
       int r = p / CHUNKS, c = p % CHUNKS;
       bool ok = c < real_chunks;
+      // value rows behind the sequence's last position are zero here, whatever the cache holds:
+      // their weights are zero, but zero times anything must be zero
+      bool okv = ok && tile * PF_N + r <= seq_last;
       size_t off = (size_t)r * head_dim + c * 8;
       pf_cp_async16(s_k + stage * TILE_BYTES + tile_off<HD>(r, c), ok ? kb + off : kb, ok);
-      pf_cp_async16(s_v + stage * TILE_BYTES + tile_off<HD>(r, c), ok ? vb + off : vb, ok);
+      pf_cp_async16(s_v + stage * TILE_BYTES + tile_off<HD>(r, c), okv ? vb + off : vb, okv);
     }
   };
   load_kv(tile_lo, 0);

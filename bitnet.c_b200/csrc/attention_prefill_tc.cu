@@ -1,0 +1,458 @@
+// Causal attention of many new tokens per sequence in bfloat16 (prefill) on the 5th-generation
+// tensor cores: scores and the weighted value sum are tcgen05.mma instructions with their
+// accumulators in tensor memory, operands arrive by TMA.
+//
+// One block takes 128 consecutive new tokens of one sequence and one query head and walks the
+// sequence's cache pages (64 positions of one key/value head, contiguous: one key tile) from the
+// first visible key to the last.  Per page j:
+//     S_j = Q K_j^T          M=128, N=64,  K=head size   -> tensor memory, two buffers
+//     P_j = exp2(S_j * scale * log2(e) - m)  in float32 by 128 threads, one query row each (the
+//                             row of the accumulator is the thread's own TMEM lane: no shuffles),
+//                             rounded to bfloat16 into shared memory (two buffers)
+//     O  += P_j V_j          M=128, N=head size, K=64    -> tensor memory
+// Roles of the 192 threads: warp 0 requests Q once and the pages through a ring of stages (TMA,
+// 128-byte swizzle); one thread of warp 1 issues the MMAs, S_{j+1} ahead of P_j V_j so that the
+// tensor pipe works on the next scores while the softmax warps handle the current ones; warps 2-5
+// do the softmax and the epilogue.  The running maximum m of a row is only raised when the new
+// maximum exceeds it by more than 8 (a factor 256, harmless in float32 and bfloat16); then the
+// row's O is rescaled in tensor memory.  Sums and maxima are float32; the result is O / sum.
+//
+// V is the MMA's B operand with the head dimension contiguous (MN-major); K, Q and P are K-major.
+// The new tokens' own keys and values must already be in the cache, so the same kernel serves
+// whole prompts, pieces of prompts and ragged batches (a table gives each block its sequence and
+// first row).  Head sizes in steps of 16 up to 128 run on the instantiation for 64 or 128: columns
+// past the head size read as zero (TMA fills what lies outside the tensor).  Value rows behind a
+// sequence's last position are cleared in shared memory, whatever the cache holds there.
+//
+// Every wait on an mbarrier is bounded in time; a wait that gives up sets a flag that ends all
+// other waits of the block, records a code in *status, and the block drains, frees its tensor
+// memory and returns without storing.
+//
+// Reference: per (head, token) scores over the cached keys 0..pos, scale 1/sqrt(head size),
+// softmax, weighted sum of values; the key/value head of query head h is h / (H / KV)
+// (src/transformer/batched_attn_scalar.c:97-169, flash variant :171-245).  The reference's CUDA
+// prefill attention is one block per (head, token) on CUDA cores (src/gpu_cuda.cu:9772).
+#include "tma.cuh"
+
+#define PT_ROWS 128      // query rows per block (UMMA M)
+#define PT_KEYS 64       // keys per tile = BN_PAGE
+#define PT_THREADS 192
+#define PT_RESCALE 8.0f  // raise a row's reference maximum only beyond this (log2 domain)
+#define PT_ERR_WAIT 5
+
+struct PtArgs {
+  __nv_bfloat16* out;
+  int out_stride;
+  int n_heads, n_kv_heads, head_dim;
+  float scale_log2e;
+  int window;
+  const int* tile_seq;
+  const int* tile_row0;
+  const int* seq_start;
+  const int* seq_pos0;
+  const int* slots;
+  const int* page_table;
+  int pt_stride;
+  int* status;
+};
+
+// K-major tile with rows of 128 bytes, 128-byte swizzled: start address >> 4; leading byte offset
+// unused (1); stride byte offset 1024 between groups of 8 rows; version 1; layout SWIZZLE_128B.
+__device__ __forceinline__ unsigned long long pt_desc_k(unsigned addr) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major tile (the contiguous dimension is N): 64 elements of N per 128-byte row, rows are
+// consecutive k; groups of 8 k-rows 1024 bytes apart (stride byte offset), the next 64 elements of
+// N one box (lbo bytes) further (leading byte offset).
+__device__ __forceinline__ unsigned long long pt_desc_mn(unsigned addr, unsigned lbo) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | ((unsigned long long)((lbo >> 4) & 0x3FFF) << 16) | (64ull << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void pt_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                       unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void pt_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void pt_tmem_ld32(unsigned addr, float* v) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 64 consecutive columns of this thread's TMEM lane; the wait is part of the same statement so that
+// nothing that uses the registers can be scheduled in front of it
+__device__ __forceinline__ void pt_tmem_ld64(unsigned addr, float* v) {
+  unsigned r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(addr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ float pt_ex2(float x) {  // 2^x, two units in the last place; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void pt_tmem_st32(unsigned addr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ unsigned pt_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+// Bounded wait that also ends when another thread of the block has given up.
+__device__ __forceinline__ bool pt_wait(unsigned bar, unsigned parity, volatile int* failed, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = global_timer();
+  for (;;) {
+    if (mbar_try_wait_for(bar, parity, TMA_SUSPEND_NS)) return true;
+    if (*failed) return false;
+    if (global_timer() - t0 > TMA_WAIT_NS) {
+      *failed = 1;
+      atomicExch(status, PT_ERR_WAIT);
+      return false;
+    }
+  }
+}
+
+template <int HD, int STAGES, int PBUFS>
+__global__ void __launch_bounds__(PT_THREADS)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, PtArgs a) {
+  pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  constexpr int BOXES = HD / 64;
+  constexpr int Q_BOX = PT_ROWS * 128;             // 16 KB: 128 rows x 64 dimensions
+  constexpr int KV_BOX = PT_KEYS * 128;            // 8 KB: 64 keys x 64 dimensions
+  constexpr int Q_BYTES = BOXES * Q_BOX;
+  constexpr int PAGE_BYTES = BOXES * KV_BOX;       // one page of keys (or values) of one head
+  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+  constexpr int P_BYTES = PT_ROWS * 128;           // 128 rows x 64 keys of bfloat16
+  constexpr unsigned TMEM_COLS = 256;              // S0 at 0, S1 at 64, O at 128
+  constexpr unsigned O_COL = 128;
+  // D float32, A and B bfloat16, M = 128; scores: N = 64, both operands K-major; output: N = HD, B MN-major
+  constexpr unsigned IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) | ((PT_ROWS >> 4) << 24);
+  constexpr unsigned IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((PT_ROWS >> 4) << 24);
+
+  // The block has no static shared memory, so the dynamic part starts at the (1024-byte aligned)
+  // base of the block's window: the swizzle is a function of the address.
+  unsigned char* q_smem = smem_raw;
+  unsigned char* kv_smem = q_smem + Q_BYTES;                  // STAGES x (keys page, values page)
+  unsigned char* p_smem = kv_smem + STAGES * STAGE_BYTES;     // PBUFS buffers
+  unsigned long long* bars = (unsigned long long*)(p_smem + PBUFS * P_BYTES);
+  // barriers: q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done
+  const unsigned bar0 = smem_u32(bars);
+  const unsigned q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = kv_full0 + 8 * STAGES, s_full0 = kv_empty0 + 8 * STAGES,
+                 s_empty0 = s_full0 + 16, p_full0 = s_empty0 + 16, p_empty0 = p_full0 + 16, pv_done = p_empty0 + 16;
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 10);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int blk = gridDim.x - 1 - blockIdx.x;  // later tiles of a sequence see more keys: start them first
+  const int seq = a.tile_seq[blk], row0 = a.tile_row0[blk], h = blockIdx.y;
+  const int head_dim = a.head_dim;
+  const int kvh = h / (a.n_heads / a.n_kv_heads);
+  const int start = a.seq_start[seq], n_new = a.seq_start[seq + 1] - start, pos0 = a.seq_pos0[seq];
+  const int* pt = a.page_table + (size_t)a.slots[seq] * a.pt_stride;
+  const int rows_here = min(PT_ROWS, n_new - row0);
+  // visible key range of this block
+  const int q_first = pos0 + row0, q_last = q_first + rows_here - 1;
+  const int lo_first = a.window > 0 ? max(0, q_first - a.window + 1) : 0;
+  const int tile_lo = lo_first / PT_KEYS, tile_hi = q_last / PT_KEYS;
+  const int n_tiles = tile_hi - tile_lo + 1;
+  const int seq_last = pos0 + n_new - 1;  // the last position of this sequence that the cache holds
+
+  if (tid == 0) {
+    *failed = 0;
+    if (smem_u32(smem_raw) & 1023u) {  // a misplaced window would make every tile wrong: give up at once
+      *failed = 1;
+      atomicExch(a.status, PT_ERR_WAIT);
+    }
+    tma_prefetch_map(&map_q);
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full0 + 8 * s, 1);
+      mbar_init(kv_empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full0 + 8 * b, 1);
+      mbar_init(s_empty0 + 8 * b, 4);  // one arrival per softmax warp
+      mbar_init(p_full0 + 8 * b, 4);
+      mbar_init(p_empty0 + 8 * b, 1);
+    }
+    mbar_init(pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  pdl_wait();  // q and this step's cache rows come from the kernels before this one
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int bx = 0; bx < BOXES; ++bx)
+        tma_load_2d(smem_u32(q_smem + bx * Q_BOX), &map_q, q_full, h * head_dim + bx * 64, start + row0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % STAGES, round = j / STAGES;
+        if (round > 0 && !pt_wait(kv_empty0 + 8 * s, (unsigned)(round - 1) & 1u, failed, a.status)) break;
+        const int page = pt[tile_lo + j];
+        const unsigned bar = kv_full0 + 8 * s, sk = smem_u32(kv_smem + s * STAGE_BYTES), sv = sk + PAGE_BYTES;
+        mbar_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+        for (int bx = 0; bx < BOXES; ++bx) {
+          tma_load_3d(sk + bx * KV_BOX, &map_k, bar, bx * 64, kvh * BN_PAGE, page);
+          tma_load_3d(sv + bx * KV_BOX, &map_v, bar, bx * 64, kvh * BN_PAGE, page);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = pt_wait(q_full, 0, failed, a.status);
+      const unsigned sq = smem_u32(q_smem), sp = smem_u32(p_smem);
+      for (int j = 0; ok && j <= n_tiles; ++j) {
+        if (j < n_tiles) {
+          // S_j = Q K_j^T into score buffer j & 1
+          const int s = j % STAGES, b = j & 1;
+          if (!pt_wait(kv_full0 + 8 * s, (unsigned)(j / STAGES) & 1u, failed, a.status)) { ok = false; break; }
+          if (j >= 2 && !pt_wait(s_empty0 + 8 * b, (unsigned)((j >> 1) - 1) & 1u, failed, a.status)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned sk = smem_u32(kv_smem + s * STAGE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks)
+            pt_mma(tmem_base + b * PT_KEYS, pt_desc_k(sq + (ks >> 2) * Q_BOX + (ks & 3) * 32),
+                   pt_desc_k(sk + (ks >> 2) * KV_BOX + (ks & 3) * 32), IDESC_S, ks ? 1u : 0u);
+          pt_commit(s_full0 + 8 * b);
+        }
+        if (j >= 1) {
+          // O += P_{j-1} V_{j-1}
+          const int i = j - 1, s = i % STAGES, b = i % PBUFS;
+          if (!pt_wait(p_full0 + 8 * b, (unsigned)(i / PBUFS) & 1u, failed, a.status)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned sv = smem_u32(kv_smem + s * STAGE_BYTES) + PAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < PT_KEYS / 16; ++kk)
+            pt_mma(tmem_base + O_COL, pt_desc_k(sp + b * P_BYTES + kk * 32), pt_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
+                   (i | kk) ? 1u : 0u);
+          pt_commit(kv_empty0 + 8 * s);   // the stage may be refilled
+          pt_commit(p_empty0 + 8 * b);    // the P buffer may be rewritten
+          pt_commit(pv_done);             // O holds the pages up to i
+        }
+      }
+    }
+  } else {
+    // ---- softmax and epilogue: thread <-> query row <-> TMEM lane
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
+    // rows past the sequence's tokens look like the first row so that they see at least one key
+    const int qpos = r < rows_here ? q_first + r : q_first;
+    const int qlo = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+    float m_ref = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j & 1, tile = tile_lo + j;
+      if (!pt_wait(s_full0 + 8 * b, (unsigned)(j >> 1) & 1u, failed, a.status)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float s[PT_KEYS];
+      pt_tmem_ld64(lane_addr + b * PT_KEYS, s);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty0 + 8 * b);  // the scores are in registers
+      // mask, then the maximum of the raw scores (the scale is positive); four chains, not one
+      const int k0 = tile * PT_KEYS;
+      if (!(k0 >= qlo && k0 + PT_KEYS - 1 <= qpos)) {
+#pragma unroll
+        for (int k = 0; k < PT_KEYS; ++k) {
+          const int kpos = k0 + k;
+          if (!(kpos >= qlo && kpos <= qpos)) s[k] = -INFINITY;
+        }
+      }
+      float mx[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+      for (int k = 4; k < PT_KEYS; ++k) mx[k & 3] = fmaxf(mx[k & 3], s[k]);
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2e;
+      bool need = false;
+      if (m_ref == -INFINITY) m_ref = m_tile;  // nothing accumulated for this row yet: O and the sum are zero
+      else need = m_tile > m_ref + PT_RESCALE;
+      if (__any_sync(0xffffffffu, need)) {
+        // O of the pages before this one must be complete before it is rescaled (j >= 1 here)
+        if (!pt_wait(pv_done, (unsigned)(j - 1) & 1u, failed, a.status)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float alpha = need ? exp2f(m_ref - m_tile) : 1.0f;
+        if (need) { m_ref = m_tile; l_run *= alpha; }
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          float o[32];
+          pt_tmem_ld32(lane_addr + O_COL + c, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          pt_tmem_st32(lane_addr + O_COL + c, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      // exponentials 2^(s * scale - m) and the row's sum (a row that has seen no key yet has only
+      // -inf scores, which give 0 whatever m is)
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < PT_KEYS; ++k) {
+        s[k] = pt_ex2(fmaf(s[k], a.scale_log2e, neg_m));
+        ls[k & 3] += s[k];
+      }
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      // P as bfloat16 into its buffer, once the product that read the buffer before is done
+      const int pb = j % PBUFS, use = j / PBUFS;
+      if (use >= 1 && !pt_wait(p_empty0 + 8 * pb, (unsigned)(use - 1) & 1u, failed, a.status)) { ok = false; break; }
+      unsigned char* prow = p_smem + pb * P_BYTES + r * 128;
+#pragma unroll
+      for (int c = 0; c < PT_KEYS / 8; ++c) {
+        const float* p = s + c * 8;
+        uint4 w = make_uint4(pt_pack(p[0], p[1]), pt_pack(p[2], p[3]), pt_pack(p[4], p[5]), pt_pack(p[6], p[7]));
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
+      }
+      if (tile * PT_KEYS + PT_KEYS - 1 > seq_last) {
+        // the page holds rows behind the sequence's last position: their weights are zero, but zero
+        // times anything must be zero, so clear those value rows (warp w takes every fourth row)
+        unsigned char* sv = kv_smem + (j % STAGES) * STAGE_BYTES + PAGE_BYTES;
+        const int first = max(0, seq_last + 1 - tile * PT_KEYS);
+        for (int e = (warp - 2) * 32 + lane; e < (PT_KEYS - first) * (HD / 8); e += 128) {
+          int row = first + e / (HD / 8), c = e % (HD / 8);
+          *reinterpret_cast<uint4*>(sv + (c >> 3) * KV_BOX + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and cleared rows) before the MMA reads them
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full0 + 8 * pb);
+    }
+    // ---- epilogue: O / sum -> out
+    if (ok && pt_wait(pv_done, (unsigned)(n_tiles - 1) & 1u, failed, a.status)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.0f / l_run;
+      __nv_bfloat16* orow = a.out + (size_t)(start + row0 + r) * a.out_stride + (size_t)h * head_dim;
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        float o[32];
+        pt_tmem_ld32(lane_addr + O_COL + c, o);
+        if (r < rows_here) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (c + g * 8 < head_dim) {  // head sizes are multiples of 16: groups of 8 are whole
+              uint4 w = make_uint4(pt_pack(o[g * 8] * inv, o[g * 8 + 1] * inv), pt_pack(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv),
+                                   pt_pack(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv), pt_pack(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv));
+              *reinterpret_cast<uint4*>(orow + c + g * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*failed) {
+    // a wait gave up: loads that were requested may still be landing in this block's shared memory
+    unsigned long long t0 = global_timer();
+    while (global_timer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <int HD, int STAGES, int PBUFS>
+static int launch_pt(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PtArgs& a, int n_tiles,
+                     cudaStream_t stream) {
+  size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)STAGES * 2 * PT_KEYS * HD * 2 + PBUFS * PT_ROWS * 128 +
+                (2 * STAGES + 10) * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, STAGES, PBUFS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+    configured = true;
+  }
+  dim3 grid(n_tiles, a.n_heads);
+  BN_LAUNCH((attention_prefill_tc_kernel<HD, STAGES, PBUFS>), grid, PT_THREADS, smem, stream, mq, mk, mv, a);
+  return BN_OK;
+}
+
+// q: [n_tokens, q_stride] bfloat16 (head h at element h*head_dim; 16-byte aligned, q_stride a
+// multiple of 8), out [n_tokens, out_stride] (out_stride a multiple of 8, 16-byte aligned).
+// tile_seq / tile_row0: for each block its sequence and the first of its 128 new-token rows;
+// seq_start [n_seqs+1]: first packed row of each sequence; seq_pos0: its length before the step.
+// The caches are [n_cache_pages, n_kv_heads, 64, head_dim], contiguous and 16-byte aligned, and
+// already hold the new tokens.  head_dim: a multiple of 16 up to 128.  status: one int on the
+// device, left as it is unless a wait inside the kernel gave up (then 5; nothing is stored by
+// that block).
+extern "C" int bn_attention_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, int n_tiles,
+                                       int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                       const int* tile_seq, const int* tile_row0, const int* seq_start,
+                                       const int* seq_pos0, const int* slots, const int* page_table, int pt_stride,
+                                       const void* k_cache, const void* v_cache, int n_cache_pages, int* status,
+                                       cudaStream_t stream) {
+  if (n_tiles <= 0) return BN_OK;
+  if (head_dim <= 0 || head_dim % 16 || head_dim > 128 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 ||
+      n_heads > 65535 || (q_stride % 8) || (out_stride % 8) || n_tokens <= 0 || n_cache_pages <= 0 || !status ||
+      (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15))
+    return BN_ERR_BAD_ARG;
+  CUtensorMap mq, mk, mv;
+  if (!tma_map_bf16_strided(&mq, q, (unsigned long long)n_tokens, (unsigned long long)n_heads * head_dim,
+                            (unsigned long long)q_stride, PT_ROWS) ||
+      !tma_map_bf16_pages(&mk, k_cache, n_cache_pages, (unsigned long long)n_kv_heads * BN_PAGE, head_dim, BN_PAGE) ||
+      !tma_map_bf16_pages(&mv, v_cache, n_cache_pages, (unsigned long long)n_kv_heads * BN_PAGE, head_dim, BN_PAGE))
+    return BN_ERR_BAD_ARG;
+  PtArgs a = {};
+  a.out = (__nv_bfloat16*)out; a.out_stride = out_stride; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads;
+  a.head_dim = head_dim; a.scale_log2e = scale * 1.4426950408889634f; a.window = window; a.tile_seq = tile_seq;
+  a.tile_row0 = tile_row0; a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.slots = slots; a.page_table = page_table;
+  a.pt_stride = pt_stride; a.status = status;
+  // shared memory per block: 96 KB and 112 KB, so that two blocks share an SM and one block's
+  // softmax overlaps the other's products
+  if (head_dim <= 64) return launch_pt<64, 3, 2>(mq, mk, mv, a, n_tiles, stream);
+  return launch_pt<128, 2, 1>(mq, mk, mv, a, n_tiles, stream);
+}

@@ -37,6 +37,7 @@ SOURCES: Dict[str, str] = {
     "attention_decode": "attention_decode.cu",
     "attention_decode_tc": "attention_decode_tc.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
     "linear": "linear.cu",
     "linear_mma": "linear_mma.cu",
     "linear_tc": "linear_tc.cu",

@@ -231,6 +231,39 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     return out
 
 
+USE_TCGEN05_ATTENTION = True  # prefill attention with head sizes up to 128 runs on tcgen05 (attention_prefill_tc.cu)
+
+
+def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                         scale: float, window: int, tile_seq: torch.Tensor, tile_row0: torch.Tensor,
+                         seq_start: torch.Tensor, seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                         k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
+    """bfloat16 causal attention of runs of new tokens on tcgen05 tensor cores with TMA-fed operands;
+    block i handles up to 128 new tokens of sequence tile_seq[i] from its row tile_row0[i] on.
+    Head sizes up to 128."""
+    if not q.is_cuda or q.dim() != 2 or q.stride(-1) != 1 or q.stride(0) != q_stride or q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc: q must be a bfloat16 CUDA matrix with unit inner stride")
+    _need(out, "out", torch.bfloat16, 2)
+    for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"),
+                  (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_prefill_tc: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+    if head_dim % 16 or head_dim > 128 or n_heads % n_kv_heads:
+        raise KernelError(f"attention_prefill_tc: head_dim={head_dim}, heads {n_heads}/{n_kv_heads} not supported")
+    if out.shape[1] != n_heads * head_dim or q_stride % 8 or n_heads * head_dim > q_stride or out.shape[0] < q.shape[0]:
+        raise KernelError("attention_prefill_tc: out or q_stride does not fit")
+    _check(_fn("attention_prefill_tc", "bn_attention_prefill_tc")(
+        _ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), c_int(out.shape[1]), c_int(tile_seq.shape[0]),
+        c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), _ptr(tile_seq), _ptr(tile_row0),
+        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
+        _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(tc_status(q.device)), _stream()), "attention_prefill_tc")
+    return out
+
+
 DECODE_CHUNK = 128  # positions per block of the decode attention; must equal DEC_CHUNK in attention_decode.cu
 
 
@@ -369,7 +402,8 @@ def check_tc_status(device) -> None:
         _split_scratch(device)[1].zero_()  # tickets of the launch that gave up may be left over
         what = {1: "linear_tc: a stage never filled (TMA load)", 2: "linear_tc: a stage was never released (MMA commit)",
                 3: "linear_tc: the accumulator never completed",
-                4: "attention_decode_tc: a cache page never arrived (TMA load)"}.get(code, f"code {code}")
+                4: "attention_decode_tc: a cache page never arrived (TMA load)",
+                5: "attention_prefill_tc: a wait inside the kernel gave up"}.get(code, f"code {code}")
         raise KernelError(f"{what}; the result of that launch is not valid")
 
 

@@ -34,17 +34,30 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// The same, but the thread may stay suspended up to `ns` nanoseconds while the phase is incomplete
+// (it is woken when the phase completes): a waiting thread then takes no issue slots from the
+// warps that compute.
+__device__ __forceinline__ bool mbar_try_wait_for(unsigned bar, unsigned parity, unsigned ns) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
+#define TMA_SUSPEND_NS 20000u
 // Bounded wait: false (and *status set to code) when the phase did not complete within TMA_WAIT_NS.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = global_timer();
-  while (!mbar_try_wait(bar, parity)) {
+  for (;;) {
+    if (mbar_try_wait_for(bar, parity, TMA_SUSPEND_NS)) return true;
     if (global_timer() - t0 > TMA_WAIT_NS) {
       atomicExch(status, code);
       return false;
     }
   }
-  return true;
 }
 // One box of a two-dimensional tensor map into shared memory; c0 is the coordinate along the
 // contiguous dimension (c0 x element size must be a multiple of 16 bytes), c1 the row.
@@ -74,12 +87,19 @@ static PFN_cuTensorMapEncodeTiled tma_encoder() {
 // memory a box is box_rows rows of 128 bytes, and the 16-byte chunk c of row r lies at chunk
 // c ^ (r & 7) (the box must start on a 1024-byte boundary).  Rows and columns outside the matrix
 // read as zero.
+// The same with rows `row_stride` elements apart (a multiple of 8, at least cols).
+static bool tma_map_bf16_strided(CUtensorMap* map, const void* ptr, unsigned long long rows, unsigned long long cols,
+                                 unsigned long long row_stride, int box_rows);
 static bool tma_map_bf16_rows(CUtensorMap* map, const void* ptr, unsigned long long rows, unsigned long long cols,
                               int box_rows) {
+  return tma_map_bf16_strided(map, ptr, rows, cols, cols, box_rows);
+}
+static bool tma_map_bf16_strided(CUtensorMap* map, const void* ptr, unsigned long long rows, unsigned long long cols,
+                                 unsigned long long row_stride, int box_rows) {
   PFN_cuTensorMapEncodeTiled enc = tma_encoder();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,

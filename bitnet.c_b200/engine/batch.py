@@ -17,6 +17,7 @@ import torch
 
 
 TILE_ROWS = 64  # new tokens per block of the prefill attention (PF_M in attention_prefill.cu)
+WIDE_TILE_ROWS = 128  # and of its tcgen05 form (PT_ROWS in attention_prefill_tc.cu)
 
 
 @dataclass
@@ -44,6 +45,8 @@ class StepContext:
     decode: bool  # every sequence brings exactly one token
     tile_seq: Optional[torch.Tensor] = None  # [n_tiles] int32: the sequence of each block of 64 new tokens
     tile_row0: Optional[torch.Tensor] = None  # [n_tiles] int32: its first row within the sequence's new tokens
+    wide_tile_seq: Optional[torch.Tensor] = None  # the same for blocks of 128 new tokens
+    wide_tile_row0: Optional[torch.Tensor] = None
     host_new: List[int] = field(default_factory=list)  # the same facts on the host, for parts that
     host_pos0: List[int] = field(default_factory=list)  # loop over sequences there
     host_slots: List[int] = field(default_factory=list)
@@ -57,7 +60,9 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
     n_rows = sum(len(s.want) for s in seqs)
     tiles = [(i, r) for i, c in enumerate(new) for r in range(0, c, TILE_ROWS)]
     n_tiles = len(tiles)
-    buf = np.empty(3 * T + 3 * n + 1 + n_rows + 2 * n_tiles, dtype=np.int32)
+    wide = [(i, r) for i, c in enumerate(new) for r in range(0, c, WIDE_TILE_ROWS)]
+    n_wide = len(wide)
+    buf = np.empty(3 * T + 3 * n + 1 + n_rows + 2 * n_tiles + 2 * n_wide, dtype=np.int32)
     tokens, tok_seq, tok_pos = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
     o = 3 * T
     slots, seq_start, seq_pos0 = buf[o:o + n], buf[o + n:o + 2 * n + 1], buf[o + 2 * n + 1:o + 3 * n + 1]
@@ -66,6 +71,9 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
     t0 = r0 + n_rows
     buf[t0:t0 + n_tiles] = [i for i, _r in tiles]
     buf[t0 + n_tiles:t0 + 2 * n_tiles] = [r for _i, r in tiles]
+    w0 = t0 + 2 * n_tiles
+    buf[w0:w0 + n_wide] = [i for i, _r in wide]
+    buf[w0 + n_wide:w0 + 2 * n_wide] = [r for _i, r in wide]
     at, r = 0, 0
     for i, s in enumerate(seqs):
         c = new[i]
@@ -84,6 +92,7 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
         slots=dev[o:o + n], seq_start=dev[o + n:o + 2 * n + 1], seq_pos0=dev[o + 2 * n + 1:o + 3 * n + 1],
         rows=dev[r0:r0 + n_rows] if n_rows else None, max_new=max(new),
         max_len=max(l + c for l, c in zip(lengths, new)), decode=all(c == 1 for c in new),
-        tile_seq=dev[t0:t0 + n_tiles], tile_row0=dev[t0 + n_tiles:t0 + 2 * n_tiles], host_new=new,
+        tile_seq=dev[t0:t0 + n_tiles], tile_row0=dev[t0 + n_tiles:t0 + 2 * n_tiles],
+        wide_tile_seq=dev[w0:w0 + n_wide], wide_tile_row0=dev[w0 + n_wide:w0 + 2 * n_wide], host_new=new,
         host_pos0=list(lengths),
         host_slots=[s.slot for s in seqs])

@@ -16,7 +16,8 @@ class Attention(Mixer):
     over the causal range (optionally the last ``window`` keys); output projection.
     Order and formulas: src/transformer/cpu.c:859-939, src/transformer/gqa_scalar.c:61-121."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "attention", "attention_decode", "attention_decode_tc", "attention_prefill", "rope")
+    kernels = ("linear", "linear_mma", "linear_tc", "attention", "attention_decode", "attention_decode_tc", "attention_prefill",
+               "attention_prefill_tc", "rope")
     graph_safe = True
 
     def __init__(self, spec, build):
@@ -81,8 +82,14 @@ class Attention(Mixer):
             # one token per sequence: row b is sequence b; split over the keys
             ops.attention_decode(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.softmax_scale,
                                  s.window, ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, ctx.max_len)
+        elif (qkv.dtype == torch.bfloat16 and ctx.wide_tile_seq is not None and qkv.shape[1] % 8 == 0
+              and s.head_dim <= 128 and ops.USE_TCGEN05_ATTENTION):
+            # runs of new tokens on tcgen05: 128 tokens of one sequence and one head per block
+            ops.attention_prefill_tc(qkv, qkv.shape[1], out, s.n_heads, s.n_kv_heads, s.head_dim, s.softmax_scale,
+                                     s.window, ctx.wide_tile_seq, ctx.wide_tile_row0, ctx.seq_start, ctx.seq_pos0,
+                                     ctx.slots, kv.page_table, kv.k, kv.v)
         elif qkv.dtype == torch.bfloat16 and ctx.tile_seq is not None and qkv.shape[1] % 8 == 0:
-            # runs of new tokens: tensor-core kernel, 64 tokens of one sequence per block
+            # larger heads: mma.sync kernel, 64 tokens of one sequence per block
             ops.attention_prefill(qkv, qkv.shape[1], out, s.n_heads, s.n_kv_heads, s.head_dim, s.softmax_scale,
                                   s.window, ctx.tile_seq, ctx.tile_row0, ctx.seq_start, ctx.seq_pos0, ctx.slots,
                                   kv.page_table, kv.k, kv.v)

@@ -317,10 +317,17 @@ def test_attention_decode(cuda_device, H, KV, hd, lens, window):
     (4, 4, 32, [150, 40], [150, 1], 17),
     (6, 3, 80, [513], [260], 100),
     (32, 8, 128, [700], [700], 0),
+    (5, 5, 64, [130, 300, 64], [128, 129, 64], 0),
+    (4, 1, 112, [400, 90], [399, 3], 130),
 ])
-def test_attention_prefill(cuda_device, H, KV, hd, lens, news, window):
-    """The tensor-core prefill kernel: ragged runs of new tokens after cached ones, scattered pages,
-    head sizes that are padded inside the kernel, windows, and a far key that must dominate."""
+@pytest.mark.parametrize("impl", ["mma", "tcgen05"])
+def test_attention_prefill(cuda_device, impl, H, KV, hd, lens, news, window):
+    """The tensor-core prefill kernels (mma.sync with 64-row blocks, tcgen05 with 128-row blocks):
+    ragged runs of new tokens after cached ones, scattered pages, head sizes that are padded inside
+    the kernel, windows, a far key that must dominate, a late key that raises a row's maximum by
+    far more than the rescaling threshold, and non-finite leftovers behind a sequence's end."""
+    if impl == "tcgen05" and hd > 128:
+        pytest.skip("the tcgen05 kernel takes head sizes up to 128")
     from bitnet_c_b200.engine import SeqStep, pack_step
     g = torch.Generator().manual_seed(16)
     n_seq, n_pages, per_seq = len(lens), 64, 16
@@ -331,20 +338,31 @@ def test_attention_prefill(cuda_device, H, KV, hd, lens, news, window):
     qs = [(torch.randn(n, H, hd, generator=g) * 0.5).to(torch.bfloat16) for n in news]
     if lens[0] > 2 and window == 0:
         ks[0][1, 0] = (qs[0][-1, 0].float() * 4).to(torch.bfloat16)
+    if lens[0] > 200:
+        ks[0][lens[0] - 3, 0] = (qs[0][-1, 0].float() * 9).to(torch.bfloat16)
     slots = list(range(n_seq))[::-1]
     for s, L in enumerate(lens):
         for p in range(L):
             page = perm[slots[s], p // 64].item()
             k[page, :, p % 64] = ks[s][p].to(cuda_device)
             v[page, :, p % 64] = vs[s][p].to(cuda_device)
+        if L % 64:  # whatever lies behind the sequence's end in its last page must not reach the result
+            page = perm[slots[s], (L - 1) // 64].item()
+            k[page, :, L % 64:] = float("nan")
+            v[page, :, L % 64:] = float("inf")
     T = sum(news)
     wide = torch.zeros(T, H * hd + 2 * KV * hd, dtype=torch.bfloat16, device=cuda_device)
     wide[:, : H * hd] = torch.cat([x.reshape(x.shape[0], H * hd) for x in qs]).to(cuda_device)
     ctx = pack_step([SeqStep(slots[i], [0] * news[i]) for i in range(n_seq)], [L - n for L, n in zip(lens, news)],
                     cuda_device)
     out = torch.full((T, H * hd), 7.0, dtype=torch.bfloat16, device=cuda_device)
-    ops.attention_prefill(wide, wide.shape[1], out, H, KV, hd, hd ** -0.5, window, ctx.tile_seq, ctx.tile_row0,
-                          ctx.seq_start, ctx.seq_pos0, ctx.slots, perm.to(cuda_device), k, v)
+    if impl == "mma":
+        ops.attention_prefill(wide, wide.shape[1], out, H, KV, hd, hd ** -0.5, window, ctx.tile_seq, ctx.tile_row0,
+                              ctx.seq_start, ctx.seq_pos0, ctx.slots, perm.to(cuda_device), k, v)
+    else:
+        ops.attention_prefill_tc(wide, wide.shape[1], out, H, KV, hd, hd ** -0.5, window, ctx.wide_tile_seq,
+                                 ctx.wide_tile_row0, ctx.seq_start, ctx.seq_pos0, ctx.slots, perm.to(cuda_device), k, v)
+        ops.check_tc_status(cuda_device)
     got = out.double().cpu().numpy().reshape(T, H, hd)
     at = 0
     for s, (L, n) in enumerate(zip(lens, news)):
