@@ -54,7 +54,9 @@ struct PtArgs {
   const int* page_table;
   int pt_stride;
   int* status;
+  unsigned long long* trace;  // debugging: timestamps of block (0, 0), or null
 };
+#define PT_TRACE_TILES 12  // per tile: 6 stamps of a softmax thread, 3 of the MMA thread
 
 // K-major tile with rows of 128 bytes, 128-byte swizzled: start address >> 4; leading byte offset
 // unused (1); stride byte offset 1024 between groups of 8 rows; version 1; layout SWIZZLE_128B.
@@ -128,6 +130,16 @@ __device__ __forceinline__ void pt_tmem_st32(unsigned addr, const float* v) {
         "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
+// One lane of the (converged) warp: the same one every time.
+__device__ __forceinline__ bool pt_elect_one() {
+  unsigned pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ unsigned pt_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -172,11 +184,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char* kv_smem = q_smem + Q_BYTES;                  // STAGES x (keys page, values page)
   unsigned char* p_smem = kv_smem + STAGES * STAGE_BYTES;     // PBUFS buffers
   unsigned long long* bars = (unsigned long long*)(p_smem + PBUFS * P_BYTES);
-  // barriers: q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done
+  // barriers: q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done
   const unsigned bar0 = smem_u32(bars);
-  const unsigned q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = kv_full0 + 8 * STAGES, s_full0 = kv_empty0 + 8 * STAGES,
+  const unsigned q_full = bar0, k_full0 = bar0 + 8, k_empty0 = k_full0 + 8 * STAGES, v_full0 = k_empty0 + 8 * STAGES,
+                 v_empty0 = v_full0 + 8 * STAGES, s_full0 = v_empty0 + 8 * STAGES,
                  s_empty0 = s_full0 + 16, p_full0 = s_empty0 + 16, p_empty0 = p_full0 + 16, pv_done = p_empty0 + 16;
-  unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 10);
+  unsigned* tmem_slot = (unsigned*)(bars + 4 * STAGES + 10);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,8 +218,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tma_prefetch_map(&map_v);
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(kv_full0 + 8 * s, 1);
-      mbar_init(kv_empty0 + 8 * s, 1);
+      mbar_init(k_full0 + 8 * s, 1);
+      mbar_init(k_empty0 + 8 * s, 1);
+      mbar_init(v_full0 + 8 * s, 1);
+      mbar_init(v_empty0 + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full0 + 8 * b, 1);
@@ -234,51 +249,83 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int bx = 0; bx < BOXES; ++bx)
         tma_load_2d(smem_u32(q_smem + bx * Q_BOX), &map_q, q_full, h * head_dim + bx * 64, start + row0);
-      for (int j = 0; j < n_tiles; ++j) {
+      // Keys and values have rings of their own: a key stage is free as soon as the scores that
+      // read it are done, a value stage only after the output product, one softmax later.  The
+      // order of the requests is the order in which the stages come free: K(t+1), then V(t).
+      auto request = [&](int j, bool values) -> bool {
         const int s = j % STAGES, round = j / STAGES;
-        if (round > 0 && !pt_wait(kv_empty0 + 8 * s, (unsigned)(round - 1) & 1u, failed, a.status)) break;
-        const int page = pt[tile_lo + j];
-        const unsigned bar = kv_full0 + 8 * s, sk = smem_u32(kv_smem + s * STAGE_BYTES), sv = sk + PAGE_BYTES;
-        mbar_expect_tx(bar, STAGE_BYTES);
+        const unsigned empty = (values ? v_empty0 : k_empty0) + 8 * s, bar = (values ? v_full0 : k_full0) + 8 * s;
+        const int page = __ldg(pt + tile_lo + j);  // asked for before the wait, needed after it
+        if (round > 0 && !pt_wait(empty, (unsigned)(round - 1) & 1u, failed, a.status)) return false;
+        const unsigned dst = smem_u32(kv_smem + s * STAGE_BYTES) + (values ? PAGE_BYTES : 0);
+        mbar_expect_tx(bar, PAGE_BYTES);
 #pragma unroll
-        for (int bx = 0; bx < BOXES; ++bx) {
-          tma_load_3d(sk + bx * KV_BOX, &map_k, bar, bx * 64, kvh * BN_PAGE, page);
-          tma_load_3d(sv + bx * KV_BOX, &map_v, bar, bx * 64, kvh * BN_PAGE, page);
-        }
+        for (int bx = 0; bx < BOXES; ++bx)
+          tma_load_3d(dst + bx * KV_BOX, values ? &map_v : &map_k, bar, bx * 64, kvh * BN_PAGE, page);
+        return true;
+      };
+      bool ok = request(0, false);
+      for (int t = 0; ok && t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) ok = request(t + 1, false);
+        if (ok) ok = request(t, true);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      bool ok = pt_wait(q_full, 0, failed, a.status);
-      const unsigned sq = smem_u32(q_smem), sp = smem_u32(p_smem);
-      for (int j = 0; ok && j <= n_tiles; ++j) {
-        if (j < n_tiles) {
-          // S_j = Q K_j^T into score buffer j & 1
-          const int s = j % STAGES, b = j & 1;
-          if (!pt_wait(kv_full0 + 8 * s, (unsigned)(j / STAGES) & 1u, failed, a.status)) { ok = false; break; }
-          if (j >= 2 && !pt_wait(s_empty0 + 8 * b, (unsigned)((j >> 1) - 1) & 1u, failed, a.status)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const unsigned sk = smem_u32(kv_smem + s * STAGE_BYTES);
+    // The whole warp walks the loop, so that addresses and descriptors are warp-uniform values;
+    // one elected lane issues the MMAs and commits.
+    const bool issuer = pt_elect_one();
+    const unsigned tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
+    bool ok = __all_sync(0xffffffffu, pt_wait(q_full, 0, failed, a.status));
+    const unsigned sq = smem_u32(q_smem), sp = smem_u32(p_smem);
+    const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && issuer;
+    for (int j = 0; ok && j <= n_tiles; ++j) {
+      if (j < n_tiles) {
+        // S_j = Q K_j^T into score buffer j & 1
+        const int s = j % STAGES, b = j & 1;
+        const bool trs = tracing && j < PT_TRACE_TILES;
+        ok = __all_sync(0xffffffffu, pt_wait(k_full0 + 8 * s, (unsigned)(j / STAGES) & 1u, failed, a.status));
+        if (!ok) break;
+        if (trs) a.trace[j * 12 + 9] = global_timer();
+        if (j >= 2) {
+          ok = __all_sync(0xffffffffu, pt_wait(s_empty0 + 8 * b, (unsigned)((j >> 1) - 1) & 1u, failed, a.status));
+          if (!ok) break;
+        }
+        if (trs) a.trace[j * 12 + 10] = global_timer();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned sk = smem_u32(kv_smem + s * STAGE_BYTES);
+        if (issuer) {
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks)
-            pt_mma(tmem_base + b * PT_KEYS, pt_desc_k(sq + (ks >> 2) * Q_BOX + (ks & 3) * 32),
+            pt_mma(tbase + b * PT_KEYS, pt_desc_k(sq + (ks >> 2) * Q_BOX + (ks & 3) * 32),
                    pt_desc_k(sk + (ks >> 2) * KV_BOX + (ks & 3) * 32), IDESC_S, ks ? 1u : 0u);
+          if (trs) a.trace[j * 12 + 11] = global_timer();
+          pt_commit(k_empty0 + 8 * s);  // the key stage may be refilled
           pt_commit(s_full0 + 8 * b);
+          if (trs) a.trace[j * 12 + 6] = global_timer();
         }
-        if (j >= 1) {
-          // O += P_{j-1} V_{j-1}
-          const int i = j - 1, s = i % STAGES, b = i % PBUFS;
-          if (!pt_wait(p_full0 + 8 * b, (unsigned)(i / PBUFS) & 1u, failed, a.status)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const unsigned sv = smem_u32(kv_smem + s * STAGE_BYTES) + PAGE_BYTES;
+        __syncwarp();
+      }
+      if (j >= 1) {
+        // O += P_{j-1} V_{j-1}
+        const int i = j - 1, s = i % STAGES, b = i % PBUFS;
+        ok = __all_sync(0xffffffffu, pt_wait(p_full0 + 8 * b, (unsigned)(i / PBUFS) & 1u, failed, a.status) &&
+                                         pt_wait(v_full0 + 8 * s, (unsigned)(i / STAGES) & 1u, failed, a.status));
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool tr = tracing && i < PT_TRACE_TILES;
+        if (tr) a.trace[i * 12 + 7] = global_timer();
+        const unsigned sv = smem_u32(kv_smem + s * STAGE_BYTES) + PAGE_BYTES;
+        if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < PT_KEYS / 16; ++kk)
-            pt_mma(tmem_base + O_COL, pt_desc_k(sp + b * P_BYTES + kk * 32), pt_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
+            pt_mma(tbase + O_COL, pt_desc_k(sp + b * P_BYTES + kk * 32), pt_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
                    (i | kk) ? 1u : 0u);
-          pt_commit(kv_empty0 + 8 * s);   // the stage may be refilled
+          pt_commit(v_empty0 + 8 * s);    // the value stage may be refilled
           pt_commit(p_empty0 + 8 * b);    // the P buffer may be rewritten
           pt_commit(pv_done);             // O holds the pages up to i
+          if (tr) a.trace[i * 12 + 8] = global_timer();
         }
+        __syncwarp();
       }
     }
   } else {
@@ -293,10 +340,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1, tile = tile_lo + j;
+      const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 64 && j < PT_TRACE_TILES;
+      if (tr) a.trace[j * 12 + 0] = global_timer();
       if (!pt_wait(s_full0 + 8 * b, (unsigned)(j >> 1) & 1u, failed, a.status)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (tr) a.trace[j * 12 + 1] = global_timer();
       float s[PT_KEYS];
       pt_tmem_ld64(lane_addr + b * PT_KEYS, s);
+      if (tr) a.trace[j * 12 + 2] = global_timer();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty0 + 8 * b);  // the scores are in registers
@@ -342,9 +393,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ls[k & 3] += s[k];
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      if (tr) a.trace[j * 12 + 3] = global_timer();
       // P as bfloat16 into its buffer, once the product that read the buffer before is done
       const int pb = j % PBUFS, use = j / PBUFS;
       if (use >= 1 && !pt_wait(p_empty0 + 8 * pb, (unsigned)(use - 1) & 1u, failed, a.status)) { ok = false; break; }
+      if (tr) a.trace[j * 12 + 4] = global_timer();
       unsigned char* prow = p_smem + pb * P_BYTES + r * 128;
 #pragma unroll
       for (int c = 0; c < PT_KEYS / 8; ++c) {
@@ -366,6 +419,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full0 + 8 * pb);
+      if (tr) a.trace[j * 12 + 5] = global_timer();
     }
     // ---- epilogue: O / sum -> out
     if (ok && pt_wait(pv_done, (unsigned)(n_tiles - 1) & 1u, failed, a.status)) {
@@ -404,11 +458,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
+// Debugging aid: bn_attention_prefill_tc_trace(1) makes the next launch record timestamps of block
+// (0, 0) (device buffer allocated here; not used on the product path).
+static unsigned long long* g_pt_trace = nullptr;
+static bool g_pt_trace_armed = false;
+extern "C" int bn_attention_prefill_tc_trace(int on) {
+  if (g_pt_trace) cudaFree(g_pt_trace);
+  g_pt_trace = nullptr; g_pt_trace_armed = false;
+  if (!on) return 0;
+  if (cudaMalloc(&g_pt_trace, PT_TRACE_TILES * 12 * 8) != cudaSuccess) return 1;
+  cudaMemset(g_pt_trace, 0, PT_TRACE_TILES * 12 * 8);
+  g_pt_trace_armed = true;
+  return 0;
+}
+extern "C" int bn_attention_prefill_tc_trace_read(unsigned long long* host) {
+  if (!g_pt_trace) return 1;
+  return cudaMemcpy(host, g_pt_trace, PT_TRACE_TILES * 12 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
+}
+
 template <int HD, int STAGES, int PBUFS>
 static int launch_pt(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PtArgs& a, int n_tiles,
                      cudaStream_t stream) {
   size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)STAGES * 2 * PT_KEYS * HD * 2 + PBUFS * PT_ROWS * 128 +
-                (2 * STAGES + 10) * 8 + 16;
+                (4 * STAGES + 10) * 8 + 16;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, STAGES, PBUFS>,
@@ -451,6 +523,8 @@ extern "C" int bn_attention_prefill_tc(const void* q, int q_stride, int n_tokens
   a.head_dim = head_dim; a.scale_log2e = scale * 1.4426950408889634f; a.window = window; a.tile_seq = tile_seq;
   a.tile_row0 = tile_row0; a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.slots = slots; a.page_table = page_table;
   a.pt_stride = pt_stride; a.status = status;
+  a.trace = nullptr;
+  if (g_pt_trace_armed) { a.trace = g_pt_trace; g_pt_trace_armed = false; }
   // shared memory per block: 96 KB and 112 KB, so that two blocks share an SM and one block's
   // softmax overlaps the other's products
   if (head_dim <= 64) return launch_pt<64, 3, 2>(mq, mk, mv, a, n_tiles, stream);
