@@ -297,6 +297,9 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_seqs: 
     return out
 
 
+_FORCE_SPLITS = 0  # experiments: a fixed number of blocks per sequence in attention_decode_fused
+
+
 def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch.Tensor, n_seqs: int, n_heads: int,
                            n_kv_heads: int, head_dim: int, scale: float, window: int, rotary_dims: int,
                            theta_scale: float, tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
@@ -330,6 +333,8 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         want_splits = 1
     else:
         want_splits = max(1, min(pages, (4 * N_SMS + blocks_per_split - 1) // blocks_per_split))
+    if _FORCE_SPLITS:
+        want_splits = max(1, min(pages, _FORCE_SPLITS))
     pages_per_block = (pages + want_splits - 1) // want_splits
     n_splits = (pages + pages_per_block - 1) // pages_per_block
     part_o = torch.empty((n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)

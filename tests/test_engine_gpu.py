@@ -10,7 +10,7 @@ import pytest
 import bitnet_c_b200 as bn
 from helpers import (TOL_F32, bf16_bound, collect_trace_output, compare, make_model_dir, plain_logits,
                      random_tokens, replay, steps_to_jsonl, trace_batches, trace_tail, trace_whole)
-from tiny_configs import TINY_A, TINY_B, TINY_C
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
@@ -18,6 +18,7 @@ CASES = {
     "a": (TINY_A, 11, [40, 64, 65, 128, 33, 1]),
     "b": (TINY_B, 22, [17, 1, 40, 200, 129, 256]),
     "c": (TINY_C, 33, [70, 300, 64, 513, 97]),
+    "d": (TINY_D, 44, [700, 130, 1, 260, 64, 500]),
 }
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

@@ -13,6 +13,7 @@ pytestmark = pytest.mark.gpu
     (1, 128, 64, 1), (8, 128, 256, 1), (16, 256, 512, 3), (3, 50, 72, 2), (17, 333, 4096, 0), (32, 1000, 200, 3),
     (33, 130, 264, 5), (64, 272, 2048, 0), (8, 6144, 4096, 0), (64, 4096, 1024, 7), (8, 1000, 14336, 8),
     (5, 128256, 128, 0), (64, 4096, 14336, 0), (40, 200, 4096, 6),
+    (8, 15360, 5120, 0), (64, 5120, 13824, 0), (8, 3072, 2048, 0), (9, 2048, 8192, 0),  # other models' layer sizes
 ])
 def test_linear_tc_store(cuda_device, M, N, K, blocks):
     """``blocks`` blocks of a cluster share each tile's inner dimension: 1 (none), every size up to 8
@@ -34,7 +35,8 @@ def test_linear_tc_store(cuda_device, M, N, K, blocks):
 
 
 @pytest.mark.parametrize("M,I,K,blocks", [(1, 64, 64, 1), (8, 176, 64, 1), (20, 200, 256, 3), (64, 256, 1024, 5),
-                                          (8, 14336, 4096, 0), (64, 64, 2048, 8)])
+                                          (8, 14336, 4096, 0), (64, 64, 2048, 8), (8, 13824, 5120, 0),
+                                          (64, 8192, 2048, 0)])
 def test_linear_tc_swiglu(cuda_device, M, I, K, blocks):
     g = torch.Generator().manual_seed(22)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
@@ -45,4 +47,9 @@ def test_linear_tc_swiglu(cuda_device, M, I, K, blocks):
     ref = a / (1 + torch.exp(-a)) * b
     y = ops.linear_tc(x, w, out_dtype=torch.float32, swiglu=True, cluster=blocks)
     ops.check_tc_status(cuda_device)
-    assert y.shape == (M, I) and (y.double() - ref).abs().max().item() < 2e-4 * max(1.0, K / 1024)
+    # float32 accumulation leaves an error d in each of the two products (d grows with the length of
+    # the sum); through silu(a) * b it reaches the result as at most d * (|silu'(a) b| + |silu(a)|), and
+    # silu' <= 1.1.  An absolute bound alone would ignore that a * b is of order 100 for long rows.
+    d = 2.5e-6 * max(1.0, K / 64)
+    bound = d * (1.1 * b.abs() + a.abs()) + 1e-6
+    assert y.shape == (M, I) and ((y.double() - ref).abs() <= bound).all()

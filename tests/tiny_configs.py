@@ -28,3 +28,13 @@ TINY_C = {
     "vocab_size": 331, "max_position_embeddings": 1024, "rope_theta": 50000.0,
     "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "hidden_act": "silu",
 }
+
+# A fourth one with the head size of the large models (128) and as many key/value heads as query
+# heads, for sequences of many cache pages.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 256, "intermediate_size": 344, "num_hidden_layers": 2,
+    "num_attention_heads": 2, "num_key_value_heads": 2, "head_dim": 128,
+    "vocab_size": 1000, "max_position_embeddings": 2048, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
+}
