@@ -29,6 +29,18 @@ LLAMA_8B = {
     "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256, "max_position_embeddings": 4096,
     "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
 }
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 2048,
+    "intermediate_size": 8192, "num_hidden_layers": 16, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256, "max_position_embeddings": 8192,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+LLAMA_13B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 5120,
+    "intermediate_size": 13824, "num_hidden_layers": 40, "num_attention_heads": 40,
+    "num_key_value_heads": 40, "head_dim": 128, "vocab_size": 32000, "max_position_embeddings": 4096,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
+}
 PROMPT_LEN = 512
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -207,6 +219,43 @@ def run_prefill(bn, model, cfg, warmup=3, iters=5):
     return times[len(times) // 2]
 
 
+def run_workload(name):
+    """The generation workloads of the two other size sets, through the Python entry point:
+    1b: 64 requests with prompts of 1 to 2,048 tokens (one ragged prefill step), 256 greedy tokens
+    each; 13b: 8 requests with prompts of 2,048 down to 1 tokens, 1,024 greedy tokens each."""
+    import torch
+    import bitnet_c_b200 as bn
+    from bitnet_c_b200.engine import Model
+    cfg = dict(LLAMA_1B if name == "1b" else LLAMA_13B)
+    g = torch.Generator().manual_seed(7)
+    if name == "1b":
+        lens = torch.randint(1, 2049, (64,), generator=g).tolist()
+        new = 256
+    else:
+        lens = [2048, 1024, 512, 256, 128, 64, 16, 1]
+        new = 1024
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
+    times = []
+    for _ in range(2):  # the first run compiles nothing but records the graphs' pools; the second is timed
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = bn.generate(model, prompts, max_new_tokens=new, temperature=0.0, stop_ids=[])
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    made = sum(len(c.tokens) for c in out)
+    print(json.dumps({"metric": f"generated tokens/s, {name} workload (prefill of {sum(lens)} prompt tokens included)",
+                      "value": round(made / times[-1], 1), "unit": "tokens/s", "seconds": round(times[-1], 3),
+                      "generated": made, "prompt_tokens": sum(lens), "requests": len(lens), "dtype": "bf16",
+                      "data": "synthetic", "impl": "ours",
+                      "config": {"model": f"llama-{name}-sizes-random", "layers": cfg["num_hidden_layers"],
+                                 "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                                 "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                                 "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                                 "seq_len": cfg["max_position_embeddings"], "new_tokens": new}}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -217,12 +266,15 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64 and the prefill (quick runs)")
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill and print its record (profiling)")
     ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
+    ap.add_argument("--workload", choices=["1b", "13b"], help="run the generation workload of another size set instead")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload:
+        return run_workload(args.workload)
     warmup = max(3, args.warmup)
 
     import torch
