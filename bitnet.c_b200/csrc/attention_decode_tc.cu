@@ -16,7 +16,10 @@
 // m16n8k16 MMAs, statistics in float32), so the loop needs no exchange between warps; at the end
 // the four are merged in shared memory.  With more than one split per sequence the merged result
 // is written as an unnormalised partial with maximum and sum, and the block that draws the last
-// ticket of its (sequence, head group) merges the splits and writes the output.  How many pages a
+// ticket of its (sequence, head group) merges the splits and writes the output; with at most eight
+// splits these are one thread-block cluster instead, every block keeps its result in its own
+// shared memory and, after the cluster's barrier, adds up a slice of the output read from all of
+// them through distributed shared memory (no global round trip, no ticket).  How many pages a
 // block walks is chosen by the host from the batch (few sequences: many splits; many sequences:
 // one block per sequence and head group, no partials at all).
 // Page borders are fixed in position, so a row's arithmetic depends on its own position and the
@@ -65,6 +68,18 @@ __device__ __forceinline__ unsigned dt_koff(int row, int chunk) {
   return (unsigned)((chunk >> 3) * DT_BOX_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 #define DT_ERR_PAGE_WAIT 4
+__device__ __forceinline__ void dt_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One float of block `rank`'s shared memory, at the address that `local_addr` has here.
+__device__ __forceinline__ float dt_ld_dsmem(unsigned local_addr, unsigned rank) {
+  unsigned remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 __device__ __forceinline__ float dt_angle(int pos, int i, float theta_scale) {
   float angle = (float)pos;
   for (int k = 0; k < i; ++k) angle *= theta_scale;
@@ -86,9 +101,11 @@ struct DtArgs {
   __nv_bfloat16* k_cache;
   __nv_bfloat16* v_cache;
   int* status;     // 0, or DT_ERR_PAGE_WAIT when a page never arrived
+  unsigned long long* trace;  // debugging: timestamps of blocks (0, 0, z), 16 per block, or null
   float* part_o;   // [n_seqs][n_heads][splits][head_dim]
   float* part_ml;  // [n_seqs][n_heads][splits][2]: maximum (in the scaled log2 domain) and sum
   int pages_per_block;
+  int cluster;     // 1: the splits of a sequence are one thread-block cluster and merge through distributed shared memory
   int* tickets;    // [n_seqs][gridDim.y], zero before and after
   __nv_bfloat16* out;
   int out_stride;
@@ -99,6 +116,8 @@ __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DtArgs a) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned long long* tr = (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? a.trace + 16 * blockIdx.z : nullptr;
+  if (tr) tr[0] = global_timer();
   constexpr int CHUNKS = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, BOXES = HD / 64;
   constexpr int PAGE_BYTES = BN_PAGE * HD * 2;       // one page of keys (or values) of one head
   constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
@@ -111,8 +130,10 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   float* ml_fin = ml_part + 4 * DT_ROWS * 2;                   // [16][2]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(ml_fin + DT_ROWS * 2);  // [DT_STAGES]
   float* cs_tab = reinterpret_cast<float*>(bars + DT_STAGES);  // [rotary_dims / 2][2]: cosine, sine of this position's angles
+  float* wsc = cs_tab + HD;                                    // [4 warps][16]: each warp's weight in the block's result
   float* o_part = reinterpret_cast<float*>(stages);            // [4 warps][16][OSTRIDE], after the loop
-  static_assert(4 * DT_ROWS * OSTRIDE * 4 <= DT_STAGES * STAGE_BYTES, "the warps' outputs reuse the stages");
+  float* o_fin = o_part + 4 * DT_ROWS * OSTRIDE;               // [16][HD]: the block's unnormalised result
+  static_assert((4 * DT_ROWS * OSTRIDE + DT_ROWS * HD) * 4 <= DT_STAGES * STAGE_BYTES, "the warps' outputs and the block's result reuse the stages");
   const unsigned s_q = smem_u32(q_tile), s_st = smem_u32(stages), full0 = smem_u32(bars);
   __shared__ int s_last;
 
@@ -130,8 +151,15 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const int p_lo = lo / BN_PAGE, p_hi = pos / BN_PAGE;
   const int my_lo = max(p_lo, (int)blockIdx.z * a.pages_per_block);
   const int my_hi = min(p_hi, (int)(blockIdx.z + 1) * a.pages_per_block - 1);
+  const int z_lo = p_lo / a.pages_per_block, z_hi = p_hi / a.pages_per_block;  // splits with a visible page
+  const bool alone = (z_lo == z_hi);
+  const bool clustered = a.cluster != 0 && !alone;  // the same for every block of the cluster
   if (my_lo > my_hi) {
     pdl_wait();  // no block of this grid ends before the grids in front of it have
+    if (clustered) {  // nothing to add, but the cluster's barriers need every block
+      dt_cluster_sync();
+      dt_cluster_sync();
+    }
     return;
   }
   const int n_pages = my_hi - my_lo + 1;
@@ -158,6 +186,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     for (int st = 0; st < DT_STAGES; ++st)  // the whole ring is requested at once
       if (st < n_pages) request_page(my_lo + st, st);
   }
+  if (tr) tr[1] = global_timer();
   // the rotation of this position, also before the wait: it depends on the position only
   const int half = a.rotary_dims >> 1;
   for (int i = tid; i < half; i += DT_THREADS) {
@@ -166,7 +195,9 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     cs_tab[2 * i] = cs;
     cs_tab[2 * i + 1] = sn;
   }
+  if (tr) tr[2] = global_timer();
   pdl_wait();  // the kernel before this one has completed: the q|k|v rows are there
+  if (tr) tr[3] = global_timer();
   __syncthreads();
 
   // ---- queries of this head group: rotate, round to bfloat16, place as rows of the 16-row tile
@@ -231,6 +262,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   constexpr bool Q_IN_REGS = HD <= 128;
   unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
   bool failed = false;
+  if (tr) tr[4] = global_timer();
   for (int i = 0; i < n_pages; ++i) {
     const int stage = i % DT_STAGES;
     // one thread watches the stage's mbarrier, the others sleep at the block's barrier
@@ -238,6 +270,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (tid == 0) arrived = mbar_wait(full0 + 8 * stage, (unsigned)(i / DT_STAGES) & 1u, a.status, DT_ERR_PAGE_WAIT);
     // page i has landed for everyone; the stage of page i-1 is free; q and new_kv are written
     if (__syncthreads_or(arrived ? 0 : 1)) { failed = true; break; }
+    if (tr && i < 2) tr[5 + i] = global_timer();
     if (tid == 0 && i >= 1 && i - 1 + DT_STAGES < n_pages) request_page(my_lo + i - 1 + DT_STAGES, (i - 1) % DT_STAGES);
     if (Q_IN_REGS && i == 0) {
 #pragma unroll
@@ -335,8 +368,13 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     // memory, so give them a bounded time and leave without a result (the status word says so)
     unsigned long long t0 = global_timer();
     while (global_timer() - t0 < 200000ull) __nanosleep(1000);
+    if (clustered) {
+      dt_cluster_sync();
+      dt_cluster_sync();
+    }
     return;
   }
+  if (tr) tr[7] = global_timer();
   __syncthreads();  // every warp is done with the stages: they now hold the warps' outputs
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -354,34 +392,82 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     }
   }
   __syncthreads();
-  // ---- merge the four warps
-  if (tid < G) {
+  // ---- merge the four warps: weights first (one thread per warp and row), then the rows
+  if (tid < 4 * DT_ROWS) {
+    const int w = tid >> 4, g = tid & 15;
     float m = -INFINITY;
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_part[(w * DT_ROWS + tid) * 2]);
-    float l = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      float mw = ml_part[(w * DT_ROWS + tid) * 2];
-      if (mw != -INFINITY) l += exp2f(mw - m) * ml_part[(w * DT_ROWS + tid) * 2 + 1];
-    }
-    ml_fin[tid * 2] = m;
-    ml_fin[tid * 2 + 1] = l;
+    for (int x = 0; x < 4; ++x) m = fmaxf(m, ml_part[(x * DT_ROWS + g) * 2]);
+    const float mw = ml_part[(w * DT_ROWS + g) * 2];
+    wsc[tid] = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+    if (w == 0) ml_fin[g * 2] = m;
   }
   __syncthreads();
-  const int z_lo = p_lo / a.pages_per_block, z_hi = p_hi / a.pages_per_block;  // splits with a visible page
-  const bool alone = (z_lo == z_hi);
+  if (tid < DT_ROWS) {
+    float l = 0.f;
+    for (int w = 0; w < 4; ++w) l += wsc[w * DT_ROWS + tid] * ml_part[(w * DT_ROWS + tid) * 2 + 1];
+    ml_fin[tid * 2 + 1] = l;  // rows past G hold zeros: maximum -inf, sum 0
+  }
   for (int i = tid; i < G * head_dim; i += DT_THREADS) {
     int g = i / head_dim, d = i - g * head_dim;
-    float m = ml_fin[g * 2], acc = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      float mw = ml_part[(w * DT_ROWS + g) * 2];
-      if (mw != -INFINITY) acc += exp2f(mw - m) * o_part[(size_t)(w * DT_ROWS + g) * OSTRIDE + d];
-    }
-    if (alone)  // the only split of this sequence: normalise and store, no partials
-      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(acc / ml_fin[g * 2 + 1]);
-    else
-      a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + blockIdx.z) * head_dim + d] = acc;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) acc += wsc[w * DT_ROWS + g] * o_part[(size_t)(w * DT_ROWS + g) * OSTRIDE + d];
+    if (clustered) o_fin[g * HD + d] = acc;
+    else if (!alone) a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + blockIdx.z) * head_dim + d] = acc;
+    else o_fin[g * HD + d] = acc;  // the only split of this sequence: normalised below
   }
-  if (alone) return;
+  __syncthreads();
+  if (alone) {
+    for (int i = tid; i < G * head_dim; i += DT_THREADS) {
+      int g = i / head_dim, d = i - g * head_dim;
+      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(o_fin[g * HD + d] / ml_fin[g * 2 + 1]);
+    }
+    if (tr) tr[8] = global_timer();
+    return;
+  }
+  if (clustered) {
+    // ---- every block's result is in its own shared memory: after the cluster's barrier each
+    // active block adds up, in split order, a slice of the rows' dimensions read from all of them
+    dt_cluster_sync();
+    if (tr) tr[8] = global_timer();
+    const unsigned a_ml = smem_u32(ml_fin), a_o = smem_u32(o_fin);
+    float* wz = ml_part;  // [16][8]: each split's weight, divided by the total sum (ml_part is free now)
+    if (tid < G) {
+      float mz[8], lz[8], m = -INFINITY;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        const bool on = z >= z_lo && z <= z_hi;
+        mz[z] = on ? dt_ld_dsmem(a_ml + (unsigned)(tid * 2) * 4, (unsigned)z) : -INFINITY;
+        lz[z] = on ? dt_ld_dsmem(a_ml + (unsigned)(tid * 2 + 1) * 4, (unsigned)z) : 0.f;
+        m = fmaxf(m, mz[z]);
+      }
+      float den = 0.f;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        mz[z] = (mz[z] == -INFINITY) ? 0.f : exp2f(mz[z] - m);
+        den += mz[z] * lz[z];
+      }
+#pragma unroll
+      for (int z = 0; z < 8; ++z) wz[tid * 8 + z] = mz[z] / den;
+    }
+    __syncthreads();
+    const int n_act = z_hi - z_lo + 1, mine = (int)blockIdx.z - z_lo;
+    const int total = G * head_dim, per = (total + n_act - 1) / n_act;
+    for (int i = mine * per + tid; i < min(total, (mine + 1) * per); i += DT_THREADS) {
+      int g = i / head_dim, d = i - g * head_dim;
+      float v[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z)
+        v[z] = (z >= z_lo && z <= z_hi) ? dt_ld_dsmem(a_o + (unsigned)(g * HD + d) * 4, (unsigned)z) : 0.f;
+      float num = 0.f;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) num += wz[g * 8 + z] * v[z];
+      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num);
+    }
+    if (tr) tr[10] = global_timer();
+    dt_cluster_sync();  // no block leaves while another still reads its result
+    return;
+  }
   if (tid < G) {
     size_t oo = (((size_t)b * n_heads + h0 + tid) * n_splits + blockIdx.z) * 2;
     a.part_ml[oo] = ml_fin[tid * 2];
@@ -398,6 +484,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (s_last) *t = 0;
   }
   __syncthreads();
+  if (tr) tr[9] = global_timer();
   if (!s_last) return;
   __threadfence();
   if (tid < G) {
@@ -418,18 +505,44 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     for (int z = z_lo; z <= z_hi; ++z) num += exp2f(__ldcg(ml + 2 * z) - m) * __ldcg(po + (size_t)z * head_dim + d);
     a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num / ml_fin[g * 2 + 1]);
   }
+  if (tr) tr[10] = global_timer();
+}
+
+// Debugging aid: bn_attention_decode_tc_trace(n) makes the next n launches record timestamps of
+// their blocks (0, 0, z < 8) (device buffer allocated here; not used on the product path).
+static unsigned long long* g_dt_trace = nullptr;
+static int g_dt_trace_n = 0, g_dt_trace_cap = 0;
+extern "C" int bn_attention_decode_tc_trace(int n) {
+  if (g_dt_trace) cudaFree(g_dt_trace);
+  g_dt_trace = nullptr; g_dt_trace_n = 0; g_dt_trace_cap = 0;
+  if (n <= 0) return 0;
+  if (cudaMalloc(&g_dt_trace, (size_t)n * 8 * 16 * 8) != cudaSuccess) return 1;
+  cudaMemset(g_dt_trace, 0, (size_t)n * 8 * 16 * 8);
+  g_dt_trace_cap = n;
+  return 0;
+}
+extern "C" int bn_attention_decode_tc_trace_read(unsigned long long* host, int n) {
+  if (!g_dt_trace || n > g_dt_trace_cap) return 1;
+  return cudaMemcpy(host, g_dt_trace, (size_t)n * 8 * 16 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
 
 template <int HD, int DT_STAGES>
 static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
   size_t smem = 1024 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + (size_t)DT_ROWS * HD * 2 + 2 * HD * 2 +
-                (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float) + DT_STAGES * 8 + HD * sizeof(float);
+                (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float) + DT_STAGES * 8 + HD * sizeof(float) +
+                4 * DT_ROWS * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<HD, DT_STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
+  }
+  if (a.cluster) {
+    cudaError_t e = bn_launch_cluster(attention_decode_tc_kernel<HD, DT_STAGES>, grid, dim3(DT_THREADS), smem, stream,
+                                      dim3(1, 1, grid.z), mk, mv, a);
+    if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+    return BN_OK;
   }
   BN_LAUNCH((attention_decode_tc_kernel<HD, DT_STAGES>), grid, DT_THREADS, smem, stream, mk, mv, a);
   return BN_OK;
@@ -476,6 +589,9 @@ extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, 
   a.theta_scale = theta_scale; a.tok_pos = tok_pos; a.slots = slots; a.page_table = page_table; a.pt_stride = pt_stride;
   a.k_cache = (__nv_bfloat16*)k_cache; a.v_cache = (__nv_bfloat16*)v_cache; a.part_o = part_o; a.part_ml = part_ml;
   a.status = status;
+  a.trace = nullptr;
+  if (g_dt_trace && g_dt_trace_n < g_dt_trace_cap && n_splits <= 8) a.trace = g_dt_trace + (size_t)8 * 16 * (g_dt_trace_n++);
+  a.cluster = (n_splits > 1 && n_splits <= 8) ? 1 : 0;  // few splits: one cluster per (sequence, head group)
   a.pages_per_block = pages_per_block; a.tickets = tickets; a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
   dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits);
   CUtensorMap mk, mv;

@@ -55,6 +55,26 @@ static inline cudaError_t bn_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   cfg.numAttrs = bn_pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
+// The same for a grid of thread-block clusters.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t bn_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, dim3 cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = bn_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 #define BN_LAUNCH(kernel, grid, block, smem, stream, ...)                                  \
   do {                                                                                     \
     cudaError_t e__ = bn_launch(kernel, grid, block, smem, stream, __VA_ARGS__);           \

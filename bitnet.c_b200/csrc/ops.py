@@ -297,7 +297,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_seqs: 
     return out
 
 
-_FORCE_SPLITS = 0  # experiments: a fixed number of blocks per sequence in attention_decode_fused
+_FORCE_SPLITS = 0  # tests and experiments: a fixed number of blocks per sequence in attention_decode_fused
+# (more than eight take the path that merges through global memory and a ticket)
 
 
 def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch.Tensor, n_seqs: int, n_heads: int,
@@ -325,14 +326,13 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         raise KernelError("attention_decode_fused: offsets run past the row")
     if out.shape[0] < n_seqs or out.shape[1] != n_heads * head_dim or tok_pos.shape[0] < n_seqs or qkv.shape[0] < n_seqs:
         raise KernelError("attention_decode_fused: out, qkv or tok_pos does not fit")
-    # few sequences: many blocks per sequence so that all SMs read the cache; many sequences: one
-    # block per (sequence, head group) walks all its pages and no partial results are needed
+    # Few sequences: several blocks per sequence so that many SMs read the cache, but no more
+    # blocks than two per SM, and at most eight per sequence: these merge their results inside
+    # a thread-block cluster.  Many sequences: one block per (sequence, head group) walks all its
+    # pages and no partial results are needed.
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     blocks_per_split = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-    if blocks_per_split >= 2 * N_SMS:
-        want_splits = 1
-    else:
-        want_splits = max(1, min(pages, (4 * N_SMS + blocks_per_split - 1) // blocks_per_split))
+    want_splits = max(1, min(pages, 8, (2 * N_SMS) // blocks_per_split))
     if _FORCE_SPLITS:
         want_splits = max(1, min(pages, _FORCE_SPLITS))
     pages_per_block = (pages + want_splits - 1) // want_splits

@@ -459,9 +459,13 @@ def _last_row_attention(q, k, v, scale, window):
     (2, 2, 256, 64, [257], 0), (40, 40, 64, 0, [100, 300], 0), (12, 1, 32, 32, [150, 40, 260], 17),
     (40, 40, 128, 128, [3000, 17, 2049], 0), (32, 8, 64, 64, [2303, 1], 0), (8, 2, 128, 128, [5000, 4097], 1024),
 ])
-def test_attention_decode_fused(cuda_device, H, KV, hd, rd, lens, window):
+@pytest.mark.parametrize("splits", [0, 3, 12])
+def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd, lens, window):
     """The one-launch decode attention against plain rotary + attention: the new key and value must land
-    in the cache (rotated / as they are) and the result must see them."""
+    in the cache (rotated / as they are) and the result must see them.  ``splits``: blocks per
+    sequence, 0 = chosen from the batch; up to eight merge inside a thread-block cluster, more
+    through global memory and a ticket."""
+    monkeypatch.setattr(ops, "_FORCE_SPLITS", splits)
     g = torch.Generator().manual_seed(23)
     theta = 10000.0
     n_seq = len(lens)
