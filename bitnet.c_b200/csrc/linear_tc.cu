@@ -29,7 +29,12 @@
 // tiles are issued before griddepcontrol.wait, i.e. while the kernel before it in the stream is
 // still draining; everything that reads x or writes memory comes after the wait.
 //
-// Epilogues: (0) store, (2) SwiGLU over weight rows that alternate 8 gate and 8 up rows.
+// Epilogues: (0) store, (2) SwiGLU over weight rows that alternate 8 gate and 8 up rows, (3) add
+// to a float32 residual in place and prepare the RMSNorm that follows it: the residual's new
+// values times the norm's gain go out in bfloat16, and each block leaves the sum of squares of its
+// slice of every row; the product that consumes those rows (any epilogue) multiplies its result
+// rows by 1 / sqrt(sum of the parts / width + eps), which is the same as normalising its input
+// rows (W (s x) = s (W x)).  The parts are added in a fixed order, statistics stay in float32.
 //
 // Every wait on an mbarrier is bounded in time; when a wait gives up the block records a code
 // in *status, still takes part in the cluster barriers, lets its loads drain for a bounded time,
@@ -56,8 +61,16 @@ struct TcArgs {
   int out_dtype;
   int M, N, K;
   int ldo;
-  int mode;        // 0 store, 2 swiglu
+  int mode;        // 0 store, 2 swiglu, 3 residual add + gain + sums of squares
   int k_blocks;    // ceil(K / 64)
+  const float* row_ss;   // [ss_parts][ss_stride]: sums of squares of the input rows, or null (rows are plain)
+  int ss_parts, ss_stride;
+  float inv_width, eps;  // of the norm whose scale the input rows still lack
+  const void* gain;      // mode 3: the next norm's weight [N]
+  int gain_dtype;
+  __nv_bfloat16* xg;     // mode 3: [M, N] residual * gain
+  float* ss_out;         // mode 3: [tiles * cluster][ss_out_stride] sums of squares of this block's slice of each row
+  int ss_out_stride;
   int* status;     // 0, or the code of a wait that gave up
   unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
 };
@@ -153,7 +166,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
   unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
+  float* row_scale = (float*)(tmem_slot + 2);  // [64]: 1 / rms of the input rows (when row_ss is given)
   float* partial = (float*)base;  // [MP][PSTRIDE]: partial[m][row], valid once all MMAs have read the ring
+  float* item_sq = partial + MP * PSTRIDE;  // mode 3: the sum of squares of each epilogue item
+  static_assert((MP * PSTRIDE + 32 * 64) * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and item sums reuse the ring");
   __shared__ int s_failed;
   __shared__ int s_acc_ok;
 
@@ -236,6 +252,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     // ---- epilogue warps, part one: accumulator -> shared memory (TMEM lane quadrant warp % 4)
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
+    if (a.row_ss != nullptr) {
+      // the scale each input row still lacks, from the parts its producer left (fixed order)
+      pdl_wait();
+      for (int m = tid - 64; m < a.M; m += 128) {
+        float ss = 0.f;
+        for (int p = 0; p < a.ss_parts; ++p) ss += a.row_ss[(size_t)p * a.ss_stride + m];
+        row_scale[m] = 1.0f / sqrtf(ss * a.inv_width + a.eps);
+      }
+    }
     if (warp == 2 && lane == 0) {
       int ok = mbar_wait(acc_bar, 0, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
       if (!ok) s_failed = 1;
@@ -277,7 +302,43 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         int n = tile * TC_BM + r0 + rl;
         if (n >= a.N) continue;
         float4 sum = sum_dsmem4(pbase + (unsigned)((m * PSTRIDE + r0 + rl) * 4), C);
+        if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
         store4(a.out, a.out_dtype, (size_t)m * a.ldo + n, sum, min(4, a.N - n));
+      }
+    } else if (a.mode == 3) {
+      // out is the float32 residual [M, ldo]: add, write back, hand on residual * gain, and leave
+      // this slice's sum of squares per row (items in a fixed order, then one thread per row)
+      const int groups = rows / 4;
+      float* res = (float*)a.out;
+      for (int e = t; e < groups * a.M; e += 128) {
+        int m = e / groups, rl = (e - m * groups) * 4;
+        int n = tile * TC_BM + r0 + rl;
+        float sq = 0.f;
+        if (n < a.N) {
+          float4 sum = sum_dsmem4(pbase + (unsigned)((m * PSTRIDE + r0 + rl) * 4), C);
+          if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
+          const int valid = min(4, a.N - n);
+          float v[4] = {sum.x, sum.y, sum.z, sum.w};
+          float* rp = res + (size_t)m * a.ldo + n;
+          float gv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (i < valid) {
+              v[i] += rp[i];
+              rp[i] = v[i];
+              gv[i] = v[i] * load_as_f32(a.gain, a.gain_dtype, (size_t)(n + i));
+              sq += v[i] * v[i];
+            }
+          }
+          store4(a.xg, BN_BF16, (size_t)m * a.N + n, make_float4(gv[0], gv[1], gv[2], gv[3]), valid);
+        }
+        item_sq[e] = sq;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int m = t; m < a.M; m += 128) {
+        float ss = 0.f;
+        for (int gq = 0; gq < groups; ++gq) ss += item_sq[m * groups + gq];
+        a.ss_out[(size_t)(tile * C + rank) * a.ss_out_stride + m] = ss;
       }
     } else {
       // rows 16j..16j+7 of a tile are gate rows, rows 16j+8..16j+15 the up rows of the same indices;
@@ -290,6 +351,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         if (n >= a.N) continue;
         unsigned ag = pbase + (unsigned)((m * PSTRIDE + rg) * 4);
         float4 g = sum_dsmem4(ag, C), u = sum_dsmem4(ag + 8 * 4, C);
+        if (a.row_ss != nullptr) {
+          const float rs = row_scale[m];
+          g.x *= rs; g.y *= rs; g.z *= rs; g.w *= rs;
+          u.x *= rs; u.y *= rs; u.z *= rs; u.w *= rs;
+        }
         float4 act;
         act.x = g.x / (1.0f + expf(-g.x)) * u.x;
         act.y = g.y / (1.0f + expf(-g.y)) * u.y;
@@ -351,7 +417,7 @@ template <int MP>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int cluster, int tiles,
                      cudaStream_t stream) {
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
-  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + 1024;
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + 64 * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -377,38 +443,71 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs&
   return BN_OK;
 }
 
+static int auto_cluster(int tiles, int k_blocks) {
+  int cluster = sm_count() / tiles;
+  int by_k = k_blocks / 4;  // at least four k-blocks per block
+  if (cluster > by_k) cluster = by_k;
+  if (cluster > 8) cluster = 8;
+  if (cluster < 1) cluster = 1;
+  return cluster;
+}
+// How many blocks share a tile's inner dimension when the caller leaves the choice to the kernel
+// (mode 3 writes tiles x this many parts of sums of squares).
+extern "C" int bn_linear_tc_auto_cluster(int N, int K) {
+  if (N <= 0 || K <= 0) return 1;
+  return auto_cluster((N + TC_BM - 1) / TC_BM, (K + TC_BK - 1) / TC_BK);
+}
+
 // x [M, K], w [N, K] bfloat16, both 16-byte aligned with K a multiple of 8.  mode 0: out [M, ldo]
 // of out_dtype; mode 2: N = 2 I weight rows in blocks of 8 gate / 8 up rows, out holds
-// silu(gate) * up in I columns.  cluster: blocks that share a tile's inner dimension, 1 to 8
-// (0: chosen so that cluster x tiles is about the number of SMs).  status: one int on the device,
-// left 0 unless a wait inside the kernel gave up.
-extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
-                            int mode, int cluster, int* status, cudaStream_t stream) {
+// silu(gate) * up in I columns; mode 3: out is a float32 residual [M, ldo] that the product is
+// added to in place, xg [M, N] bfloat16 receives residual * gain (gain [N] of gain_dtype) and
+// ss_out [tiles * cluster][ss_out_stride] the sums of squares of each block's slice of every row
+// (tiles = ceil(N / 128); cluster must be given).  row_ss (or null): [ss_parts][ss_stride] sums of
+// squares of the rows of x as a mode-3 product left them; the result rows are then multiplied by
+// 1 / sqrt(sum / width + eps) with inv_width = 1 / width.  cluster: blocks that share a tile's
+// inner dimension, 1 to 8 (0: chosen so that cluster x tiles is about the number of SMs).  status:
+// one int on the device, left 0 unless a wait inside the kernel gave up.
+extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
+                               int mode, int cluster, const float* row_ss, int ss_parts, int ss_stride, float inv_width,
+                               float eps, const void* gain, int gain_dtype, void* xg, float* ss_out, int ss_out_stride,
+                               int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
-  if (M > 64 || K <= 0 || K % 8 || cluster < 0 || cluster > 8 || (mode != 0 && mode != 2) || !status)
+  if (M > 64 || K <= 0 || K % 8 || cluster < 0 || cluster > 8 || (mode != 0 && mode != 2 && mode != 3) || !status)
     return BN_ERR_BAD_ARG;
   if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
+  if (mode == 3 && (!gain || !xg || !ss_out || ss_out_stride < M || cluster == 0 || out_dtype != BN_F32 ||
+                    (gain_dtype != BN_F32 && gain_dtype != BN_BF16)))
+    return BN_ERR_BAD_ARG;
+  if (row_ss && (ss_parts <= 0 || ss_stride < M)) return BN_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return BN_ERR_BAD_ARG;
   int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   int tiles = (N + TC_BM - 1) / TC_BM;
   int k_blocks = (K + TC_BK - 1) / TC_BK;
   if (tiles > 65535) return BN_ERR_BAD_ARG;
-  if (cluster == 0) {
-    cluster = sm_count() / tiles;
-    int by_k = k_blocks / 4;  // at least four k-blocks per block
-    if (cluster > by_k) cluster = by_k;
-    if (cluster > 8) cluster = 8;
-    if (cluster < 1) cluster = 1;
+  if (cluster == 0) cluster = auto_cluster(tiles, k_blocks);
+  if (cluster > k_blocks) {
+    if (mode == 3) return BN_ERR_BAD_ARG;  // the caller sized ss_out for the cluster it named
+    cluster = k_blocks;
   }
-  if (cluster > k_blocks) cluster = k_blocks;
   CUtensorMap mw, mx;
   if (!tma_map_bf16_rows(&mw, w, N, K, TC_BM) || !tma_map_bf16_rows(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
   TcArgs a;
   a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
   a.k_blocks = k_blocks; a.status = status;
+  a.row_ss = row_ss; a.ss_parts = ss_parts; a.ss_stride = ss_stride; a.inv_width = inv_width; a.eps = eps;
+  a.gain = gain; a.gain_dtype = gain_dtype; a.xg = (__nv_bfloat16*)xg; a.ss_out = ss_out; a.ss_out_stride = ss_out_stride;
   a.trace = nullptr;
   if (g_trace && g_trace_n < g_trace_cap) a.trace = g_trace + 8 * (g_trace_n++);
   if (mp == 16) return launch_tc<16>(mw, mx, a, cluster, tiles, stream);
   if (mp == 32) return launch_tc<32>(mw, mx, a, cluster, tiles, stream);
   return launch_tc<64>(mw, mx, a, cluster, tiles, stream);
+}
+
+// The plain forms (modes 0 and 2, plain input rows).
+extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
+                            int mode, int cluster, int* status, cudaStream_t stream) {
+  if (mode == 3) return BN_ERR_BAD_ARG;
+  return bn_linear_tc_ex(x, w, out, out_dtype, M, N, K, ldo, mode, cluster, nullptr, 0, 0, 0.f, 0.f, nullptr, 0, nullptr,
+                         nullptr, 0, status, stream);
 }

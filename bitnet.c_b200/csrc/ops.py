@@ -412,29 +412,105 @@ def check_tc_status(device) -> None:
         raise KernelError(f"{what}; the result of that launch is not valid")
 
 
-def linear_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-              cluster: int = 0) -> torch.Tensor:
+class RowScaled:
+    """Rows of activations that still lack their RMS scale: the value of row m is
+    ``x[m] / sqrt(sum_p ss[p, m] / width + eps)``.  A product whose epilogue added to the residual
+    (``linear(..., sink=...)``) leaves the next norm's output in this form: x = residual * gain in
+    bfloat16 and, per block of the product, the sum of squares of its slice of every residual row.
+    The product that consumes the rows scales its result rows instead (W (s x) = s (W x))."""
+
+    def __init__(self, x: torch.Tensor, ss: torch.Tensor, width: int, eps: float):
+        self.x, self.ss, self.width, self.eps = x, ss, int(width), float(eps)
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def device(self):
+        return self.x.device
+
+    def dense(self) -> torch.Tensor:
+        """The rows with their scale applied (for a consumer that cannot apply it itself)."""
+        scale = torch.rsqrt(self.ss.sum(0)[: self.x.shape[0]] / self.width + self.eps)
+        return (self.x.float() * scale[:, None]).to(self.x.dtype)
+
+
+class NormSink:
+    """Where a product's result goes when the RMSNorm after it is fused into its epilogue: the
+    float32 residual it is added to, and that norm's weight and eps."""
+
+    def __init__(self, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+        self.residual, self.weight, self.eps = residual, weight, float(eps)
+
+
+USE_FUSED_NORM = True  # products of few rows add to the residual and prepare the next norm in their epilogue
+
+
+def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
+              cluster: int = 0, sink: Optional[NormSink] = None):
     """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands.
     ``cluster`` blocks (1 to 8) share the inner dimension of each 128-row tile of w and add their
-    parts up through distributed shared memory (0: chosen from the number of tiles)."""
+    parts up through distributed shared memory (0: chosen from the number of tiles).  ``x`` may be
+    ``RowScaled``.  With ``sink`` the product is added to ``sink.residual`` in place and the result
+    is the ``RowScaled`` output of the norm that follows."""
+    scaled = x if isinstance(x, RowScaled) else None
+    if scaled is not None:
+        x = scaled.x
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or M > MMA_MAX_ROWS or K % 8 or (swiglu and N % 16) or not 0 <= cluster <= 8:
         raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, cluster {cluster} not supported")
+    fn = _fn("linear_tc", "bn_linear_tc_ex")
+    if scaled is not None:
+        _need(scaled.ss, "ss", torch.float32, 2)
+        if scaled.ss.shape[1] < M or scaled.width != K:
+            raise KernelError(f"linear_tc: row sums {tuple(scaled.ss.shape)} of width {scaled.width} do not fit x {tuple(x.shape)}")
+        row = (_ptr(scaled.ss), c_int(scaled.ss.shape[0]), c_int(scaled.ss.shape[1]), c_float(1.0 / scaled.width),
+               c_float(scaled.eps))
+    else:
+        row = (c_void_p(None), c_int(0), c_int(0), c_float(0.0), c_float(0.0))
+    if sink is not None:
+        res = sink.residual
+        _need(res, "residual", torch.float32, 2)
+        _need(sink.weight, "norm weight", dims=1)
+        if swiglu or tuple(res.shape) != (M, N) or sink.weight.shape[0] != N or sink.weight.dtype not in _DT:
+            raise KernelError(f"linear_tc: residual {tuple(res.shape)} / norm weight {tuple(sink.weight.shape)} do not fit "
+                              f"a product [{M}, {N}]")
+        if cluster == 0:
+            f = getattr(build.library("linear_tc"), "bn_linear_tc_auto_cluster")
+            f.restype = c_int
+            cluster = int(f(c_int(N), c_int(K)))
+        tiles = (N + 127) // 128
+        xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ss = torch.empty((tiles * cluster, M), dtype=torch.float32, device=x.device)
+        _check(fn(_ptr(x), _ptr(w), _ptr(res), c_int(_DT[torch.float32]), c_int(M), c_int(N), c_int(K), c_int(N), c_int(3),
+                  c_int(cluster), *row, _ptr(sink.weight), c_int(_DT[sink.weight.dtype]), _ptr(xg), _ptr(ss), c_int(M),
+                  _ptr(tc_status(x.device)), _stream()), "linear_tc")
+        return RowScaled(xg, ss, N, sink.eps)
     out_dtype = out_dtype or x.dtype
     cols = N // 2 if swiglu else N
     out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
-    _check(_fn("linear_tc", "bn_linear_tc")(
-        _ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(cols),
-        c_int(2 if swiglu else 0), c_int(cluster), _ptr(tc_status(x.device)), _stream()), "linear_tc")
+    _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(cols),
+              c_int(2 if swiglu else 0), c_int(cluster), *row, c_void_p(None), c_int(0), c_void_p(None), c_void_p(None),
+              c_int(0), _ptr(tc_status(x.device)), _stream()), "linear_tc")
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
-           swiglu: bool = False, partial_sums: bool = False) -> torch.Tensor:
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
+           swiglu: bool = False, partial_sums: bool = False, sink: Optional[NormSink] = None):
     """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
+
+    ``x`` may be ``RowScaled`` (the output of a norm that a product's epilogue prepared).  With
+    ``sink`` the product is added to ``sink.residual`` and the result is the output of the norm
+    that follows it: ``RowScaled`` when the product of few rows does it in its epilogue,
+    else a tensor from the norm kernel.
 
     ``swiglu``: w holds gate and up rows in alternating blocks of 8 and the result is
     silu(gate) * up, ``[M, N / 2]``.  ``partial_sums``: return the float32 partial sums
@@ -443,16 +519,27 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     ``allow_partials`` is accepted for callers that add the result to the residual and is
     ignored.
     """
-    _need(x, "x", dims=2)
     _need(w, "w", dims=2)
-    if x.shape[1] != w.shape[1]:
+    if x.shape[1] != w.shape[1] or len(x.shape) != 2:
         raise KernelError(f"linear: x {tuple(x.shape)} and w {tuple(w.shape)} do not share the inner size")
-    out_dtype = out_dtype or x.dtype
-    if x.dtype != w.dtype:
-        x = x.to(w.dtype)
     M, K = x.shape
     N = w.shape[0]
     small = w.dtype == torch.bfloat16 and M <= MMA_MAX_ROWS and K % 8 == 0 and (not swiglu or N % 16 == 0)
+    fast = small and not partial_sums and USE_TCGEN05 and x.dtype == torch.bfloat16
+    if sink is not None:
+        if fast and USE_FUSED_NORM and not swiglu and tuple(sink.residual.shape) == (M, N):
+            return linear_tc(x, w, sink=sink)
+        delta = linear(x, w, out_dtype=out_dtype, allow_partials=allow_partials, swiglu=swiglu)
+        normed = torch.empty((M, sink.residual.shape[1]), dtype=delta.dtype, device=delta.device)
+        return add_rmsnorm(sink.residual, delta, sink.weight, sink.eps, normed)
+    if isinstance(x, RowScaled):
+        if fast:
+            return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
+        x = x.dense()
+    _need(x, "x", dims=2)
+    out_dtype = out_dtype or x.dtype
+    if x.dtype != w.dtype:
+        x = x.to(w.dtype)
     if small and not partial_sums and USE_TCGEN05:
         return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
     if small:

@@ -43,6 +43,7 @@ class StepContext:
     max_new: int  # longest run of new tokens in this step
     max_len: int  # longest sequence after this step
     decode: bool  # every sequence brings exactly one token
+    rows_all: bool = False  # ``rows`` names every packed row once, in order (logits for every token)
     tile_seq: Optional[torch.Tensor] = None  # [n_tiles] int32: the sequence of each block of 64 new tokens
     tile_row0: Optional[torch.Tensor] = None  # [n_tiles] int32: its first row within the sequence's new tokens
     wide_tile_seq: Optional[torch.Tensor] = None  # the same for blocks of 128 new tokens
@@ -92,6 +93,7 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
         slots=dev[o:o + n], seq_start=dev[o + n:o + 2 * n + 1], seq_pos0=dev[o + 2 * n + 1:o + 3 * n + 1],
         rows=dev[r0:r0 + n_rows] if n_rows else None, max_new=max(new),
         max_len=max(l + c for l, c in zip(lengths, new)), decode=all(c == 1 for c in new),
+        rows_all=(n_rows == T and all(list(s.want) == list(range(len(s.tokens))) for s in seqs)),
         tile_seq=dev[t0:t0 + n_tiles], tile_row0=dev[t0 + n_tiles:t0 + 2 * n_tiles],
         wide_tile_seq=dev[w0:w0 + n_wide], wide_tile_row0=dev[w0 + n_wide:w0 + 2 * n_wide], host_new=new,
         host_pos0=list(lengths),

@@ -37,7 +37,7 @@ class DecodeRunner:
         ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
         self.ctx = StepContext(n_seqs=B, n_tokens=B, tokens=self.tokens, tok_seq=ar[:B], tok_pos=self.tok_pos,
                                slots=self.slots, seq_start=ar, seq_pos0=self.tok_pos, rows=ar[:B], max_new=1,
-                               max_len=cache.max_positions, decode=True)
+                               max_len=cache.max_positions, decode=True, rows_all=True)
         self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
         self.graphs = {}  # length bucket -> recorded graph
         self.pool = pool

@@ -18,6 +18,7 @@ from ..config import ConfigError, ModelSpec, architecture_of, read_config_json
 from ..csrc import build as kernel_build
 from ..csrc import ops
 from ..parts import BuildContext, ParamSpec, Part, build_part
+from ..parts.base import Normed
 from .batch import SeqStep, StepContext, pack_step
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -214,11 +215,26 @@ class Model:
         x = torch.empty((ctx.n_tokens, self.spec.width), dtype=torch.float32, device=self.device)
         ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
         pending = None
-        for i, e in enumerate(self.spec.schedule):
-            pending = self.blocks[e.block].forward(x, pending, ctx, cache.view(i), cache.state(i))
+        sched = self.spec.schedule
+        for i, e in enumerate(sched):
+            blk = self.blocks[e.block]
+            if not getattr(blk, "accepts_normed", False):
+                pending = blk.forward(x, pending, ctx, cache.view(i), cache.state(i))
+                continue
+            # the norm after this block, if whoever applies it can take its output ready-made:
+            # the next block's first norm, or the final norm when every row's logits are wanted
+            if i + 1 < len(sched):
+                nxt = self.blocks[sched[i + 1].block]
+                next_norm = nxt.entry_norm() if getattr(nxt, "accepts_normed", False) else None
+            else:
+                next_norm = self.final_norm if ctx.rows is not None and ctx.rows_all else None
+            pending = blk.forward(x, pending, ctx, cache.view(i), cache.state(i), next_norm=next_norm)
         if ctx.rows is None:
             return None
-        h = self.final_norm.add_norm(x, pending, ctx, rows=ctx.rows)
+        if isinstance(pending, Normed):
+            h = pending.value
+        else:
+            h = self.final_norm.add_norm(x, pending, ctx, rows=ctx.rows)
         return ops.linear(h, self.head, out_dtype=torch.float32)
 
 

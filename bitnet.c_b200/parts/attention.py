@@ -17,8 +17,9 @@ class Attention(Mixer):
     Order and formulas: src/transformer/cpu.c:859-939, src/transformer/gqa_scalar.c:61-121."""
 
     kernels = ("linear", "linear_mma", "linear_tc", "attention", "attention_decode", "attention_decode_tc", "attention_prefill",
-               "attention_prefill_tc", "rope")
+               "attention_prefill_tc", "rope", "norm")
     graph_safe = True
+    accepts_sink = True
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -50,7 +51,7 @@ class Attention(Mixer):
         s = self.spec
         return KvRequest(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
 
-    def forward(self, h, ctx, kv, state):
+    def forward(self, h, ctx, kv, state, sink=None):
         s = self.spec
         n = h.shape[0]
         fusable = getattr(self.position, "rotary_params", None)
@@ -63,7 +64,7 @@ class Attention(Mixer):
             ops.attention_decode_fused(qkv, s.q_dim, s.q_dim + s.kv_dim, out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                        s.softmax_scale, s.window, rotary_dims, theta_scale, ctx.tok_pos, ctx.slots,
                                        kv.page_table, kv.k, kv.v, ctx.max_len)
-            return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True)
+            return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True, sink=sink)
         if kv.owner:
             qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)
             n_rot = s.n_heads + s.n_kv_heads
@@ -97,4 +98,4 @@ class Attention(Mixer):
             ops.attention_general(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                   s.softmax_scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
                                   kv.page_table, kv.k, kv.v)
-        return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True)
+        return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True, sink=sink)

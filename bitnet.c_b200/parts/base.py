@@ -98,6 +98,12 @@ class Part:
 
 
 class Mixer(Part):
+    # A mixer or feed-forward that sets ``accepts_sink`` takes ``h`` as ``ops.RowScaled`` too and a
+    # keyword ``sink`` (``ops.NormSink`` or None); with a sink it adds its result to the residual
+    # itself and returns the output of the norm that follows (``ops.linear(..., sink=sink)``)
+    # instead of the delta.
+    accepts_sink = False
+
     def cache_request(self) -> Optional[KvRequest]:
         return None
 
@@ -109,13 +115,28 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_sink = False  # as for Mixer
+
     def forward(self, h, ctx):
         raise NotImplementedError
+
+
+class Normed:
+    """A norm's output that an earlier product already prepared in its epilogue (``value`` is a
+    tensor or ``ops.RowScaled``); a block that gets it as ``pending`` skips its first norm."""
+
+    def __init__(self, value):
+        self.value = value
 
 
 class Norm(Part):
     def add_norm(self, x, delta, ctx, rows=None):
         raise NotImplementedError
+
+    def sink(self, x, ctx):
+        """What a product needs to add its result to the residual ``x`` and prepare this norm's
+        output in its own epilogue (``ops.NormSink``), or None when this norm cannot be fused."""
+        return None
 
 
 class Position(Part):
@@ -128,6 +149,14 @@ class Block(Part):
         return None
 
     def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    # A block that sets ``accepts_normed`` takes ``pending`` as ``Normed`` too, and a keyword
+    # ``next_norm``: the norm that follows this block, whose output its last product may prepare.
+    accepts_normed = False
+
+    def entry_norm(self):
+        """The norm this block applies first (None: not fusable into the block before it)."""
         return None
 
     def forward(self, x, pending, ctx, kv, state):

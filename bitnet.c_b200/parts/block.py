@@ -1,7 +1,8 @@
 """How a mixer, a feed-forward and their norms are arranged into one block."""
 from __future__ import annotations
 
-from .base import Block
+from ..csrc import ops
+from .base import Block, Normed
 from .registry import build_part, register_block
 
 
@@ -11,9 +12,16 @@ class PreNormBlock(Block):
 
     Each delta is handed to the next norm, which adds it to the residual while it reads
     it anyway; the block's last delta is returned as ``pending`` for whoever norms next.
+    Where a part's last product can do that norm's work in its epilogue (few rows, bfloat16:
+    ``Norm.sink``), the part gets a sink, adds to the residual itself and returns the norm's
+    output; what the block then returns is ``Normed`` for the block after it.
     """
 
     graph_safe = True  # as far as its parts are
+    accepts_normed = True
+
+    def entry_norm(self):
+        return self.mixer_norm
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -31,8 +39,21 @@ class PreNormBlock(Block):
     def state_request(self):
         return self.mixer.state_request()
 
-    def forward(self, x, pending, ctx, kv, state):
-        h = self.mixer_norm.add_norm(x, pending, ctx)
-        d = self.mixer.forward(h, ctx, kv, state)
-        h = self.ffn_norm.add_norm(x, d, ctx)
-        return self.ffn.forward(h, ctx)
+    @staticmethod
+    def _input_for(part, h):
+        if isinstance(h, ops.RowScaled) and not getattr(part, "accepts_sink", False):
+            return h.dense()
+        return h
+
+    def forward(self, x, pending, ctx, kv, state, next_norm=None):
+        h = pending.value if isinstance(pending, Normed) else self.mixer_norm.add_norm(x, pending, ctx)
+        sink = self.ffn_norm.sink(x, ctx) if getattr(self.mixer, "accepts_sink", False) else None
+        if sink is not None:
+            h = self.mixer.forward(self._input_for(self.mixer, h), ctx, kv, state, sink=sink)
+        else:
+            d = self.mixer.forward(self._input_for(self.mixer, h), ctx, kv, state)
+            h = self.ffn_norm.add_norm(x, d, ctx)
+        sink = next_norm.sink(x, ctx) if next_norm is not None and getattr(self.ffn, "accepts_sink", False) else None
+        if sink is not None:
+            return Normed(self.ffn.forward(self._input_for(self.ffn, h), ctx, sink=sink))
+        return self.ffn.forward(self._input_for(self.ffn, h), ctx)

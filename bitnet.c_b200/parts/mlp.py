@@ -14,8 +14,9 @@ from .registry import register_ffn
 class GatedMlp(FeedForward):
     """y = W_down (silu(W_gate h) * (W_up h))   (src/transformer/cpu.c:1247-1303)."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "act")
+    kernels = ("linear", "linear_mma", "linear_tc", "act", "norm")
     graph_safe = True
+    accepts_sink = True
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -36,6 +37,6 @@ class GatedMlp(FeedForward):
         self.w_gate_up = ops.interleave_gate_up(g.to(dt), u.to(dt))
         self.w_down = tensors["down"]
 
-    def forward(self, h, ctx):
+    def forward(self, h, ctx, sink=None):
         act = ops.linear(h, self.w_gate_up, out_dtype=self.build.dtype, swiglu=True)
-        return ops.linear(act, self.w_down, out_dtype=self.build.dtype, allow_partials=True)
+        return ops.linear(act, self.w_down, out_dtype=self.build.dtype, allow_partials=True, sink=sink)

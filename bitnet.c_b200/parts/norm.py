@@ -24,6 +24,13 @@ class RmsNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
+    def sink(self, x, ctx):
+        # a product of few rows in bfloat16 can add to the residual and prepare this norm's output
+        if (self.build.dtype == torch.bfloat16 and x.shape[0] <= ops.MMA_MAX_ROWS and ops.USE_TCGEN05
+                and ops.USE_FUSED_NORM and x.dtype == torch.float32):
+            return ops.NormSink(x, self.weight, self.spec.eps)
+        return None
+
     def add_norm(self, x, delta, ctx, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.spec.width), dtype=self.build.dtype, device=x.device)

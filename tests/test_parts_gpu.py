@@ -210,3 +210,40 @@ def test_a_new_mixer_with_state_needs_no_change_to_the_library(cuda_device):
             compare(replay(model, cache, steps), ref, lambda r: 2e-4, "toy mixer")
     finally:
         unregister("mixer", "toy_decay_mix")
+
+
+def test_norms_fused_into_products_agree_with_norm_kernels(cuda_device, monkeypatch):
+    """With few rows in bfloat16 the products before a norm add to the residual and prepare the
+    norm's output themselves (``ops.RowScaled``).  The logits must agree with the path through
+    the norm kernels to a few bfloat16 roundings, for prompts in one step and for decode steps,
+    and a request for only some rows' logits must still take the final norm kernel."""
+    from bitnet_c_b200.csrc import ops
+    from tiny_configs import TINY_D
+    model = Model.from_random(dict(TINY_D), seed=5, dtype="bfloat16", device=cuda_device)
+    toks = [torch.randint(0, TINY_D["vocab_size"], (n,), generator=torch.Generator().manual_seed(n)).tolist()
+            for n in (40, 9, 23)]
+
+    def run(fused):
+        monkeypatch.setattr(ops, "USE_FUSED_NORM", fused)
+        cache = model.new_cache(max_tokens=1024, max_seqs=3)
+        slots = [cache.open() for _ in toks]
+        outs = [model.step(cache, [SeqStep(s, t, list(range(len(t)))) for s, t in zip(slots, toks)])]  # 72 rows: kernels
+        outs.append(model.step(cache, [SeqStep(s, [7, 8, 9], [0, 1, 2]) for s in slots]))  # 9 rows, all wanted
+        outs.append(model.step(cache, [SeqStep(s, [3], [0]) for s in slots]))              # decode
+        outs.append(model.step(cache, [SeqStep(s, [4, 5], [1]) for s in slots]))           # only some rows wanted
+        model.check_kernels()
+        return [o.double().cpu().numpy() for o in outs]
+
+    launches = []
+    real = ops.add_rmsnorm
+    monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (launches.append(1), real(*a, **k))[1])
+    a = run(False)
+    n_unfused = len(launches)
+    del launches[:]
+    b = run(True)
+    n_fused = len(launches)
+    # 2 layers: 5 norm launches per step unfused; fused: all five in the prompt step (72 rows), one
+    # (the first norm) in the steps of few rows, two (first and final) when only some rows are wanted
+    assert n_unfused == 20 and n_fused == 5 + 1 + 1 + 2
+    for x, y in zip(a, b):
+        assert np.abs(x - y).max() <= bf16_bound(x)
