@@ -167,6 +167,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
   unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
   float* row_scale = (float*)(tmem_slot + 2);  // [64]: 1 / rms of the input rows (when row_ss is given)
+  float* ss_chunk = row_scale + 64;            // [128 / MP][MP]: partial sums on the way there
   float* partial = (float*)base;  // [MP][PSTRIDE]: partial[m][row], valid once all MMAs have read the ring
   float* item_sq = partial + MP * PSTRIDE;  // mode 3: the sum of squares of each epilogue item
   static_assert((MP * PSTRIDE + 32 * 64) * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and item sums reuse the ring");
@@ -253,12 +254,22 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     if (a.row_ss != nullptr) {
-      // the scale each input row still lacks, from the parts its producer left (fixed order)
+      // the scale each input row still lacks, from the parts its producer left: the 128 threads
+      // share a row's parts in 128 / MP chunks, then one thread per row adds the chunks in order
       pdl_wait();
-      for (int m = tid - 64; m < a.M; m += 128) {
-        float ss = 0.f;
-        for (int p = 0; p < a.ss_parts; ++p) ss += a.row_ss[(size_t)p * a.ss_stride + m];
-        row_scale[m] = 1.0f / sqrtf(ss * a.inv_width + a.eps);
+      constexpr int CH = 128 / MP;
+      const int t = tid - 64, m = t % MP, c = t / MP;
+      const int per = (a.ss_parts + CH - 1) / CH;
+      float ss = 0.f;
+      if (m < a.M)
+        for (int p = c * per; p < min(a.ss_parts, (c + 1) * per); ++p) ss += a.row_ss[(size_t)p * a.ss_stride + m];
+      ss_chunk[c * MP + m] = ss;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (t < a.M) {
+        float tot = 0.f;
+#pragma unroll
+        for (int q = 0; q < CH; ++q) tot += ss_chunk[q * MP + t];
+        row_scale[t] = 1.0f / sqrtf(tot * a.inv_width + a.eps);
       }
     }
     if (warp == 2 && lane == 0) {
@@ -417,7 +428,7 @@ template <int MP>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int cluster, int tiles,
                      cudaStream_t stream) {
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
-  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + 64 * 4 + 1024;
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + (64 + 128) * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

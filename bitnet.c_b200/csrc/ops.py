@@ -8,6 +8,7 @@ back to the CPU: tensors that are not on a CUDA device are refused.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Optional
 
@@ -448,7 +449,8 @@ class NormSink:
         self.residual, self.weight, self.eps = residual, weight, float(eps)
 
 
-USE_FUSED_NORM = True  # products of few rows add to the residual and prepare the next norm in their epilogue
+USE_FUSED_NORM = not os.environ.get("BN_NO_FUSED_NORM")  # products of few rows add to the residual and prepare the
+# next norm in their epilogue (the variable switches it off for comparisons)
 
 
 def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
