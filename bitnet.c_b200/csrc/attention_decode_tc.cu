@@ -195,60 +195,108 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     cs_tab[2 * i] = cs;
     cs_tab[2 * i + 1] = sn;
   }
+  // rows past the head group and dimensions past the head size are zero in the query tile and in
+  // the new token's row (also before the wait)
+  for (int p = tid; p < DT_ROWS * HD / 8; p += DT_THREADS) reinterpret_cast<uint4*>(q_tile)[p] = make_uint4(0u, 0u, 0u, 0u);
+  for (int p = tid; p < 2 * HD / 8; p += DT_THREADS) reinterpret_cast<uint4*>(new_kv)[p] = make_uint4(0u, 0u, 0u, 0u);
   if (tr) tr[2] = global_timer();
   pdl_wait();  // the kernel before this one has completed: the q|k|v rows are there
   if (tr) tr[3] = global_timer();
   __syncthreads();
 
-  // ---- queries of this head group: rotate, round to bfloat16, place as rows of the 16-row tile
+  // ---- queries of this head group (rotated, rounded to bfloat16, rows of the 16-row tile) and the
+  // new token's key (rotated) and value (to the cache, and kept for this block's stage).  The
+  // work is a list of 16-byte items, one per thread, so that all loads are in flight together.
   const __nv_bfloat16* qrow = a.qkv + (size_t)b * a.q_stride;
-  auto q_at = [&](int g, int d) -> __nv_bfloat16* {
-    return reinterpret_cast<__nv_bfloat16*>(q_tile + dt_off<HD>(g, d >> 3)) + (d & 7);
-  };
-  for (int p = tid; p < DT_ROWS * HD; p += DT_THREADS) {  // zero rows past G and padding dimensions
-    int g = p / HD, d = p - g * HD;
-    if (g >= G || d >= head_dim) *q_at(g, d) = __float2bfloat16_rn(0.f);
-  }
-  for (int p = tid; p < G * half; p += DT_THREADS) {
-    int g = p / half, i = p - g * half;
-    const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
-    const __nv_bfloat16* hd = qrow + (size_t)(h0 + g) * head_dim;
-    float x = __bfloat162float(hd[i]), y = __bfloat162float(hd[i + half]);
-    *q_at(g, i) = __float2bfloat16_rn(x * cs - y * sn);
-    *q_at(g, i + half) = __float2bfloat16_rn(x * sn + y * cs);
-  }
-  {
+  const __nv_bfloat16* kraw = qrow + a.k_off + (size_t)kvh * head_dim;
+  const __nv_bfloat16* vraw = qrow + a.v_off + (size_t)kvh * head_dim;
+  const size_t new_off = has_new ? (((size_t)pt[p_hi] * n_kv_heads + kvh) * BN_PAGE + new_row) * (size_t)head_dim : 0;
+  if ((a.rotary_dims & 15) == 0) {
+    const int hc = half >> 3;                           // chunks of 8 in half the rotary dimensions
+    const int rc = (head_dim - a.rotary_dims) >> 3;     // chunks that are not rotated
+    const int per_head = hc + rc;                       // items of one head: rotary pairs, then plain chunks
+    const int n_q = G * per_head, n_k = has_new ? per_head : 0, n_v = has_new ? (head_dim >> 3) : 0;
+    for (int item = tid; item < n_q + n_k + n_v; item += DT_THREADS) {
+      if (item >= n_q + n_k) {  // a chunk of the new value
+        const int c = item - n_q - n_k;
+        const uint4 v = *reinterpret_cast<const uint4*>(vraw + c * 8);
+        *reinterpret_cast<uint4*>(a.v_cache + new_off + c * 8) = v;
+        *reinterpret_cast<uint4*>(new_kv + HD + c * 8) = v;
+        continue;
+      }
+      const bool is_k = item >= n_q;
+      const int g = is_k ? 0 : item / per_head, c = is_k ? item - n_q : item - g * per_head;
+      const __nv_bfloat16* src = is_k ? kraw : qrow + (size_t)(h0 + g) * head_dim;
+      if (c >= hc) {  // a plain chunk behind the rotary dimensions
+        const int d = a.rotary_dims + (c - hc) * 8;
+        const uint4 v = *reinterpret_cast<const uint4*>(src + d);
+        if (is_k) {
+          *reinterpret_cast<uint4*>(a.k_cache + new_off + d) = v;
+          *reinterpret_cast<uint4*>(new_kv + d) = v;
+        } else {
+          *reinterpret_cast<uint4*>(q_tile + dt_off<HD>(g, d >> 3)) = v;
+        }
+        continue;
+      }
+      uint4 xv = *reinterpret_cast<const uint4*>(src + c * 8), yv = *reinterpret_cast<const uint4*>(src + half + c * 8);
+      const __nv_bfloat16* xs = reinterpret_cast<const __nv_bfloat16*>(&xv);
+      const __nv_bfloat16* ys = reinterpret_cast<const __nv_bfloat16*>(&yv);
+      uint4 lo4, hi4;
+      __nv_bfloat16* los = reinterpret_cast<__nv_bfloat16*>(&lo4);
+      __nv_bfloat16* his = reinterpret_cast<__nv_bfloat16*>(&hi4);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float cs = cs_tab[2 * (c * 8 + e)], sn = cs_tab[2 * (c * 8 + e) + 1];
+        const float x = __bfloat162float(xs[e]), y = __bfloat162float(ys[e]);
+        los[e] = __float2bfloat16_rn(x * cs - y * sn);
+        his[e] = __float2bfloat16_rn(x * sn + y * cs);
+      }
+      if (is_k) {
+        *reinterpret_cast<uint4*>(a.k_cache + new_off + c * 8) = lo4;
+        *reinterpret_cast<uint4*>(a.k_cache + new_off + half + c * 8) = hi4;
+        *reinterpret_cast<uint4*>(new_kv + c * 8) = lo4;
+        *reinterpret_cast<uint4*>(new_kv + half + c * 8) = hi4;
+      } else {
+        *reinterpret_cast<uint4*>(q_tile + dt_off<HD>(g, c)) = lo4;
+        *reinterpret_cast<uint4*>(q_tile + dt_off<HD>(g, c + hc)) = hi4;
+      }
+    }
+  } else {
+    // rotary dimensions that are no multiple of 16: element by element
+    auto q_at = [&](int g, int d) -> __nv_bfloat16* {
+      return reinterpret_cast<__nv_bfloat16*>(q_tile + dt_off<HD>(g, d >> 3)) + (d & 7);
+    };
+    for (int p = tid; p < G * half; p += DT_THREADS) {
+      int g = p / half, i = p - g * half;
+      const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
+      const __nv_bfloat16* hd = qrow + (size_t)(h0 + g) * head_dim;
+      float x = __bfloat162float(hd[i]), y = __bfloat162float(hd[i + half]);
+      *q_at(g, i) = __float2bfloat16_rn(x * cs - y * sn);
+      *q_at(g, i + half) = __float2bfloat16_rn(x * sn + y * cs);
+    }
     const int rest = head_dim - a.rotary_dims;
     for (int p = tid; p < G * rest; p += DT_THREADS) {
       int g = p / rest, d = a.rotary_dims + p - g * rest;
       *q_at(g, d) = qrow[(size_t)(h0 + g) * head_dim + d];
     }
-  }
-  // ---- the new token's key (rotated) and value: to the cache, and kept for this block's stage
-  if (has_new) {
-    const size_t off = (((size_t)pt[p_hi] * n_kv_heads + kvh) * BN_PAGE + new_row) * (size_t)head_dim;
-    const __nv_bfloat16* kraw = qrow + a.k_off + (size_t)kvh * head_dim;
-    const __nv_bfloat16* vraw = qrow + a.v_off + (size_t)kvh * head_dim;
-    for (int i = tid; i < half; i += DT_THREADS) {
-      const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
-      float x = __bfloat162float(kraw[i]), y = __bfloat162float(kraw[i + half]);
-      __nv_bfloat16 k0 = __float2bfloat16_rn(x * cs - y * sn), k1 = __float2bfloat16_rn(x * sn + y * cs);
-      a.k_cache[off + i] = k0;
-      a.k_cache[off + i + half] = k1;
-      new_kv[i] = k0;
-      new_kv[i + half] = k1;
-    }
-    for (int d = a.rotary_dims + tid; d < head_dim; d += DT_THREADS) {
-      a.k_cache[off + d] = kraw[d];
-      new_kv[d] = kraw[d];
-    }
-    for (int d = tid; d < head_dim; d += DT_THREADS) {
-      a.v_cache[off + d] = vraw[d];
-      new_kv[HD + d] = vraw[d];
-    }
-    for (int d = head_dim + tid; d < HD; d += DT_THREADS) {
-      new_kv[d] = __float2bfloat16_rn(0.f);
-      new_kv[HD + d] = __float2bfloat16_rn(0.f);
+    if (has_new) {
+      for (int i = tid; i < half; i += DT_THREADS) {
+        const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
+        float x = __bfloat162float(kraw[i]), y = __bfloat162float(kraw[i + half]);
+        __nv_bfloat16 k0 = __float2bfloat16_rn(x * cs - y * sn), k1 = __float2bfloat16_rn(x * sn + y * cs);
+        a.k_cache[new_off + i] = k0;
+        a.k_cache[new_off + i + half] = k1;
+        new_kv[i] = k0;
+        new_kv[i + half] = k1;
+      }
+      for (int d = a.rotary_dims + tid; d < head_dim; d += DT_THREADS) {
+        a.k_cache[new_off + d] = kraw[d];
+        new_kv[d] = kraw[d];
+      }
+      for (int d = tid; d < head_dim; d += DT_THREADS) {
+        a.v_cache[new_off + d] = vraw[d];
+        new_kv[HD + d] = vraw[d];
+      }
     }
   }
 
@@ -407,21 +455,18 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     for (int w = 0; w < 4; ++w) l += wsc[w * DT_ROWS + tid] * ml_part[(w * DT_ROWS + tid) * 2 + 1];
     ml_fin[tid * 2 + 1] = l;  // rows past G hold zeros: maximum -inf, sum 0
   }
+  __syncthreads();
   for (int i = tid; i < G * head_dim; i += DT_THREADS) {
     int g = i / head_dim, d = i - g * head_dim;
     float acc = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) acc += wsc[w * DT_ROWS + g] * o_part[(size_t)(w * DT_ROWS + g) * OSTRIDE + d];
-    if (clustered) o_fin[g * HD + d] = acc;
-    else if (!alone) a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + blockIdx.z) * head_dim + d] = acc;
-    else o_fin[g * HD + d] = acc;  // the only split of this sequence: normalised below
+    if (alone)  // the only split of this sequence: normalise and store
+      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(acc / ml_fin[g * 2 + 1]);
+    else if (clustered) o_fin[g * HD + d] = acc;
+    else a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + blockIdx.z) * head_dim + d] = acc;
   }
-  __syncthreads();
   if (alone) {
-    for (int i = tid; i < G * head_dim; i += DT_THREADS) {
-      int g = i / head_dim, d = i - g * head_dim;
-      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(o_fin[g * HD + d] / ml_fin[g * 2 + 1]);
-    }
     if (tr) tr[8] = global_timer();
     return;
   }

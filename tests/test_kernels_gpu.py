@@ -458,6 +458,7 @@ def _last_row_attention(q, k, v, scale, window):
     (4, 2, 16, 16, [1, 5, 64, 130], 0), (3, 1, 48, 48, [200, 129, 128], 0), (32, 8, 128, 128, [700, 3, 513], 0),
     (2, 2, 256, 64, [257], 0), (40, 40, 64, 0, [100, 300], 0), (12, 1, 32, 32, [150, 40, 260], 17),
     (40, 40, 128, 128, [3000, 17, 2049], 0), (32, 8, 64, 64, [2303, 1], 0), (8, 2, 128, 128, [5000, 4097], 1024),
+    (4, 2, 64, 40, [70, 200], 0),  # rotary dimensions that are no multiple of 16
 ])
 @pytest.mark.parametrize("splits", [0, 3, 12])
 def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd, lens, window):
