@@ -103,9 +103,12 @@ def _paged_cache(cuda_device, dtype, n_pages, kv, hd, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,KV,hd,theta,pos", [(4, 2, 16, 1e4, [0, 5, 63, 64]), (3, 1, 48, 5e5, [700, 1, 129, 130]),
-                                               (5, 5, 128, 1e6, [4000, 4001, 3, 64])])
-def test_rope_append(cuda_device, dtype, H, KV, hd, theta, pos):
+@pytest.mark.parametrize("H,KV,hd,rd,theta,pos", [(4, 2, 16, 16, 1e4, [0, 5, 63, 64]), (3, 1, 48, 48, 5e5, [700, 1, 129, 130]),
+                                                  (5, 5, 128, 128, 1e6, [4000, 4001, 3, 64]),
+                                                  (3, 3, 64, 32, 1e4, [7, 8, 200, 64]), (2, 1, 64, 40, 1e4, [7, 8, 200, 64])])
+def test_rope_append(cuda_device, dtype, H, KV, hd, rd, theta, pos):
+    """Rotation in place and the cache write; ``rd`` rotary dimensions of ``hd`` (the last case is
+    no multiple of 16 and takes the element-wise kernel in bfloat16 too)."""
     T = len(pos)
     g = torch.Generator().manual_seed(6)
     x = torch.randn(T, (H + 2 * KV) * hd, generator=g).to(DT[dtype]).to(cuda_device)
@@ -118,11 +121,11 @@ def test_rope_append(cuda_device, dtype, H, KV, hd, theta, pos):
     perm = torch.randperm(n_pages, generator=g)[: 3 * per_seq].reshape(3, per_seq).to(torch.int32).to(cuda_device)
     k, v = _paged_cache(cuda_device, dtype, n_pages, KV, hd, 7)
     k0, v0 = k.clone(), v.clone()
-    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(hd)))
-    ops.rope_append(x, H + KV, hd, hd, scale, tok_pos, k_off=H * hd, v_off=(H + KV) * hd, n_kv_heads=KV,
+    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(rd)))
+    ops.rope_append(x, H + KV, hd, rd, scale, tok_pos, k_off=H * hd, v_off=(H + KV) * hd, n_kv_heads=KV,
                     tok_seq=tok_seq, slots=slots, page_table=perm, k_cache=k, v_cache=v)
     heads = x0.double().cpu().numpy().reshape(T, H + 2 * KV, hd)
-    rot = plain_llama.apply_rope(heads[:, : H + KV], pos, theta)
+    rot = plain_llama.apply_rope(heads[:, : H + KV], pos, theta, dims=rd)
     got = x.double().cpu().numpy().reshape(T, H + 2 * KV, hd)
     t_ = tol(dtype, 2e-6, 2e-2)
     assert np.abs(got[:, : H + KV] - rot).max() < t_
