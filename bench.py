@@ -104,8 +104,8 @@ class ClockSampler:
 
 
 def reference_arm():
-    """The reference is a C11 project with a Makefile and no Python packaging; the prescribed
-    offline ``pip install --target baseline/_ref /root/reference`` therefore installs nothing."""
+    """The reference is a C11 project with a Makefile and no Python packaging; an offline
+    ``pip install --target baseline/_ref`` of its source tree therefore installs nothing."""
     print(json.dumps({"impl": "reference",
                       "unavailable": "artalis-io/bitnet.c is a C/Makefile project without setup.py or pyproject.toml: "
                                      "the offline pip install into baseline/_ref fails, and it has no safetensors or "
