@@ -50,7 +50,10 @@
 // the next kernel in the stream fits on the same SM and fetches its first weight tiles while this
 // kernel's blocks are finishing (programmatic dependent launch).
 #define TC_STAGES_FOR(MP) ((MP) == 16 ? 6 : ((MP) == 32 ? 5 : 4))
-#define TC_THREADS 192
+// Threads of a block: producer warp, MMA warp, and four epilogue warps (one per TMEM lane
+// quadrant), eight for the widest accumulator (two warps share a quadrant, half the columns each).
+#define TC_EPI_FOR(MP) ((MP) == 64 ? 256 : 128)
+#define TC_THREADS_FOR(MP) (64 + TC_EPI_FOR(MP))
 
 #define TC_ERR_FULL_WAIT 1
 #define TC_ERR_EMPTY_WAIT 2
@@ -131,6 +134,23 @@ __device__ __forceinline__ float4 sum_dsmem4(unsigned local_addr, int C) {
   for (int q = 1; q < 8; ++q) { s.x += p[q].x; s.y += p[q].y; s.z += p[q].z; s.w += p[q].w; }
   return s;
 }
+// The loads of such a sum alone, so that the loads of two sums can be in flight together.
+__device__ __forceinline__ void load_dsmem4_set(unsigned local_addr, int C, float4* p) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) p[q] = q < C ? ld_dsmem4(local_addr, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+__device__ __forceinline__ float4 sum_set(const float4* p) {
+  float4 s = p[0];
+#pragma unroll
+  for (int q = 1; q < 8; ++q) { s.x += p[q].x; s.y += p[q].y; s.z += p[q].z; s.w += p[q].w; }
+  return s;
+}
+// Four consecutive floats of the tile summed over the cluster; a cluster of one reads its own
+// shared memory directly.
+__device__ __forceinline__ float4 part4(const float* partial, unsigned pbase, int off, int C) {
+  if (C == 1) return *reinterpret_cast<const float4*>(partial + off);
+  return sum_dsmem4(pbase + (unsigned)off * 4, C);
+}
 __device__ __forceinline__ void store4(void* out, int out_dtype, size_t idx, float4 v, int valid) {
   // idx..idx+3 are consecutive elements; `valid` of them exist
   if (valid == 4 && out_dtype == BN_BF16 && (idx & 3) == 0) {
@@ -148,13 +168,14 @@ __device__ __forceinline__ void store4(void* out, int out_dtype, size_t idx, flo
 }
 
 template <int MP>  // batch columns of the accumulator: 16, 32 or 64
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(TC_THREADS_FOR(MP))
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
   constexpr int B_BYTES = MP * TC_BK * 2;      // 2, 4 or 8 KB
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
+  constexpr int EPI = TC_EPI_FOR(MP);          // epilogue threads
   constexpr int PSTRIDE = TC_BM + 4;           // floats per batch column of the partial tile in shared memory
   static_assert(MP * PSTRIDE * 4 <= TC_STAGES * STAGE_BYTES, "the partial tile reuses the ring");
   constexpr unsigned TMEM_COLS = MP < 32 ? 32 : MP;
@@ -167,7 +188,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
   unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
   float* row_scale = (float*)(tmem_slot + 2);  // [64]: 1 / rms of the input rows (when row_ss is given)
-  float* ss_chunk = row_scale + 64;            // [128 / MP][MP]: partial sums on the way there
+  float* ss_chunk = row_scale + 64;            // [EPI / MP][MP]: partial sums on the way there
   float* partial = (float*)base;  // [MP][PSTRIDE]: partial[m][row], valid once all MMAs have read the ring
   float* item_sq = partial + MP * PSTRIDE;  // mode 3: the sum of squares of each epilogue item
   static_assert((MP * PSTRIDE + 32 * 64) * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and item sums reuse the ring");
@@ -254,17 +275,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     if (a.row_ss != nullptr) {
-      // the scale each input row still lacks, from the parts its producer left: the 128 threads
-      // share a row's parts in 128 / MP chunks, then one thread per row adds the chunks in order
+      // the scale each input row still lacks, from the parts its producer left: the epilogue threads
+      // share a row's parts in EPI / MP chunks, then one thread per row adds the chunks in order
       pdl_wait();
-      constexpr int CH = 128 / MP;
+      constexpr int CH = EPI / MP;
       const int t = tid - 64, m = t % MP, c = t / MP;
       const int per = (a.ss_parts + CH - 1) / CH;
       float ss = 0.f;
       if (m < a.M)
         for (int p = c * per; p < min(a.ss_parts, (c + 1) * per); ++p) ss += a.row_ss[(size_t)p * a.ss_stride + m];
       ss_chunk[c * MP + m] = ss;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI) : "memory");
       if (t < a.M) {
         float tot = 0.f;
 #pragma unroll
@@ -277,21 +298,25 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (!ok) s_failed = 1;
       s_acc_ok = ok;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(EPI) : "memory");
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float v[MP];
+    if (tracing && tid == 64) a.trace[7] = global_timer();  // accumulator complete
+    // with eight epilogue warps, warps 2-5 take the first half of the columns and 6-9 the second
+    constexpr int COLS = MP * 128 / EPI;
+    const int c0 = ((warp - 2) >> 2) * COLS;
+    float v[COLS];
     if (s_acc_ok) {
 #pragma unroll
-      for (int c = 0; c < MP; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + c, v + c);
+      for (int c = 0; c < COLS; c += 16) tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + c0 + c, v + c);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     } else {
 #pragma unroll
-      for (int c = 0; c < MP; ++c) v[c] = 0.f;
+      for (int c = 0; c < COLS; ++c) v[c] = 0.f;
     }
     // every MMA has completed, so nothing reads the ring any more: it now holds the partial tile,
     // batch column by batch column (consecutive threads write consecutive addresses)
 #pragma unroll
-    for (int c = 0; c < MP; ++c) partial[c * PSTRIDE + row] = v[c];
+    for (int c = 0; c < COLS; ++c) partial[(c0 + c) * PSTRIDE + row] = v[c];
   }
 
   // ---- all blocks of the cluster have their partial tiles in shared memory
@@ -307,26 +332,63 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const unsigned pbase = smem_u32(partial);
     if (a.mode == 0) {
       // item = (batch row m, group of four weight rows): four consecutive output columns
-      const int groups = rows / 4;
-      for (int e = t; e < groups * a.M; e += 128) {
-        int m = e / groups, rl = (e - m * groups) * 4;
-        int n = tile * TC_BM + r0 + rl;
-        if (n >= a.N) continue;
-        float4 sum = sum_dsmem4(pbase + (unsigned)((m * PSTRIDE + r0 + rl) * 4), C);
-        if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
-        store4(a.out, a.out_dtype, (size_t)m * a.ldo + n, sum, min(4, a.N - n));
+      const int groups = rows / 4, total = groups * a.M;
+      if constexpr (MP == 16) {
+        for (int e = t; e < total; e += EPI) {
+          int m = e / groups, rl = (e - m * groups) * 4;
+          int n = tile * TC_BM + r0 + rl;
+          if (n >= a.N) continue;
+          float4 sum = part4(partial, pbase, m * PSTRIDE + r0 + rl, C);
+          if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
+          store4(a.out, a.out_dtype, (size_t)m * a.ldo + n, sum, min(4, a.N - n));
+        }
+      } else {
+      // wider accumulators: two items per turn, the loads of both in flight together
+      for (int e = t; e < total; e += 2 * EPI) {
+        int m[2], n[2];
+        float4 sum[2];
+        if (C == 1) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int eu = min(e + EPI * u, total - 1);
+            m[u] = eu / groups;
+            const int rl = (eu - m[u] * groups) * 4;
+            n[u] = tile * TC_BM + r0 + rl;
+            sum[u] = *reinterpret_cast<const float4*>(partial + m[u] * PSTRIDE + r0 + rl);
+          }
+        } else {
+          float4 p[2][8];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int eu = min(e + EPI * u, total - 1);
+            m[u] = eu / groups;
+            const int rl = (eu - m[u] * groups) * 4;
+            n[u] = tile * TC_BM + r0 + rl;
+            load_dsmem4_set(pbase + (unsigned)((m[u] * PSTRIDE + r0 + rl) * 4), C, p[u]);
+          }
+          sum[0] = sum_set(p[0]);
+          sum[1] = sum_set(p[1]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (e + EPI * u >= total || n[u] >= a.N) continue;
+          float4 v = sum[u];
+          if (a.row_ss != nullptr) { const float rs = row_scale[m[u]]; v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs; }
+          store4(a.out, a.out_dtype, (size_t)m[u] * a.ldo + n[u], v, min(4, a.N - n[u]));
+        }
+      }
       }
     } else if (a.mode == 3) {
       // out is the float32 residual [M, ldo]: add, write back, hand on residual * gain, and leave
       // this slice's sum of squares per row (items in a fixed order, then one thread per row)
       const int groups = rows / 4;
       float* res = (float*)a.out;
-      for (int e = t; e < groups * a.M; e += 128) {
+      for (int e = t; e < groups * a.M; e += EPI) {
         int m = e / groups, rl = (e - m * groups) * 4;
         int n = tile * TC_BM + r0 + rl;
         float sq = 0.f;
         if (n < a.N) {
-          float4 sum = sum_dsmem4(pbase + (unsigned)((m * PSTRIDE + r0 + rl) * 4), C);
+          float4 sum = part4(partial, pbase, m * PSTRIDE + r0 + rl, C);
           if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
           const int valid = min(4, a.N - n);
           float v[4] = {sum.x, sum.y, sum.z, sum.w};
@@ -345,8 +407,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         item_sq[e] = sq;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int m = t; m < a.M; m += 128) {
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI) : "memory");
+      for (int m = t; m < a.M; m += EPI) {
         float ss = 0.f;
         for (int gq = 0; gq < groups; ++gq) ss += item_sq[m * groups + gq];
         a.ss_out[(size_t)(tile * C + rank) * a.ss_out_stride + m] = ss;
@@ -355,13 +417,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       // rows 16j..16j+7 of a tile are gate rows, rows 16j+8..16j+15 the up rows of the same indices;
       // item = (batch row m, four gate rows and their up rows): four consecutive activations
       const int groups = rows / 8;
-      for (int e = t; e < groups * a.M; e += 128) {
+      for (int e = t; e < groups * a.M; e += EPI) {
         int m = e / groups, gq = e - m * groups;
         int rg = r0 + (gq >> 1) * 16 + (gq & 1) * 4;  // first of the four gate rows within the tile
         int n = tile * TC_BM + rg;
         if (n >= a.N) continue;
-        unsigned ag = pbase + (unsigned)((m * PSTRIDE + rg) * 4);
-        float4 g = sum_dsmem4(ag, C), u = sum_dsmem4(ag + 8 * 4, C);
+        float4 g = part4(partial, pbase, m * PSTRIDE + rg, C), u = part4(partial, pbase, m * PSTRIDE + rg + 8, C);
         if (a.row_ss != nullptr) {
           const float rs = row_scale[m];
           g.x *= rs; g.y *= rs; g.z *= rs; g.w *= rs;
@@ -428,7 +489,7 @@ template <int MP>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int cluster, int tiles,
                      cudaStream_t stream) {
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
-  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + (64 + 128) * 4 + 1024;
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + (64 + 256) * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -437,7 +498,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs&
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(cluster, tiles);
-  cfg.blockDim = dim3(TC_THREADS);
+  cfg.blockDim = dim3(TC_THREADS_FOR(MP));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
