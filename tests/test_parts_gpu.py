@@ -10,8 +10,8 @@ import bitnet_c_b200 as bn
 from bitnet_c_b200.config import (AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NoPositionSpec, RmsNormSpec,
                                   RotarySpec, ScheduleEntry)
 from bitnet_c_b200.engine import Model, SeqStep, pack_step
-from bitnet_c_b200.parts import (BuildContext, Mixer, ParamSpec, StateRequest, build_part, register_mixer,
-                                 unregister)
+from bitnet_c_b200.parts import (BuildContext, FeedForward, Mixer, ParamSpec, Position, StateRequest, build_part,
+                                 register_ffn, register_mixer, register_position, unregister)
 import plain_llama
 from helpers import bf16_bound
 
@@ -210,6 +210,116 @@ def test_a_new_mixer_with_state_needs_no_change_to_the_library(cuda_device):
             compare(replay(model, cache, steps), ref, lambda r: 2e-4, "toy mixer")
     finally:
         unregister("mixer", "toy_decay_mix")
+
+
+@dataclass(frozen=True)
+class RoutedToySpec:
+    """A toy feed-forward with routing: every token goes to the expert with the largest router
+    logit, weighted by that expert's softmax probability; an expert is W_out relu(W_in h)."""
+    width: int
+    intermediate: int
+    n_experts: int
+    kind: str = "toy_routed"
+
+
+@dataclass(frozen=True)
+class PositionScaleSpec:
+    """A toy position encoding: the heads of a token at position p are divided by 1 + rate * p."""
+    head_dim: int
+    rate: float
+    kind: str = "toy_position_scale"
+
+
+def test_a_routed_feed_forward_and_another_position_encoding_need_no_change_to_the_library(cuda_device):
+    """Both are defined here, registered, built by the model from its spec like any other part,
+    and stepped whole, token by token and in unequal batches.  The attention mixer finds no fast
+    paths on this position encoding and takes its general ones."""
+    @register_ffn("toy_routed")
+    class RoutedToy(FeedForward):
+        def params(self):
+            s = self.spec
+            return {"router": ParamSpec((s.n_experts, s.width)), "w_in": ParamSpec((s.n_experts * s.intermediate, s.width)),
+                    "w_out": ParamSpec((s.n_experts * s.width, s.intermediate))}
+
+        def bind(self, tensors):
+            s = self.spec
+            self.router = tensors["router"].float()
+            self.w_in = tensors["w_in"].float().reshape(s.n_experts, s.intermediate, s.width)
+            self.w_out = tensors["w_out"].float().reshape(s.n_experts, s.width, s.intermediate)
+
+        def forward(self, h, ctx):
+            hf = h.float()
+            prob = torch.softmax(hf @ self.router.t(), dim=-1)
+            top = prob.argmax(dim=-1)
+            out = torch.zeros_like(hf)
+            for e in range(self.spec.n_experts):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel():
+                    x = hf[rows]
+                    out[rows] = (torch.relu(x @ self.w_in[e].t()) @ self.w_out[e].t()) * prob[rows, e][:, None]
+            return out.to(h.dtype)
+
+    @register_position("toy_position_scale")
+    class PositionScale(Position):
+        graph_safe = True
+
+        def rotate(self, x, n_heads, head_dim, ctx):
+            scale = 1.0 / (1.0 + self.spec.rate * ctx.tok_pos.to(torch.float32))
+            part = x[:, : n_heads * head_dim]
+            part.copy_((part.float() * scale[:, None]).to(x.dtype))
+
+    try:
+        width, E, inter = 32, 3, 40
+        norm = RmsNormSpec(width=width, eps=1e-5)
+        attn = AttentionSpec(width=width, n_heads=2, n_kv_heads=1, head_dim=16, position=PositionScaleSpec(16, 0.05))
+        blocks = (BlockSpec(mixer=attn, ffn=RoutedToySpec(width, inter, E), mixer_norm=norm, ffn_norm=norm),
+                  BlockSpec(mixer=attn, ffn=GatedMlpSpec(width=width, intermediate=48), mixer_norm=norm, ffn_norm=norm))
+        spec = ModelSpec(vocab_size=50, width=width, blocks=blocks, schedule=(ScheduleEntry(0), ScheduleEntry(1)),
+                         final_norm=norm, max_positions=256)
+        model = Model(spec, dtype="float32", device=cuda_device)
+        assert "blocks.0.ffn.router" in model.parameter_table()
+        w = random_bind(model, 9, scale=0.12)
+        # a decisive router: top-1 routing is a discontinuous function, and the comparison with the
+        # plain implementation only means something where rounding cannot flip a choice
+        model.blocks[0].ffn.router *= 16
+        w["blocks.0.ffn.router"] = w["blocks.0.ffn.router"] * 16
+
+        def plain(tokens):
+            T = len(tokens)
+            x = w["embedding.table"][np.asarray(tokens)]
+            pos_scale = 1.0 / (1.0 + 0.05 * np.arange(T))
+            for i, b in enumerate(spec.blocks):
+                p = f"blocks.{i}."
+                h = plain_llama.rmsnorm(x, w[p + "mixer_norm.weight"], 1e-5)
+                q = (h @ w[p + "mixer.q"].T).reshape(T, 2, 16) * pos_scale[:, None, None]
+                k = (h @ w[p + "mixer.k"].T).reshape(T, 1, 16) * pos_scale[:, None, None]
+                v = (h @ w[p + "mixer.v"].T).reshape(T, 1, 16)
+                x = x + plain_llama.attention(q, k, v, 0.25).reshape(T, 32) @ w[p + "mixer.o"].T
+                h = plain_llama.rmsnorm(x, w[p + "ffn_norm.weight"], 1e-5)
+                if b.ffn.kind == "toy_routed":
+                    logits = h @ w[p + "ffn.router"].T
+                    prob = np.exp(logits - logits.max(-1, keepdims=True))
+                    prob /= prob.sum(-1, keepdims=True)
+                    w_in = w[p + "ffn.w_in"].reshape(E, inter, width)
+                    w_out = w[p + "ffn.w_out"].reshape(E, width, inter)
+                    y = np.zeros_like(h)
+                    for t in range(T):
+                        e = int(np.argmax(prob[t]))
+                        y[t] = (np.maximum(h[t] @ w_in[e].T, 0) @ w_out[e].T) * prob[t, e]
+                    x = x + y
+                else:
+                    x = x + plain_llama.swiglu(h, w[p + "ffn.gate"], w[p + "ffn.up"], w[p + "ffn.down"])
+            return plain_llama.rmsnorm(x, w["final_norm.weight"], 1e-5) @ w["head.weight"].T
+
+        from helpers import compare, replay, trace_batches, trace_tail, trace_whole
+        toks = {"p": np.random.default_rng(3).integers(0, 50, 90).tolist(), "q": [9, 8, 7, 6, 5]}
+        ref = {k: plain(v) for k, v in toks.items()}
+        cache = model.new_cache(max_tokens=512, max_seqs=2)
+        for steps in (trace_whole(toks), trace_tail(toks, 32), trace_batches([{"p": (toks["p"], 12), "q": (toks["q"], 4)}])):
+            compare(replay(model, cache, steps), ref, lambda r: 2e-4, "toy routed feed-forward and position encoding")
+    finally:
+        unregister("ffn", "toy_routed")
+        unregister("position", "toy_position_scale")
 
 
 def test_norms_fused_into_products_agree_with_norm_kernels(cuda_device, monkeypatch):
