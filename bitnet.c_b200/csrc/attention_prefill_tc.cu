@@ -8,7 +8,8 @@
 //     S_j = Q K_j^T          M=128, N=64,  K=head size   -> tensor memory, two buffers
 //     P_j = exp2(S_j * scale * log2(e) - m)  in float32 by 128 threads, one query row each (the
 //                             row of the accumulator is the thread's own TMEM lane: no shuffles),
-//                             rounded to bfloat16 into shared memory (two buffers)
+//                             rounded to bfloat16 and written back into tensor memory, over the
+//                             first half of the columns S_j came from
 //     O  += P_j V_j          M=128, N=head size, K=64    -> tensor memory
 // Roles of the 192 threads: warp 0 requests Q once and the pages through a ring of stages (TMA,
 // 128-byte swizzle); one thread of warp 1 issues the MMAs, S_{j+1} ahead of P_j V_j so that the
@@ -17,7 +18,10 @@
 // maximum exceeds it by more than 8 (a factor 256, harmless in float32 and bfloat16); then the
 // row's O is rescaled in tensor memory.  Sums and maxima are float32; the result is O / sum.
 //
-// V is the MMA's B operand with the head dimension contiguous (MN-major); K, Q and P are K-major.
+// P is the second product's A operand read from tensor memory (two bfloat16 per 32-bit column);
+// the tensor pipe runs its instructions in order, so S_{j+2}, issued after P_j V_j, cannot
+// overwrite P_j before it has been used.  V is that product's B operand with the head dimension
+// contiguous (MN-major); K and Q are K-major.
 // The new tokens' own keys and values must already be in the cache, so the same kernel serves
 // whole prompts, pieces of prompts and ragged batches (a table gives each block its sequence and
 // first row).  Head sizes in steps of 16 up to 128 run on the instantiation for 64 or 128: columns
@@ -77,6 +81,15 @@ __device__ __forceinline__ void pt_mma(unsigned tmem_d, unsigned long long da, u
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// The same with the A operand in tensor memory (lane = row, two bfloat16 of k per 32-bit column).
+__device__ __forceinline__ void pt_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long db, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void pt_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -159,7 +172,7 @@ __device__ __forceinline__ bool pt_wait(unsigned bar, unsigned parity, volatile 
   }
 }
 
-template <int HD, int STAGES, int PBUFS>
+template <int HD, int STAGES>
 __global__ void __launch_bounds__(PT_THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PtArgs a) {
@@ -171,7 +184,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   constexpr int Q_BYTES = BOXES * Q_BOX;
   constexpr int PAGE_BYTES = BOXES * KV_BOX;       // one page of keys (or values) of one head
   constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
-  constexpr int P_BYTES = PT_ROWS * 128;           // 128 rows x 64 keys of bfloat16
   constexpr unsigned TMEM_COLS = 256;              // S0 at 0, S1 at 64, O at 128
   constexpr unsigned O_COL = 128;
   // D float32, A and B bfloat16, M = 128; scores: N = 64, both operands K-major; output: N = HD, B MN-major
@@ -182,14 +194,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // base of the block's window: the swizzle is a function of the address.
   unsigned char* q_smem = smem_raw;
   unsigned char* kv_smem = q_smem + Q_BYTES;                  // STAGES x (keys page, values page)
-  unsigned char* p_smem = kv_smem + STAGES * STAGE_BYTES;     // PBUFS buffers
-  unsigned long long* bars = (unsigned long long*)(p_smem + PBUFS * P_BYTES);
-  // barriers: q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], s_empty[2], p_full[2], p_empty[2], pv_done
+  unsigned long long* bars = (unsigned long long*)(kv_smem + STAGES * STAGE_BYTES);
+  // barriers: q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], p_full[2], pv_done s_empty[2], p_full[2], p_empty[2], pv_done
   const unsigned bar0 = smem_u32(bars);
   const unsigned q_full = bar0, k_full0 = bar0 + 8, k_empty0 = k_full0 + 8 * STAGES, v_full0 = k_empty0 + 8 * STAGES,
                  v_empty0 = v_full0 + 8 * STAGES, s_full0 = v_empty0 + 8 * STAGES,
-                 s_empty0 = s_full0 + 16, p_full0 = s_empty0 + 16, p_empty0 = p_full0 + 16, pv_done = p_empty0 + 16;
-  unsigned* tmem_slot = (unsigned*)(bars + 4 * STAGES + 10);
+                 p_full0 = s_full0 + 16, pv_done = p_full0 + 16;
+  unsigned* tmem_slot = (unsigned*)(bars + 4 * STAGES + 6);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -225,9 +236,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full0 + 8 * b, 1);
-      mbar_init(s_empty0 + 8 * b, 4);  // one arrival per softmax warp
-      mbar_init(p_full0 + 8 * b, 4);
-      mbar_init(p_empty0 + 8 * b, 1);
+      mbar_init(p_full0 + 8 * b, 4);  // one arrival per softmax warp
     }
     mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -276,7 +285,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const bool issuer = pt_elect_one();
     const unsigned tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
     bool ok = __all_sync(0xffffffffu, pt_wait(q_full, 0, failed, a.status));
-    const unsigned sq = smem_u32(q_smem), sp = smem_u32(p_smem);
+    const unsigned sq = smem_u32(q_smem);
     const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && issuer;
     for (int j = 0; ok && j <= n_tiles; ++j) {
       if (j < n_tiles) {
@@ -286,10 +295,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ok = __all_sync(0xffffffffu, pt_wait(k_full0 + 8 * s, (unsigned)(j / STAGES) & 1u, failed, a.status));
         if (!ok) break;
         if (trs) a.trace[j * 12 + 9] = global_timer();
-        if (j >= 2) {
-          ok = __all_sync(0xffffffffu, pt_wait(s_empty0 + 8 * b, (unsigned)((j >> 1) - 1) & 1u, failed, a.status));
-          if (!ok) break;
-        }
+        // (S_j reuses the buffer of S_{j-2} and P_{j-2}: P_{j-2} V_{j-2} was issued before and the
+        // tensor pipe keeps the order)
         if (trs) a.trace[j * 12 + 10] = global_timer();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned sk = smem_u32(kv_smem + s * STAGE_BYTES);
@@ -307,8 +314,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       if (j >= 1) {
         // O += P_{j-1} V_{j-1}
-        const int i = j - 1, s = i % STAGES, b = i % PBUFS;
-        ok = __all_sync(0xffffffffu, pt_wait(p_full0 + 8 * b, (unsigned)(i / PBUFS) & 1u, failed, a.status) &&
+        const int i = j - 1, s = i % STAGES, b = i & 1;
+        ok = __all_sync(0xffffffffu, pt_wait(p_full0 + 8 * b, (unsigned)(i >> 1) & 1u, failed, a.status) &&
                                          pt_wait(v_full0 + 8 * s, (unsigned)(i / STAGES) & 1u, failed, a.status));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -318,10 +325,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < PT_KEYS / 16; ++kk)
-            pt_mma(tbase + O_COL, pt_desc_k(sp + b * P_BYTES + kk * 32), pt_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
-                   (i | kk) ? 1u : 0u);
+            pt_mma_ts(tbase + O_COL, tbase + b * PT_KEYS + kk * 8, pt_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
+                      (i | kk) ? 1u : 0u);
           pt_commit(v_empty0 + 8 * s);    // the value stage may be refilled
-          pt_commit(p_empty0 + 8 * b);    // the P buffer may be rewritten
           pt_commit(pv_done);             // O holds the pages up to i
           if (tr) a.trace[i * 12 + 8] = global_timer();
         }
@@ -348,9 +354,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       float s[PT_KEYS];
       pt_tmem_ld64(lane_addr + b * PT_KEYS, s);
       if (tr) a.trace[j * 12 + 2] = global_timer();
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty0 + 8 * b);  // the scores are in registers
       // mask, then the maximum of the raw scores (the scale is positive); four chains, not one
       const int k0 = tile * PT_KEYS;
       if (!(k0 >= qlo && k0 + PT_KEYS - 1 <= qpos)) {
@@ -394,16 +397,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       if (tr) a.trace[j * 12 + 3] = global_timer();
-      // P as bfloat16 into its buffer, once the product that read the buffer before is done
-      const int pb = j % PBUFS, use = j / PBUFS;
-      if (use >= 1 && !pt_wait(p_empty0 + 8 * pb, (unsigned)(use - 1) & 1u, failed, a.status)) { ok = false; break; }
+      // P as bfloat16 into tensor memory, two keys per column, over the columns S came from
       if (tr) a.trace[j * 12 + 4] = global_timer();
-      unsigned char* prow = p_smem + pb * P_BYTES + r * 128;
+      {
+        float pk[32];
 #pragma unroll
-      for (int c = 0; c < PT_KEYS / 8; ++c) {
-        const float* p = s + c * 8;
-        uint4 w = make_uint4(pt_pack(p[0], p[1]), pt_pack(p[2], p[3]), pt_pack(p[4], p[5]), pt_pack(p[6], p[7]));
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
+        for (int c = 0; c < 32; ++c) pk[c] = __uint_as_float(pt_pack(s[2 * c], s[2 * c + 1]));
+        pt_tmem_st32(lane_addr + b * PT_KEYS, pk);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       if (tile * PT_KEYS + PT_KEYS - 1 > seq_last) {
         // the page holds rows behind the sequence's last position: their weights are zero, but zero
@@ -414,11 +415,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           int row = first + e / (HD / 8), c = e % (HD / 8);
           *reinterpret_cast<uint4*>(sv + (c >> 3) * KV_BOX + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before the MMA reads the cleared rows
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and cleared rows) before the MMA reads them
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full0 + 8 * pb);
+      if (lane == 0) mbar_arrive(p_full0 + 8 * b);
       if (tr) a.trace[j * 12 + 5] = global_timer();
     }
     // ---- epilogue: O / sum -> out
@@ -476,20 +477,19 @@ extern "C" int bn_attention_prefill_tc_trace_read(unsigned long long* host) {
   return cudaMemcpy(host, g_pt_trace, PT_TRACE_TILES * 12 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
 
-template <int HD, int STAGES, int PBUFS>
+template <int HD, int STAGES>
 static int launch_pt(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PtArgs& a, int n_tiles,
                      cudaStream_t stream) {
-  size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)STAGES * 2 * PT_KEYS * HD * 2 + PBUFS * PT_ROWS * 128 +
-                (4 * STAGES + 10) * 8 + 16;
+  size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)STAGES * 2 * PT_KEYS * HD * 2 + (4 * STAGES + 6) * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, STAGES, PBUFS>,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
   dim3 grid(n_tiles, a.n_heads);
-  BN_LAUNCH((attention_prefill_tc_kernel<HD, STAGES, PBUFS>), grid, PT_THREADS, smem, stream, mq, mk, mv, a);
+  BN_LAUNCH((attention_prefill_tc_kernel<HD, STAGES>), grid, PT_THREADS, smem, stream, mq, mk, mv, a);
   return BN_OK;
 }
 
@@ -525,8 +525,8 @@ extern "C" int bn_attention_prefill_tc(const void* q, int q_stride, int n_tokens
   a.pt_stride = pt_stride; a.status = status;
   a.trace = nullptr;
   if (g_pt_trace_armed) { a.trace = g_pt_trace; g_pt_trace_armed = false; }
-  // shared memory per block: 96 KB and 112 KB, so that two blocks share an SM and one block's
-  // softmax overlaps the other's products
-  if (head_dim <= 64) return launch_pt<64, 3, 2>(mq, mk, mv, a, n_tiles, stream);
-  return launch_pt<128, 2, 1>(mq, mk, mv, a, n_tiles, stream);
+  // shared memory per block: 64 KB and 96 KB, so that two blocks share an SM (tensor memory
+  // allows no more: 256 columns each) and one block's softmax overlaps the other's products
+  if (head_dim <= 64) return launch_pt<64, 3>(mq, mk, mv, a, n_tiles, stream);
+  return launch_pt<128, 2>(mq, mk, mv, a, n_tiles, stream);
 }
