@@ -172,7 +172,7 @@ __device__ __forceinline__ bool pt_wait(unsigned bar, unsigned parity, volatile 
   }
 }
 
-template <int HD, int STAGES>
+template <int HD, int KS, int VS>
 __global__ void __launch_bounds__(PT_THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PtArgs a) {
@@ -183,7 +183,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   constexpr int KV_BOX = PT_KEYS * 128;            // 8 KB: 64 keys x 64 dimensions
   constexpr int Q_BYTES = BOXES * Q_BOX;
   constexpr int PAGE_BYTES = BOXES * KV_BOX;       // one page of keys (or values) of one head
-  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
   constexpr unsigned TMEM_COLS = 256;              // S0 at 0, S1 at 64, O at 128
   constexpr unsigned O_COL = 128;
   // D float32, A and B bfloat16, M = 128; scores: N = 64, both operands K-major; output: N = HD, B MN-major
@@ -193,14 +192,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // The block has no static shared memory, so the dynamic part starts at the (1024-byte aligned)
   // base of the block's window: the swizzle is a function of the address.
   unsigned char* q_smem = smem_raw;
-  unsigned char* kv_smem = q_smem + Q_BYTES;                  // STAGES x (keys page, values page)
-  unsigned long long* bars = (unsigned long long*)(kv_smem + STAGES * STAGE_BYTES);
-  // barriers: q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], p_full[2], pv_done s_empty[2], p_full[2], p_empty[2], pv_done
+  unsigned char* k_smem = q_smem + Q_BYTES;                   // KS pages of keys
+  unsigned char* v_smem = k_smem + KS * PAGE_BYTES;           // VS pages of values
+  unsigned long long* bars = (unsigned long long*)(v_smem + VS * PAGE_BYTES);
+  // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], pv_done
   const unsigned bar0 = smem_u32(bars);
-  const unsigned q_full = bar0, k_full0 = bar0 + 8, k_empty0 = k_full0 + 8 * STAGES, v_full0 = k_empty0 + 8 * STAGES,
-                 v_empty0 = v_full0 + 8 * STAGES, s_full0 = v_empty0 + 8 * STAGES,
+  const unsigned q_full = bar0, k_full0 = bar0 + 8, k_empty0 = k_full0 + 8 * KS, v_full0 = k_empty0 + 8 * KS,
+                 v_empty0 = v_full0 + 8 * VS, s_full0 = v_empty0 + 8 * VS,
                  p_full0 = s_full0 + 16, pv_done = p_full0 + 16;
-  unsigned* tmem_slot = (unsigned*)(bars + 4 * STAGES + 6);
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * KS + 2 * VS + 6);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -228,9 +228,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tma_prefetch_map(&map_k);
     tma_prefetch_map(&map_v);
     mbar_init(q_full, 1);
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < KS; ++s) {
       mbar_init(k_full0 + 8 * s, 1);
       mbar_init(k_empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < VS; ++s) {
       mbar_init(v_full0 + 8 * s, 1);
       mbar_init(v_empty0 + 8 * s, 1);
     }
@@ -260,22 +262,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tma_load_2d(smem_u32(q_smem + bx * Q_BOX), &map_q, q_full, h * head_dim + bx * 64, start + row0);
       // Keys and values have rings of their own: a key stage is free as soon as the scores that
       // read it are done, a value stage only after the output product, one softmax later.  The
-      // order of the requests is the order in which the stages come free: K(t+1), then V(t).
+      // order of the requests is the order in which the stages come free: K(t + KS - 1), then V(t).
       auto request = [&](int j, bool values) -> bool {
-        const int s = j % STAGES, round = j / STAGES;
+        const int n = values ? VS : KS, s = j % n, round = j / n;
         const unsigned empty = (values ? v_empty0 : k_empty0) + 8 * s, bar = (values ? v_full0 : k_full0) + 8 * s;
         const int page = __ldg(pt + tile_lo + j);  // asked for before the wait, needed after it
         if (round > 0 && !pt_wait(empty, (unsigned)(round - 1) & 1u, failed, a.status)) return false;
-        const unsigned dst = smem_u32(kv_smem + s * STAGE_BYTES) + (values ? PAGE_BYTES : 0);
+        const unsigned dst = smem_u32((values ? v_smem : k_smem) + s * PAGE_BYTES);
         mbar_expect_tx(bar, PAGE_BYTES);
 #pragma unroll
         for (int bx = 0; bx < BOXES; ++bx)
           tma_load_3d(dst + bx * KV_BOX, values ? &map_v : &map_k, bar, bx * 64, kvh * BN_PAGE, page);
         return true;
       };
-      bool ok = request(0, false);
+      bool ok = true;
+      for (int j = 0; ok && j < min(KS - 1, n_tiles); ++j) ok = request(j, false);
       for (int t = 0; ok && t < n_tiles; ++t) {
-        if (t + 1 < n_tiles) ok = request(t + 1, false);
+        if (t + KS - 1 < n_tiles) ok = request(t + KS - 1, false);
         if (ok) ok = request(t, true);
       }
     }
@@ -290,16 +293,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int j = 0; ok && j <= n_tiles; ++j) {
       if (j < n_tiles) {
         // S_j = Q K_j^T into score buffer j & 1
-        const int s = j % STAGES, b = j & 1;
+        const int s = j % KS, b = j & 1;
         const bool trs = tracing && j < PT_TRACE_TILES;
-        ok = __all_sync(0xffffffffu, pt_wait(k_full0 + 8 * s, (unsigned)(j / STAGES) & 1u, failed, a.status));
+        ok = __all_sync(0xffffffffu, pt_wait(k_full0 + 8 * s, (unsigned)(j / KS) & 1u, failed, a.status));
         if (!ok) break;
         if (trs) a.trace[j * 12 + 9] = global_timer();
         // (S_j reuses the buffer of S_{j-2} and P_{j-2}: P_{j-2} V_{j-2} was issued before and the
         // tensor pipe keeps the order)
         if (trs) a.trace[j * 12 + 10] = global_timer();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned sk = smem_u32(kv_smem + s * STAGE_BYTES);
+        const unsigned sk = smem_u32(k_smem + s * PAGE_BYTES);
         if (issuer) {
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks)
@@ -314,14 +317,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       if (j >= 1) {
         // O += P_{j-1} V_{j-1}
-        const int i = j - 1, s = i % STAGES, b = i & 1;
+        const int i = j - 1, s = i % VS, b = i & 1;
         ok = __all_sync(0xffffffffu, pt_wait(p_full0 + 8 * b, (unsigned)(i >> 1) & 1u, failed, a.status) &&
-                                         pt_wait(v_full0 + 8 * s, (unsigned)(i / STAGES) & 1u, failed, a.status));
+                                         pt_wait(v_full0 + 8 * s, (unsigned)(i / VS) & 1u, failed, a.status));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool tr = tracing && i < PT_TRACE_TILES;
         if (tr) a.trace[i * 12 + 7] = global_timer();
-        const unsigned sv = smem_u32(kv_smem + s * STAGE_BYTES) + PAGE_BYTES;
+        const unsigned sv = smem_u32(v_smem + s * PAGE_BYTES);
         if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < PT_KEYS / 16; ++kk)
@@ -409,7 +412,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (tile * PT_KEYS + PT_KEYS - 1 > seq_last) {
         // the page holds rows behind the sequence's last position: their weights are zero, but zero
         // times anything must be zero, so clear those value rows (warp w takes every fourth row)
-        unsigned char* sv = kv_smem + (j % STAGES) * STAGE_BYTES + PAGE_BYTES;
+        unsigned char* sv = v_smem + (j % VS) * PAGE_BYTES;
         const int first = max(0, seq_last + 1 - tile * PT_KEYS);
         for (int e = (warp - 2) * 32 + lane; e < (PT_KEYS - first) * (HD / 8); e += 128) {
           int row = first + e / (HD / 8), c = e % (HD / 8);
@@ -477,19 +480,19 @@ extern "C" int bn_attention_prefill_tc_trace_read(unsigned long long* host) {
   return cudaMemcpy(host, g_pt_trace, PT_TRACE_TILES * 12 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
 
-template <int HD, int STAGES>
+template <int HD, int KS, int VS>
 static int launch_pt(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PtArgs& a, int n_tiles,
                      cudaStream_t stream) {
-  size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)STAGES * 2 * PT_KEYS * HD * 2 + (4 * STAGES + 6) * 8 + 16;
+  size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)(KS + VS) * PT_KEYS * HD * 2 + (2 * KS + 2 * VS + 6) * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, KS, VS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
   dim3 grid(n_tiles, a.n_heads);
-  BN_LAUNCH((attention_prefill_tc_kernel<HD, STAGES>), grid, PT_THREADS, smem, stream, mq, mk, mv, a);
+  BN_LAUNCH((attention_prefill_tc_kernel<HD, KS, VS>), grid, PT_THREADS, smem, stream, mq, mk, mv, a);
   return BN_OK;
 }
 
@@ -527,6 +530,7 @@ extern "C" int bn_attention_prefill_tc(const void* q, int q_stride, int n_tokens
   if (g_pt_trace_armed) { a.trace = g_pt_trace; g_pt_trace_armed = false; }
   // shared memory per block: 64 KB and 96 KB, so that two blocks share an SM (tensor memory
   // allows no more: 256 columns each) and one block's softmax overlaps the other's products
-  if (head_dim <= 64) return launch_pt<64, 3>(mq, mk, mv, a, n_tiles, stream);
-  return launch_pt<128, 2>(mq, mk, mv, a, n_tiles, stream);
+  // (a third key stage at head size 128 was measured and changes nothing: the softmax is the pace)
+  if (head_dim <= 64) return launch_pt<64, 3, 3>(mq, mk, mv, a, n_tiles, stream);
+  return launch_pt<128, 2, 2>(mq, mk, mv, a, n_tiles, stream);
 }
