@@ -20,6 +20,21 @@ __device__ __forceinline__ float rng_next_float(unsigned long long* state) {
   return (float)(u >> 8) / 16777216.0f;
 }
 
+// f(value, index) for every element of a row, the block's threads striding over it; 16-byte loads
+// where the row allows them, so that a thread has several loads in flight (one block reads a whole
+// row of the vocabulary, and what it waits for is the memory's latency).
+template <class F>
+__device__ __forceinline__ void row_for_each(const float* p, int n, F f) {  // (p may have been written by this kernel)
+  const int nv = ((((uintptr_t)p) & 15) == 0) ? (n >> 2) : 0;
+  const float4* p4 = reinterpret_cast<const float4*>(p);
+#pragma unroll 4
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const float4 v = p4[i];
+    f(v.x, 4 * i); f(v.y, 4 * i + 1); f(v.z, 4 * i + 2); f(v.w, 4 * i + 3);
+  }
+  for (int i = 4 * nv + threadIdx.x; i < n; i += blockDim.x) f(p[i], i);
+}
+
 // `index` (may be null) maps a row of logits to its row of sampler state: sequences leave a
 // batch at different times, their state rows stay where they are.
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, int ld, int vocab,
@@ -162,7 +177,7 @@ extern "C" int bn_argmax(const float* logits, int ld, int n_rows, int vocab, int
 
 // One block per row.  Each thread owns a contiguous run of the vocabulary so that the
 // cumulative distribution is walked in index order.
-__global__ void sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
                                           unsigned long long* __restrict__ rng, const int* __restrict__ index,
                                           int* __restrict__ out) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
@@ -173,40 +188,63 @@ __global__ void sample_temperature_kernel(const float* __restrict__ logits, int 
   __shared__ int pick;
   int row = blockIdx.x;
   const float* l = logits + (size_t)row * ld;
-  int per = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  int lo = threadIdx.x * per, hi = min(vocab, lo + per);
+  const int per = (((vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS) + 3) & ~3;  // a multiple of four
+  const int lo = min(vocab, (int)threadIdx.x * per), hi = min(vocab, lo + per);
   float m = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, l[i] / temperature);
+  row_for_each(l, vocab, [&](float x, int) { m = fmaxf(m, x / temperature); });
   m = block_max(m, scratch);
   float s = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += expf(l[i] / temperature - m);
+  row_for_each(l, vocab, [&](float x, int) { s += expf(x / temperature - m); });
   s = block_sum(s, scratch);
+  // the mass of this thread's run, then the mass before it (runs in index order)
   float local = 0.f;
-  for (int i = lo; i < hi; ++i) local += expf(l[i] / temperature - m) / s;
-  tsum[threadIdx.x] = local;
+  if ((((uintptr_t)l) & 15) == 0) {
+    int i = lo;
+    for (; i + 4 <= hi; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(l + i);
+      local += expf(v.x / temperature - m) / s;
+      local += expf(v.y / temperature - m) / s;
+      local += expf(v.z / temperature - m) / s;
+      local += expf(v.w / temperature - m) / s;
+    }
+    for (; i < hi; ++i) local += expf(l[i] / temperature - m) / s;
+  } else {
+    for (int i = lo; i < hi; ++i) local += expf(l[i] / temperature - m) / s;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) tsum[warp] = incl;
   if (threadIdx.x == 0) {
     r_shared = rng_next_float(rng + (index ? index[row] : row));
-    pick = vocab - 1;
+    pick = vocab - 1;  // if rounding leaves the whole sum below r
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    // Serial walk over 1024 partial sums: first run whose inclusive sum exceeds r.
-    float r = r_shared, cdf = 0.f;
-    int owner = -1;
-    for (int k = 0; k < SAMPLE_THREADS; ++k) {
-      if (r < cdf + tsum[k]) { owner = k; break; }
-      cdf += tsum[k];
+  // running sums at the borders of the runs: a run's start is, bit for bit, the end of the run before it
+  float warp_off = 0.f;
+  for (int w = 0; w < warp; ++w) warp_off += tsum[w];
+  float prev = __shfl_up_sync(0xffffffffu, incl, 1);
+  if (lane == 0) prev = 0.f;
+  const float before = warp_off + prev, end = warp_off + incl;
+  // the one thread whose run takes the running sum past r walks it
+  const float r = r_shared;
+  const bool last_run = hi >= vocab;
+  if (lo < hi && !(r < before) && (r < end || last_run)) {
+    float cdf = before;
+    int got = -1;
+    for (int i = lo; i < hi; ++i) {
+      cdf += expf(l[i] / temperature - m) / s;
+      if (r < cdf) { got = i; break; }
     }
-    if (owner >= 0) {
-      int a = owner * per, b = min(vocab, a + per);
-      for (int i = a; i < b; ++i) {
-        cdf += expf(l[i] / temperature - m) / s;
-        if (r < cdf) { pick = i; break; }
-        if (i == b - 1) pick = min(vocab - 1, b);  // rounding pushed it past this run
-      }
-    }
-    out[row] = pick;
+    if (got < 0) got = min(vocab - 1, hi);  // rounding pushed it past this run
+    pick = got;
   }
+  __syncthreads();
+  if (threadIdx.x == 0) out[row] = pick;
 }
 
 extern "C" int bn_sample_temperature(const float* logits, int ld, int n_rows, int vocab, float temperature,
@@ -249,26 +287,95 @@ __device__ __forceinline__ double block_sum_double(double v, double* scratch) {
 __device__ double mass_at_least(const float* p, int n, unsigned cutoff_bits, unsigned key, double* scratch) {
   double s = 0.0;
   unsigned k = max(key, cutoff_bits);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = p[i];
+  row_for_each(p, n, [&](float v, int) {
     if (__float_as_uint(v) >= k) s += (double)v;
-  }
+  });
   return block_sum_double(s, scratch);
 }
 
-// First token in (falling p, rising index) order whose running sum exceeds thr; *cum_out is that
-// running sum.  If none exceeds it, the last candidate in that order and the whole mass.
-__device__ int nucleus_first_exceeding(const float* p, int n, unsigned cutoff_bits, unsigned max_bits, double thr,
-                                       double* cum_out, double* dscratch, int* iscratch) {
-  double total = mass_at_least(p, n, cutoff_bits, cutoff_bits, dscratch);
-  unsigned lo = cutoff_bits, hi = max_bits;
-  bool none = !(total > thr);
-  if (!none) {
-    while (lo < hi) {
-      unsigned mid = lo + (hi - lo + 1) / 2;
-      if (mass_at_least(p, n, cutoff_bits, mid, dscratch) > thr) lo = mid;
-      else hi = mid - 1;
+// Masses in fixed point: p * 2^62 as an integer is exact for every float p >= 2^-38 (the cut-off
+// (1 - topp) / (n - 1) is far above that), the whole mass fits 64 bits, and integer sums do not
+// depend on the order of the additions, so shared-memory atomics may do them.
+#define NUC_ONE 4611686018427387904.0  // 2^62
+__device__ __forceinline__ unsigned long long nuc_fixed(float v) { return (unsigned long long)((double)v * NUC_ONE); }
+
+// For every thread the sum of v over the threads behind it (higher index); *total the sum over all.
+__device__ unsigned long long block_suffix_exclusive(unsigned long long v, unsigned long long* warp_tot,
+                                                     unsigned long long* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  unsigned long long s = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    unsigned long long t = __shfl_down_sync(0xffffffffu, s, o);
+    if (lane + o < 32) s += t;
+  }
+  __syncthreads();
+  if (lane == 0) warp_tot[warp] = s;
+  __syncthreads();
+  unsigned long long behind = 0, all = 0;
+  for (int w = 0; w < nwarp; ++w) {
+    unsigned long long t = warp_tot[w];
+    all += t;
+    if (w > warp) behind += t;
+  }
+  *total = all;
+  return (s - v) + behind;
+}
+
+// One level of the search for the key: among the candidates whose bits agree with `prefix` under
+// `mask`, the masses of the 2^nbits values of the next bits (from `shift` up) go into hist; the
+// result is the largest such value whose mass, together with everything above it (`above` on
+// entry: the mass above the prefix), exceeds thr, and the mass above that value.  *total is the
+// mass of all candidates under the prefix plus `above`.
+__device__ unsigned nucleus_level(const float* p, int n, unsigned cutoff_bits, unsigned mask, unsigned prefix, int shift,
+                                  int nbits, unsigned long long above, unsigned long long thr, unsigned long long* hist,
+                                  unsigned long long* warp_tot, unsigned long long* above_out, unsigned long long* total) {
+  __shared__ unsigned s_bin;
+  __shared__ unsigned long long s_above;
+  const int bins = 1 << nbits;
+  for (int i = threadIdx.x; i < bins; i += blockDim.x) hist[i] = 0ull;
+  if (threadIdx.x == 0) { s_bin = 0u; s_above = above; }
+  __syncthreads();
+  row_for_each(p, n, [&](float v, int) {
+    const unsigned b = __float_as_uint(v);
+    if (b >= cutoff_bits && (b & mask) == prefix) atomicAdd(&hist[(b >> shift) & (unsigned)(bins - 1)], nuc_fixed(v));
+  });
+  __syncthreads();
+  // each thread owns a run of bins; runs of higher bins belong to higher threads
+  const int per = (bins + (int)blockDim.x - 1) / (int)blockDim.x;
+  const int b0 = (int)threadIdx.x * per, b1 = min(bins, b0 + per);
+  unsigned long long mine = 0;
+  for (int b = b0; b < b1; ++b) mine += hist[b];
+  unsigned long long all;
+  const unsigned long long behind = above + block_suffix_exclusive(mine, warp_tot, &all);
+  *total = above + all;
+  if (behind <= thr && behind + mine > thr) {  // the crossing lies in this thread's run (at most one thread)
+    unsigned long long run = behind;
+    for (int b = b1 - 1; b >= b0; --b) {
+      if (run + hist[b] > thr) { s_bin = (unsigned)b; s_above = run; break; }
+      run += hist[b];
     }
+  }
+  __syncthreads();
+  *above_out = s_above;
+  return s_bin;
+}
+
+// First token in (falling p, rising index) order whose running sum exceeds thr; *cum_out is that
+// running sum.  If none exceeds it, the last candidate in that order and the whole mass.  The key
+// (the wanted token's probability as bits) is found 12, 12 and 8 bits at a time.
+__device__ int nucleus_first_exceeding(const float* p, int n, unsigned cutoff_bits, unsigned max_bits, double thr,
+                                       double* cum_out, double* dscratch, int* iscratch, unsigned long long* hist,
+                                       unsigned long long* warp_tot) {
+  (void)max_bits;
+  const unsigned long long thr_fx = thr <= 0.0 ? 0ull : (thr >= 2.0 ? (unsigned long long)(2.0 * NUC_ONE) : (unsigned long long)(thr * NUC_ONE));
+  unsigned long long above_fx = 0, total_fx = 0, dummy;
+  unsigned lo = nucleus_level(p, n, cutoff_bits, 0u, 0u, 20, 12, 0ull, thr_fx, hist, warp_tot, &above_fx, &total_fx) << 20;
+  const bool none = !(total_fx > thr_fx);
+  const double total = (double)total_fx / NUC_ONE;
+  if (!none) {
+    lo |= nucleus_level(p, n, cutoff_bits, 0xFFF00000u, lo, 8, 12, above_fx, thr_fx, hist, warp_tot, &above_fx, &dummy) << 8;
+    lo |= nucleus_level(p, n, cutoff_bits, 0xFFFFFF00u, lo, 0, 8, above_fx, thr_fx, hist, warp_tot, &above_fx, &dummy);
   }
   // `lo` is now the probability (as bits) of the wanted token, or, if none exceeds thr, the
   // cut-off: then the smallest candidate probability is looked up and its last index taken.
@@ -291,60 +398,76 @@ __device__ int nucleus_first_exceeding(const float* p, int n, unsigned cutoff_bi
     __syncthreads();
     lo = s_key;
   }
-  double above = (lo == 0xffffffffu) ? 0.0 : mass_at_least(p, n, cutoff_bits, lo + 1, dscratch);
+  double above = none ? ((lo == 0xffffffffu) ? 0.0 : mass_at_least(p, n, cutoff_bits, lo + 1, dscratch))
+                      : (double)above_fx / NUC_ONE;
   float pv = __uint_as_float(lo);
   // how many tokens of probability pv are needed: the k-th (1-based) in index order
   __shared__ int s_k;
   __shared__ double s_cum;
-  // count the ties
+  __shared__ int s_pick;
+  // count the ties: every thread owns a contiguous run of the vocabulary
   int mine = 0;
-  int per = (n + blockDim.x - 1) / blockDim.x;
-  int a = threadIdx.x * per, b = min(n, a + per);
-  for (int i = a; i < b; ++i) mine += (__float_as_uint(p[i]) == lo);
+  const int per = (((n + blockDim.x - 1) / blockDim.x) + 3) & ~3;  // a multiple of four
+  const int a = min(n, (int)threadIdx.x * per), b = min(n, a + per);
+  if ((((uintptr_t)p) & 15) == 0) {
+    int i = a;
+    for (; i + 4 <= b; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(p + i);
+      mine += (__float_as_uint(v.x) == lo) + (__float_as_uint(v.y) == lo) + (__float_as_uint(v.z) == lo) +
+              (__float_as_uint(v.w) == lo);
+    }
+    for (; i < b; ++i) mine += (__float_as_uint(p[i]) == lo);
+  } else {
+    for (int i = a; i < b; ++i) mine += (__float_as_uint(p[i]) == lo);
+  }
+  // ties before this thread's run, and all of them
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
   __syncthreads();
-  iscratch[threadIdx.x] = mine;
+  if (lane == 31) iscratch[warp] = incl;
   __syncthreads();
+  int before = incl - mine, ties = 0;
+  for (int w = 0; w < nwarp; ++w) {
+    int t = iscratch[w];
+    ties += t;
+    if (w < warp) before += t;
+  }
   if (threadIdx.x == 0) {
-    int ties = 0;
-    for (int t = 0; t < (int)blockDim.x; ++t) ties += iscratch[t];
     int k = ties;  // none exceeds: the last of them
-    double cum = above;
+    double cum = total;
     if (!none) {
-      for (int j = 1; j <= ties; ++j) {
-        cum += (double)pv;
-        if (cum > thr) { k = j; break; }
-      }
-    } else {
-      cum = total;
+      // the smallest j with above + j * pv > thr
+      double j0 = floor((thr - above) / (double)pv);
+      int j = (int)fmin(fmax(j0, 0.0), (double)ties);
+      while (j > 1 && above + (double)(j - 1) * (double)pv > thr) --j;
+      while (j < ties && !(above + (double)j * (double)pv > thr)) ++j;
+      k = max(1, min(j, ties));
+      cum = above + (double)k * (double)pv;
     }
     s_k = k;
     s_cum = cum;
+    s_pick = max(0, n - 1);
   }
   __syncthreads();
-  int k = s_k;
+  const int k = s_k;
   *cum_out = s_cum;
-  // locate the k-th tie in index order
-  __shared__ int s_pick;
-  if (threadIdx.x == 0) {
-    int seen = 0, owner = 0;
-    for (int t = 0; t < (int)blockDim.x; ++t) {
-      if (seen + iscratch[t] >= k) { owner = t; break; }
-      seen += iscratch[t];
+  // the thread whose run holds the k-th tie finds it
+  if (before < k && k <= before + mine) {
+    int seen = before;
+    for (int i = a; i < b; ++i) {
+      if (__float_as_uint(p[i]) == lo && ++seen == k) { s_pick = i; break; }
     }
-    int a0 = owner * per, b0 = min(n, a0 + per), pick = max(0, b0 - 1);
-    for (int i = a0; i < b0; ++i) {
-      if (__float_as_uint(p[i]) == lo) {
-        ++seen;
-        if (seen == k) { pick = i; break; }
-      }
-    }
-    s_pick = pick;
   }
   __syncthreads();
   return s_pick;
 }
 
-__global__ void sample_topp_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_topp_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature,
                                    float topp, unsigned long long* __restrict__ rng, const int* __restrict__ index,
                                    float* __restrict__ probs, int* __restrict__ out) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
@@ -353,21 +476,23 @@ __global__ void sample_topp_kernel(const float* __restrict__ logits, int ld, int
   __shared__ double dscratch[32];
   __shared__ int iscratch[SAMPLE_THREADS];
   __shared__ float r_shared;
+  __shared__ unsigned long long hist[4096];
+  __shared__ unsigned long long warp_tot[32];
   int row = blockIdx.x;
   const float* l = logits + (size_t)row * ld;
   float* p = probs + (size_t)row * vocab;
   float m = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, l[i] / temperature);
+  row_for_each(l, vocab, [&](float x, int) { m = fmaxf(m, x / temperature); });
   m = block_max(m, scratch);
   float s = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += expf(l[i] / temperature - m);
+  row_for_each(l, vocab, [&](float x, int) { s += expf(x / temperature - m); });
   s = block_sum(s, scratch);
   float pmax = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    float v = expf(l[i] / temperature - m) / s;
+  row_for_each(l, vocab, [&](float x, int i) {
+    float v = expf(x / temperature - m) / s;
     p[i] = v;
     pmax = fmaxf(pmax, v);
-  }
+  });
   pmax = block_max(pmax, scratch);  // also orders the writes of p before the reads below
   if (threadIdx.x == 0) r_shared = rng_next_float(rng + (index ? index[row] : row));
   __syncthreads();
@@ -379,9 +504,10 @@ __global__ void sample_topp_kernel(const float* __restrict__ logits, int ld, int
   unsigned cutoff_bits = __float_as_uint(fmaxf(cutoff, 0.f));
   unsigned max_bits = __float_as_uint(pmax);
   double cumulative, c2;
-  int last = nucleus_first_exceeding(p, vocab, cutoff_bits, max_bits, (double)topp, &cumulative, dscratch, iscratch);
+  int last = nucleus_first_exceeding(p, vocab, cutoff_bits, max_bits, (double)topp, &cumulative, dscratch, iscratch, hist,
+                                     warp_tot);
   float r = r_shared * (float)cumulative;
-  int pick = nucleus_first_exceeding(p, vocab, cutoff_bits, max_bits, (double)r, &c2, dscratch, iscratch);
+  int pick = nucleus_first_exceeding(p, vocab, cutoff_bits, max_bits, (double)r, &c2, dscratch, iscratch, hist, warp_tot);
   if (threadIdx.x == 0) out[row] = (c2 > cumulative) ? last : pick;
 }
 

@@ -219,6 +219,45 @@ def test_sample_temperature_follows_the_reference_walk(cuda_device):
         assert state.cpu().tolist() == [np.int64(np.uint64(x.state)) for x in rngs]
 
 
+@pytest.mark.parametrize("V,topp,temp", [(1013, 0.9, 0.8), (50, 0.51, 1.3), (128256, 0.9, 0.7), (4099, 0.999, 1.0),
+                                         (331, 0.05, 0.6)])
+def test_sample_topp_follows_the_reference_nucleus(cuda_device, V, topp, temp):
+    """Nucleus sampling against the plain sort-based one: peaked and flat rows, rows with many equal
+    logits (ties go by index), a row where one token holds nearly all the mass, large vocabularies.
+    (The plain running sums are float32 in sorted order, as the reference's; the kernel's masses are
+    exact.  They can part only where a sum lands within rounding of topp or of the draw, so no
+    case here puts a sum of equal probabilities exactly on topp.)"""
+    rows = 6
+    g = torch.Generator().manual_seed(12)
+    logits = torch.randn(rows, V, generator=g) * 2
+    logits[1] = torch.round(logits[1])            # many ties
+    logits[2] *= 4                                # peaked
+    logits[3] *= 0.05                             # flat: almost everything is a candidate
+    logits[4, 7] = 60.0                           # one token takes the whole nucleus
+    logits[5] = 0.0                               # all equal
+    logits = logits.to(cuda_device)
+    seeds = [42, 1, 7, 123456789, 99, 2**40 + 5]
+    state = torch.tensor(seeds, dtype=torch.int64, device=cuda_device)
+    rngs = [plain_llama.Xorshift64Star(s) for s in seeds]
+    differ = 0
+    for _ in range(4):
+        got = ops.sample_topp(logits, temp, topp, state).cpu().tolist()
+        for r in range(rows):
+            want = plain_llama.sample(logits[r].cpu().numpy(), temp, topp, rngs[r])
+            if got[r] != want:
+                # only a draw within float32 rounding of a boundary of a running sum may differ
+                # (the plain sums run in float32 in sorted order, the kernel's are exact)
+                differ += 1
+                pl = torch.softmax(logits[r].double().cpu() / temp, 0)
+                assert abs(pl[got[r]].item() - pl[want].item()) <= 1e-3 * max(pl[got[r]].item(), pl[want].item()) + 1e-9 or \
+                    abs(torch.argsort(-pl, stable=True).tolist().index(got[r]) - torch.argsort(-pl, stable=True).tolist().index(want)) <= 1, (r, got[r], want)
+        assert state.cpu().tolist() == [np.int64(np.uint64(x.state)) for x in rngs]
+    # a float32 running sum over V terms is off by up to about V * 2^-24 of the total; that is below
+    # one token's mass only while V is small, so only there must (nearly) every draw agree exactly
+    if V < 5000:
+        assert differ <= 2
+
+
 def test_repeat_penalty(cuda_device):
     logits = torch.tensor([[1.0, -2.0, 3.0, 4.0, -5.0], [1.0, 1.0, 1.0, 1.0, 1.0]], device=cuda_device)
     recent = torch.tensor([[2, 4, 2, 9, 0], [1, 1, 1, 1, 1]], dtype=torch.int32, device=cuda_device)
