@@ -113,11 +113,24 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int ld, int voca
   __shared__ int s_last;
   const int r = blockIdx.x, nb = gridDim.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* l = logits + (size_t)r * ld;
-  const int per = (vocab + nb - 1) / nb;
-  const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
+  const int per = (((vocab + nb - 1) / nb) + 3) & ~3;  // a multiple of four: 16-byte loads where the row allows
+  const int lo = min(vocab, (int)blockIdx.y * per), hi = min(vocab, lo + per);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+  int i0 = lo;
+  if ((((uintptr_t)(l + lo)) & 15) == 0) {
+    const int nv = (hi - lo) >> 2;
+    for (int q = threadIdx.x; q < nv; q += blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(l + lo + 4 * q);
+      const int i = lo + 4 * q;
+      if (argmax_better(v.x, i, best, bi)) { best = v.x; bi = i; }
+      if (argmax_better(v.y, i + 1, best, bi)) { best = v.y; bi = i + 1; }
+      if (argmax_better(v.z, i + 2, best, bi)) { best = v.z; bi = i + 2; }
+      if (argmax_better(v.w, i + 3, best, bi)) { best = v.w; bi = i + 3; }
+    }
+    i0 = lo + 4 * nv;
+  }
+  for (int i = i0 + threadIdx.x; i < hi; i += blockDim.x) {
     float v = l[i];
     if (argmax_better(v, i, best, bi)) { best = v; bi = i; }
   }
