@@ -11,7 +11,7 @@ import pytest
 import bitnet_c_b200 as bn
 import plain_llama
 from helpers import TOL_F32, bf16_bound, make_model_dir, random_tokens
-from tiny_configs import TINY_A, TINY_B, TINY_C
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -139,6 +139,24 @@ def test_bfloat16_generation_stays_near_the_plain_logits(tmp_path, cuda_device):
         ref = plain_llama.forward(cfg, w, list(p) + g.tokens[:-1])[len(p) - 1:]
         for i, t in enumerate(g.tokens):
             assert ref[i, t] >= ref[i].max() - 2 * bf16_bound(ref), f"step {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_the_recorded_graphs_length_buckets(tmp_path, cuda_device, dtype):
+    """Unequal prompts whose sequences pass 1,024 positions at different steps (the recorded decode
+    graphs are kept per bucket of the longest sequence) and end at different steps (a graph per
+    batch size), with head size 128 and sequences of 16 cache pages."""
+    d = make_model_dir(tmp_path, TINY_D, 505, "float32" if dtype == "float32" else "bfloat16")
+    model = bn.load_model(d, dtype=dtype)
+    cfg, w = plain_llama.read_model(d)
+    prompts = [random_tokens(80 + i, n, TINY_D["vocab_size"]) for i, n in enumerate([1000, 30, 990])]
+    got = bn.generate(model, prompts, max_new_tokens=[60, 12, 50], stop_ids=[])
+    assert [len(g.tokens) for g in got] == [60, 12, 50]
+    for p, g in zip(prompts, got):
+        ref = plain_llama.forward(cfg, w, list(p) + g.tokens[:-1])[len(p) - 1:]
+        slack = 2 * TOL_F32 if dtype == "float32" else 2 * bf16_bound(ref)
+        for i, t in enumerate(g.tokens):
+            assert ref[i, t] >= ref[i].max() - slack, f"step {i}"
 
 
 def test_command_line(tmp_path, cuda_device):
