@@ -1,7 +1,7 @@
 """The decode step with fixed shapes, replayed from a CUDA graph.
 
-A decode step launches some 300 small kernels; at a batch of one the launches cost more than
-the kernels.  ``DecodeRunner`` keeps everything a step reads in fixed device buffers (tokens,
+A decode step launches some 170 kernels of 3 to 40 microseconds; launched one by one from the
+host they would cost more than they run.  ``DecodeRunner`` keeps everything a step reads in fixed device buffers (tokens,
 positions, slots, sampler rows), runs the model's own forward and the sampler once under
 graph capture and replays the graph afterwards.  What changes between steps is data in those
 buffers: the graph ends by moving the sampled tokens into the token buffer and advancing the
@@ -9,10 +9,11 @@ positions, so consecutive steps of an unchanged batch need no host-to-device cop
 The reference does the same for its single sequence: it records its decode op list into a
 CUDA graph and patches position and length in a device struct (src/gpu_cuda.cu:186-310).
 
-Page tables are brought up to date before each replay, outside the graph.  Attention splits
-its keys into chunks and launches one block per possible chunk, so a graph is recorded for a
-*bucket* of lengths (1024, 2048, 4096, ... positions): a longer sequence moves the step to the
-next bucket's graph instead of every step paying for the chunks of the full context.
+Page tables are brought up to date before each replay, outside the graph.  Attention chooses
+how it splits a sequence's cache pages over blocks from the longest sequence it has to expect,
+so a graph is recorded for a *bucket* of lengths (1024, 2048, 4096, ... positions): a longer
+sequence moves the step to the next bucket's graph instead of every step paying for the grid of
+the full context.
 """
 from __future__ import annotations
 
