@@ -79,7 +79,7 @@ class Model:
         return all(ok(b) for b in self.blocks) and ok(self.final_norm)
 
     def kernel_families(self) -> List[str]:
-        fams = ["embed", "linear", "sampling"]
+        fams = ["embed", "linear"]
         for blk in self.blocks:
             fams.extend(blk.all_kernels())
         fams.extend(self.final_norm.all_kernels())

@@ -15,7 +15,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..csrc import ops
+from ..csrc import build, ops
 
 
 @dataclass(frozen=True)
@@ -59,6 +59,8 @@ class Sampler:
     def __init__(self, params: SamplingParams, n_rows: int, vocab: int, device, first_index: int = 0,
                  prompts: Optional[Sequence[Sequence[int]]] = None):
         params.validate()
+        if torch.device(device).type == "cuda":
+            build.ensure_built(["sampling"])  # compiled when a sampler is first made, not with the model
         self.params, self.n_rows, self.vocab, self.device = params, n_rows, vocab, device
         states = [seed_state(params.seed + first_index + i) for i in range(n_rows)]
         self.rng = torch.tensor(states, dtype=torch.int64, device=device)
