@@ -28,8 +28,10 @@ from .batch import StepContext
 
 
 class DecodeRunner:
-    def __init__(self, model, cache: Cache, sampler: Sampler, batch: int, pool=None):
+    def __init__(self, model, cache: Cache, sampler: Sampler, batch: int, pool=None, always_upload: bool = False):
         self.model, self.cache, self.sampler, self.batch = model, cache, sampler, batch
+        self.always_upload = always_upload  # copy every step's ids, positions, slots and rows from the host, even if
+        self.h2d_bytes = 0                  # the device already holds them; bytes copied so far
         dev = model.device
         B = batch
         self.meta = torch.zeros(4 * B, dtype=torch.int32, device=dev)
@@ -61,11 +63,12 @@ class DecodeRunner:
              ) -> torch.Tensor:
         """One token for each sequence; returns the sampled ids (device tensor, valid until the next step)."""
         slots, tokens, positions, rows = list(slots), list(tokens), list(positions), list(rows)
-        if (slots != self.host_slots or rows != self.host_rows or positions != self.host_pos
+        if (self.always_upload or slots != self.host_slots or rows != self.host_rows or positions != self.host_pos
                 or tokens != self.expect_tokens):
             host = torch.from_numpy(np.asarray(tokens + positions + slots + rows, dtype=np.int32)).pin_memory()
             self.meta.copy_(host, non_blocking=True)
             self.uploads += 1
+            self.h2d_bytes += host.numel() * 4
         self.host_slots, self.host_rows = slots, rows
         from ..csrc import ops
         bucket = 1024

@@ -17,8 +17,12 @@ class ModelEngine(Engine):
     """Runs steps of ``model`` on ``cache`` and samples on the device; token ids cross to the host
     once per step (the loop's stop decisions need them)."""
 
-    def __init__(self, model: Model, cache: Cache, params: SamplingParams, use_graphs: bool = True):
+    def __init__(self, model: Model, cache: Cache, params: SamplingParams, use_graphs: bool = True,
+                 always_upload: bool = False):
         self.model, self.cache, self.params = model, cache, params
+        # a decode step whose ids are the ones the device sampled itself needs no copy from the host;
+        # ``always_upload`` makes every step copy its inputs anyway (measurements that must include it)
+        self.always_upload = always_upload
         self.max_positions = model.spec.max_positions
         self.sampler: Optional[Sampler] = None
         self.use_graphs = use_graphs and model.graph_safe()
@@ -33,6 +37,10 @@ class ModelEngine(Engine):
         if self._steps_unchecked >= every:
             self._steps_unchecked = 0
             self.model.check_kernels()
+
+    def h2d_bytes(self) -> int:
+        """Bytes of step inputs copied from the host by the recorded decode steps so far."""
+        return sum(r.h2d_bytes for r in self.runners.values())
 
     def free_tokens(self) -> int:
         return self.cache.tokens_free()
@@ -84,7 +92,8 @@ class ModelEngine(Engine):
         if runner is None:
             if self.pool is None:
                 self.pool = torch.cuda.graph_pool_handle()
-            runner = self.runners[B] = DecodeRunner(self.model, self.cache, self.sampler, B, pool=self.pool)
+            runner = self.runners[B] = DecodeRunner(self.model, self.cache, self.sampler, B, pool=self.pool,
+                                                    always_upload=self.always_upload)
         out = runner.step([s.slot for s in seqs], [int(s.tokens[0]) for s in seqs], lengths, list(rows))
         for s in seqs:
             self.cache.advance(s.slot, 1)
