@@ -24,7 +24,7 @@
 // float32 product (src/transformer/cpu_backend.c:283-296, src/model_arch.c:322-338).  Its CUDA
 // decode kernels: one block per head without a split over the keys (src/gpu_cuda.cu:9718), and a
 // variant with the rotary encoding of q fused in (src/gpu_cuda.cu:9989).
-#include "common.cuh"
+#include "mma.cuh"
 
 #define DEC_THREADS 128
 #define DEC_CHUNK 128
@@ -63,12 +63,6 @@ struct DecArgs {
   __nv_bfloat16* out;
   int out_stride;
 };
-
-__device__ __forceinline__ float rope_angle(int pos, int i, float theta_scale) {
-  float angle = (float)pos;
-  for (int k = 0; k < i; ++k) angle *= theta_scale;
-  return angle;
-}
 
 template <bool FUSED>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecArgs a) {

@@ -34,28 +34,11 @@
 // attention is one block per head on CUDA cores without a split over the keys, with a variant
 // that fuses the rotary encoding of q (src/gpu_cuda.cu:9718, 9989).
 #include "tma.cuh"
+#include "mma.cuh"
 
 #define DT_THREADS 128
 #define DT_ROWS 16  // query heads per block (the MMA's 16 rows)
 
-__device__ __forceinline__ void dt_ldsm_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void dt_ldsm_x4_trans(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void dt_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
-                                       unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned dt_pack(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
 // Byte offset of 16-byte chunk `chunk` of row `row` in the query tile, whose rows hold HD bfloat16 (XOR swizzle).
 template <int HD>
 __device__ __forceinline__ unsigned dt_off(int row, int chunk) {
@@ -80,12 +63,6 @@ __device__ __forceinline__ float dt_ld_dsmem(unsigned local_addr, unsigned rank)
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
 }
-__device__ __forceinline__ float dt_angle(int pos, int i, float theta_scale) {
-  float angle = (float)pos;
-  for (int k = 0; k < i; ++k) angle *= theta_scale;
-  return angle;
-}
-
 struct DtArgs {
   const __nv_bfloat16* qkv;  // [n_seqs, q_stride]: raw query heads, key heads at k_off, value heads at v_off
   int q_stride, k_off, v_off;
@@ -191,7 +168,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const int half = a.rotary_dims >> 1;
   for (int i = tid; i < half; i += DT_THREADS) {
     float sn, cs;
-    sincosf(dt_angle(pos, i, a.theta_scale), &sn, &cs);
+    sincosf(rope_angle(pos, i, a.theta_scale), &sn, &cs);
     cs_tab[2 * i] = cs;
     cs_tab[2 * i + 1] = sn;
   }
@@ -323,7 +300,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (Q_IN_REGS && i == 0) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
-        dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+        ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
     }
     const int page_idx = my_lo + i;
     const unsigned sk = s_st + stage * STAGE_BYTES, sv = sk + PAGE_BYTES;
@@ -352,11 +329,11 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       if (Q_IN_REGS) {
         a0 = qf[ks][0]; a1 = qf[ks][1]; a2 = qf[ks][2]; a3 = qf[ks][3];
       } else {
-        dt_ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
+        ldsm_x4(s_q + dt_off<HD>(r8 + (mi & 1) * 8, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
       }
-      dt_ldsm_x4(sk + dt_koff(krow0 + (mi >> 1) * 8 + r8, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-      dt_mma(s[0], a0, a1, a2, a3, b0, b1);
-      dt_mma(s[1], a0, a1, a2, a3, b2, b3);
+      ldsm_x4(sk + dt_koff(krow0 + (mi >> 1) * 8 + r8, ks * 2 + (mi & 1)), b0, b1, b2, b3);
+      mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+      mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
     }
     // mask, running maximum, exponentials; rows g4 and g4 + 8 of the head tile
     float m_new[2] = {m_run[0], m_run[1]};
@@ -400,14 +377,14 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     }
     // O += P V over the 16 keys
     {
-      unsigned a0 = dt_pack(s[0][0], s[0][1]), a1 = dt_pack(s[0][2], s[0][3]);
-      unsigned a2 = dt_pack(s[1][0], s[1][1]), a3 = dt_pack(s[1][2], s[1][3]);
+      unsigned a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
+      unsigned a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
 #pragma unroll
       for (int j = 0; j < NT_O; j += 2) {
         unsigned b0, b1, b2, b3;
-        dt_ldsm_x4_trans(sv + dt_koff(krow0 + (mi & 1) * 8 + r8, j + (mi >> 1)), b0, b1, b2, b3);
-        dt_mma(o[j], a0, a1, a2, a3, b0, b1);
-        dt_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+        ldsm_x4_trans(sv + dt_koff(krow0 + (mi & 1) * 8 + r8, j + (mi >> 1)), b0, b1, b2, b3);
+        mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
       }
     }
   }

@@ -15,38 +15,11 @@
 // softmax, weighted sum of values; the key/value head of query head h is h / (H / KV)
 // (src/transformer/batched_attn_scalar.c:97-169, flash variant :171-245).  The reference's CUDA
 // prefill attention is one block per (head, token) on CUDA cores (src/gpu_cuda.cu:9772).
-#include "common.cuh"
+#include "mma.cuh"
 
 #define PF_M 64       // query rows per block
 #define PF_N 64       // keys per tile = BN_PAGE
 #define PF_THREADS 128
-
-__device__ __forceinline__ void pf_cp_async16(unsigned smem, const void* gmem, bool valid) {
-  int bytes = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void pf_commit() { asm volatile("cp.async.commit_group;"); }
-template <int N>
-__device__ __forceinline__ void pf_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
-
-__device__ __forceinline__ void ldsm_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void pf_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
-                                       unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold HD bfloat16.
 template <int HD>
@@ -92,7 +65,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     int r = p / CHUNKS, c = p % CHUNKS;
     bool ok = r < rows_here && c < real_chunks;
     const __nv_bfloat16* src = ok ? q + (size_t)(start + row0 + r) * q_stride + (size_t)h * head_dim + c * 8 : q;
-    pf_cp_async16(s_q + tile_off<HD>(r, c), src, ok);
+    cp_async16(s_q + tile_off<HD>(r, c), src, ok);
   }
   auto load_kv = [&](int tile, int stage) {
     int page = pt[tile];
@@ -105,12 +78,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       // their weights are zero, but zero times anything must be zero
       bool okv = ok && tile * PF_N + r <= seq_last;
       size_t off = (size_t)r * head_dim + c * 8;
-      pf_cp_async16(s_k + stage * TILE_BYTES + tile_off<HD>(r, c), ok ? kb + off : kb, ok);
-      pf_cp_async16(s_v + stage * TILE_BYTES + tile_off<HD>(r, c), okv ? vb + off : vb, okv);
+      cp_async16(s_k + stage * TILE_BYTES + tile_off<HD>(r, c), ok ? kb + off : kb, ok);
+      cp_async16(s_v + stage * TILE_BYTES + tile_off<HD>(r, c), okv ? vb + off : vb, okv);
     }
   };
   load_kv(tile_lo, 0);
-  pf_commit();
+  cp_async_commit();
 
   float o[NT_O][4];
 #pragma unroll
@@ -131,10 +104,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int stage = (tile - tile_lo) & 1;
     if (tile + 1 <= tile_hi) {
       load_kv(tile + 1, stage ^ 1);
-      pf_commit();
-      pf_wait<1>();
+      cp_async_commit();
+      cp_async_wait<1>();
     } else {
-      pf_wait<0>();
+      cp_async_wait<0>();
     }
     __syncthreads();
 
@@ -155,8 +128,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         unsigned b0, b1, b2, b3;
         int mi = lane >> 3, r = lane & 7;
         ldsm_x4(kb + tile_off<HD>((j + (mi >> 1)) * 8 + r, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-        pf_mma(s[j], a0, a1, a2, a3, b0, b1);
-        pf_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
+        mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
       }
     }
 
@@ -219,8 +192,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         unsigned b0, b1, b2, b3;
         int mi = lane >> 3, r = lane & 7;
         ldsm_x4_trans(vb + tile_off<HD>(ks * 16 + (mi & 1) * 8 + r, j + (mi >> 1)), b0, b1, b2, b3);
-        pf_mma(o[j], a0, a1, a2, a3, b0, b1);
-        pf_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+        mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
       }
     }
     __syncthreads();  // the stage is overwritten by the load after next

@@ -24,7 +24,7 @@
 // Reference for the operation: y = W x with float32 accumulation (src/quant/bf16_scalar.c:4-21);
 // its decode path is a warp-per-row matvec (src/gpu_cuda.cu:3995) and a fused gate/up + SiLU
 // kernel (src/gpu_cuda.cu:4547).
-#include "common.cuh"
+#include "mma.cuh"
 
 #define LM_KC 128                 // k per stage
 #define LM_XS_STRIDE (LM_KC + 32) // bf16 elements per staged row of x: 320 bytes, conflict-free 16-byte reads
@@ -35,22 +35,6 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
-}
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
-
-__device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
-                                         unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 struct LmArgs {
