@@ -37,6 +37,7 @@
 // (src/transformer/batched_attn_scalar.c:97-169, flash variant :171-245).  The reference's CUDA
 // prefill attention is one block per (head, token) on CUDA cores (src/gpu_cuda.cu:9772).
 #include "tma.cuh"
+#include "umma.cuh"
 
 #define PT_ROWS 128      // query rows per block (UMMA M)
 #define PT_KEYS 64       // keys per tile = BN_PAGE
@@ -62,101 +63,6 @@ struct PtArgs {
 };
 #define PT_TRACE_TILES 12  // per tile: 6 stamps of a softmax thread, 3 of the MMA thread
 
-// K-major tile with rows of 128 bytes, 128-byte swizzled: start address >> 4; leading byte offset
-// unused (1); stride byte offset 1024 between groups of 8 rows; version 1; layout SWIZZLE_128B.
-__device__ __forceinline__ unsigned long long pt_desc_k(unsigned addr) {
-  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-// MN-major tile (the contiguous dimension is N): 64 elements of N per 128-byte row, rows are
-// consecutive k; groups of 8 k-rows 1024 bytes apart (stride byte offset), the next 64 elements of
-// N one box (lbo bytes) further (leading byte offset).
-__device__ __forceinline__ unsigned long long pt_desc_mn(unsigned addr, unsigned lbo) {
-  return (unsigned long long)((addr >> 4) & 0x3FFF) | ((unsigned long long)((lbo >> 4) & 0x3FFF) << 16) | (64ull << 32) |
-         (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void pt_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
-                                       unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// The same with the A operand in tensor memory (lane = row, two bfloat16 of k per 32-bit column).
-__device__ __forceinline__ void pt_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long db, unsigned idesc,
-                                          unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void pt_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 consecutive columns of this thread's TMEM lane
-__device__ __forceinline__ void pt_tmem_ld32(unsigned addr, float* v) {
-  unsigned r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(addr) : "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-// 64 consecutive columns of this thread's TMEM lane; the wait is part of the same statement so that
-// nothing that uses the registers can be scheduled in front of it
-__device__ __forceinline__ void pt_tmem_ld64(unsigned addr, float* v) {
-  unsigned r[64];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
-      : "r"(addr) : "memory");
-#pragma unroll
-  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ float pt_ex2(float x) {  // 2^x, two units in the last place; 2^-inf = 0
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ void pt_tmem_st32(unsigned addr, const float* v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
-        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
-        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
-        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
-        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
-        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
-        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
-        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-      : "memory");
-}
-// One lane of the (converged) warp: the same one every time.
-__device__ __forceinline__ bool pt_elect_one() {
-  unsigned pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-__device__ __forceinline__ unsigned pt_pack(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
 // Bounded wait that also ends when another thread of the block has given up.
 __device__ __forceinline__ bool pt_wait(unsigned bar, unsigned parity, volatile int* failed, int* status) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -285,7 +191,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   } else if (warp == 1) {
     // The whole warp walks the loop, so that addresses and descriptors are warp-uniform values;
     // one elected lane issues the MMAs and commits.
-    const bool issuer = pt_elect_one();
+    const bool issuer = elect_one();
     const unsigned tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
     bool ok = __all_sync(0xffffffffu, pt_wait(q_full, 0, failed, a.status));
     const unsigned sq = smem_u32(q_smem);
@@ -306,11 +212,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (issuer) {
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks)
-            pt_mma(tbase + b * PT_KEYS, pt_desc_k(sq + (ks >> 2) * Q_BOX + (ks & 3) * 32),
-                   pt_desc_k(sk + (ks >> 2) * KV_BOX + (ks & 3) * 32), IDESC_S, ks ? 1u : 0u);
+            umma_mma(tbase + b * PT_KEYS, umma_desc_k(sq + (ks >> 2) * Q_BOX + (ks & 3) * 32),
+                   umma_desc_k(sk + (ks >> 2) * KV_BOX + (ks & 3) * 32), IDESC_S, ks ? 1u : 0u);
           if (trs) a.trace[j * 12 + 11] = global_timer();
-          pt_commit(k_empty0 + 8 * s);  // the key stage may be refilled
-          pt_commit(s_full0 + 8 * b);
+          umma_commit(k_empty0 + 8 * s);  // the key stage may be refilled
+          umma_commit(s_full0 + 8 * b);
           if (trs) a.trace[j * 12 + 6] = global_timer();
         }
         __syncwarp();
@@ -328,10 +234,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < PT_KEYS / 16; ++kk)
-            pt_mma_ts(tbase + O_COL, tbase + b * PT_KEYS + kk * 8, pt_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
+            umma_mma_ts(tbase + O_COL, tbase + b * PT_KEYS + kk * 8, umma_desc_mn(sv + kk * 2048, KV_BOX), IDESC_O,
                       (i | kk) ? 1u : 0u);
-          pt_commit(v_empty0 + 8 * s);    // the value stage may be refilled
-          pt_commit(pv_done);             // O holds the pages up to i
+          umma_commit(v_empty0 + 8 * s);    // the value stage may be refilled
+          umma_commit(pv_done);             // O holds the pages up to i
           if (tr) a.trace[i * 12 + 8] = global_timer();
         }
         __syncwarp();
@@ -355,7 +261,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (tr) a.trace[j * 12 + 1] = global_timer();
       float s[PT_KEYS];
-      pt_tmem_ld64(lane_addr + b * PT_KEYS, s);
+      tmem_ld64(lane_addr + b * PT_KEYS, s);
       if (tr) a.trace[j * 12 + 2] = global_timer();
       // mask, then the maximum of the raw scores (the scale is positive); four chains, not one
       const int k0 = tile * PT_KEYS;
@@ -382,10 +288,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int c = 0; c < HD; c += 32) {
           float o[32];
-          pt_tmem_ld32(lane_addr + O_COL + c, o);
+          tmem_ld32(lane_addr + O_COL + c, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= alpha;
-          pt_tmem_st32(lane_addr + O_COL + c, o);
+          tmem_st32(lane_addr + O_COL + c, o);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
@@ -395,7 +301,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int k = 0; k < PT_KEYS; ++k) {
-        s[k] = pt_ex2(fmaf(s[k], a.scale_log2e, neg_m));
+        s[k] = ex2_approx(fmaf(s[k], a.scale_log2e, neg_m));
         ls[k & 3] += s[k];
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
@@ -405,8 +311,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       {
         float pk[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) pk[c] = __uint_as_float(pt_pack(s[2 * c], s[2 * c + 1]));
-        pt_tmem_st32(lane_addr + b * PT_KEYS, pk);
+        for (int c = 0; c < 32; ++c) pk[c] = __uint_as_float(pack_bf16x2(s[2 * c], s[2 * c + 1]));
+        tmem_st32(lane_addr + b * PT_KEYS, pk);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       if (tile * PT_KEYS + PT_KEYS - 1 > seq_last) {
@@ -433,13 +339,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int c = 0; c < HD; c += 32) {
         float o[32];
-        pt_tmem_ld32(lane_addr + O_COL + c, o);
+        tmem_ld32(lane_addr + O_COL + c, o);
         if (r < rows_here) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             if (c + g * 8 < head_dim) {  // head sizes are multiples of 16: groups of 8 are whole
-              uint4 w = make_uint4(pt_pack(o[g * 8] * inv, o[g * 8 + 1] * inv), pt_pack(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv),
-                                   pt_pack(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv), pt_pack(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv));
+              uint4 w = make_uint4(pack_bf16x2(o[g * 8] * inv, o[g * 8 + 1] * inv), pack_bf16x2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv),
+                                   pack_bf16x2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv), pack_bf16x2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv));
               *reinterpret_cast<uint4*>(orow + c + g * 8) = w;
             }
           }

@@ -43,6 +43,7 @@
 // Reference for the operation: y = W x with float32 accumulation (src/quant/bf16_scalar.c:4-21);
 // the reference's CUDA backend reaches tensor cores only through cuBLAS (src/gpu_cuda.cu:11850-11879).
 #include "tma.cuh"
+#include "umma.cuh"
 
 #define TC_BM 128      // weight rows per tile (UMMA M)
 #define TC_BK 64       // k per stage: 128 bytes of bfloat16, one swizzle row
@@ -77,34 +78,6 @@ struct TcArgs {
   int* status;     // 0, or the code of a wait that gave up
   unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
 };
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
-// start address >> 4; leading byte offset 1 (unused for swizzled K-major); stride byte offset
-// 1024 >> 4 between groups of 8 rows; descriptor version 1; layout type 2 = SWIZZLE_128B.
-__device__ __forceinline__ unsigned long long umma_desc(unsigned addr) {
-  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
-                                          unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(unsigned addr, float* v) {
-  unsigned r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(addr));
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 // First row (of 128) of the slice that cluster rank r reduces and stores: multiples of 16 so that
 // a gate row and its up row (8 apart) stay in one slice.
@@ -263,7 +236,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         unsigned sa = smem_u32(base + s * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
         for (int kk = 0; kk < TC_BK / 16; ++kk)
-          umma_bf16(tmem_base, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC, (i | kk) ? 1u : 0u);
+          umma_mma(tmem_base, umma_desc_k(sa + kk * 32), umma_desc_k(sb + kk * 32), IDESC, (i | kk) ? 1u : 0u);
         umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
       }
       if (!failed) umma_commit(acc_bar);  // arrives when every MMA above is done
