@@ -56,9 +56,17 @@ class ModelEngine(Engine):
         self.cache.close(slot)
 
     def start_batch(self, first_index: int, prompts: Sequence[Sequence[int]]) -> None:
-        self.sampler = Sampler(self.params, len(prompts), self.model.spec.vocab_size, self.model.device,
+        """A new batch: its sampler rows are seeded and filled.  The sampler's device buffers are
+        kept from batch to batch while they are large enough, so that the recorded decode graphs
+        (which point at them) serve every batch of this engine."""
+        n = len(prompts)
+        if self.sampler is not None and self.sampler.n_rows >= n:
+            self.sampler.reset(first_index, prompts)
+            return
+        rows = max(n, min(self.cache.slots.n_slots, 64))  # room for the batches to come, within reason
+        self.sampler = Sampler(self.params, rows, self.model.spec.vocab_size, self.model.device,
                                first_index=first_index, prompts=prompts)
-        self.runners = {}  # graphs hold the sampler's buffers: a new batch records new ones
+        self.runners = {}  # graphs hold the sampler's buffers: a new sampler needs new ones
 
     def _index(self, rows: Sequence[int], n_state_rows: int) -> Optional[torch.Tensor]:
         if list(rows) == list(range(n_state_rows)):

@@ -62,24 +62,41 @@ class Sampler:
         if torch.device(device).type == "cuda":
             build.ensure_built(["sampling"])  # compiled when a sampler is first made, not with the model
         self.params, self.n_rows, self.vocab, self.device = params, n_rows, vocab, device
-        states = [seed_state(params.seed + first_index + i) for i in range(n_rows)]
-        self.rng = torch.tensor(states, dtype=torch.int64, device=device)
+        self.rng = torch.zeros(n_rows, dtype=torch.int64, device=device)
         self.penalised = params.repeat_penalty != 1.0
+        # scratch of the nucleus kernel, allocated once: recorded graphs keep its address
         self.probs: Optional[torch.Tensor] = None
+        if not params.greedy and params.nucleus:
+            self.probs = torch.empty((n_rows, vocab), dtype=torch.float32, device=device)
         if self.penalised:
             w = params.repeat_window
-            recent = np.zeros((n_rows, w), dtype=np.int32)
-            length = np.zeros(n_rows, dtype=np.int32)
-            pos = np.zeros(n_rows, dtype=np.int32)
+            self.recent = torch.zeros((n_rows, w), dtype=torch.int32, device=device)
+            self.recent_len = torch.zeros(n_rows, dtype=torch.int32, device=device)
+            self.recent_pos = torch.zeros(n_rows, dtype=torch.int32, device=device)
+        self.reset(first_index, prompts)
+
+    def reset(self, first_index: int = 0, prompts: Optional[Sequence[Sequence[int]]] = None) -> None:
+        """Start a new batch in the same device buffers (recorded decode graphs point at them):
+        row i is seeded ``seed + first_index + i`` and remembers the tail of ``prompts[i]``."""
+        n = self.n_rows
+        if prompts is not None and len(prompts) > n:
+            raise ValueError(f"sampler holds {n} rows, the batch has {len(prompts)}")
+        states = np.asarray([seed_state(self.params.seed + first_index + i) for i in range(n)], dtype=np.int64)
+        self.rng.copy_(torch.from_numpy(states), non_blocking=False)
+        if self.penalised:
+            w = self.params.repeat_window
+            recent = np.zeros((n, w), dtype=np.int32)
+            length = np.zeros(n, dtype=np.int32)
+            pos = np.zeros(n, dtype=np.int32)
             # the reference pushes every prompt id before generation starts (src/main.c:1648)
             for i, p in enumerate(prompts or []):
                 tail = list(p)[-w:]
                 recent[i, :len(tail)] = tail
                 length[i] = len(tail)
                 pos[i] = len(tail) % w
-            self.recent = torch.from_numpy(recent).to(device)
-            self.recent_len = torch.from_numpy(length).to(device)
-            self.recent_pos = torch.from_numpy(pos).to(device)
+            self.recent.copy_(torch.from_numpy(recent))
+            self.recent_len.copy_(torch.from_numpy(length))
+            self.recent_pos.copy_(torch.from_numpy(pos))
 
     def sample(self, logits: torch.Tensor, index: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Next token for each row of ``logits`` (modified in place by the penalty); ``index[r]`` is
@@ -91,8 +108,7 @@ class Sampler:
             out = ops.argmax(logits)
         elif p.nucleus:
             if self.probs is None or self.probs.shape[0] < logits.shape[0]:
-                self.probs = torch.empty((max(self.n_rows, logits.shape[0]), self.vocab), dtype=torch.float32,
-                                         device=self.device)
+                raise ValueError(f"sampler holds {self.n_rows} rows, got logits of {logits.shape[0]}")
             out = ops.sample_topp(logits, p.temperature, p.top_p, self.rng, index=index, probs=self.probs)
         else:
             out = ops.sample_temperature(logits, p.temperature, self.rng, index=index)

@@ -50,6 +50,30 @@ def test_stop_ids_and_unequal_lengths(models):
     assert got[0].finish_reason == "stop" and len(got[0].tokens) <= 4
 
 
+@pytest.mark.parametrize("temperature,penalty", [(0.0, 1.0), (0.8, 1.0), (0.0, 1.3)])
+def test_batch_after_batch_reuses_slots_sampler_rows_and_recorded_steps(models, temperature, penalty):
+    """Seven requests through an engine that holds two at a time: four batches one after another
+    in the same cache, sampler buffers and recorded decode graphs.  Every request must come out
+    as it does alone (request i is seeded seed + i whatever batch it lands in)."""
+    cfg, d, model, w = models["a"]
+    prompts = [random_tokens(300 + i, n, 256) for i, n in enumerate([5, 9, 3, 12, 1, 20, 7])]
+    kw = dict(max_new_tokens=[8, 3, 8, 5, 8, 2, 6], temperature=temperature, top_p=0.9, seed=77, repeat_penalty=penalty)
+    got = bn.generate(model, prompts, max_batch=2, **kw)
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        want = plain_llama.generate(cfg, w, p, kw["max_new_tokens"][i], temperature=temperature, topp=0.9, seed=77 + i,
+                                    repeat_penalty=penalty)
+        assert g.tokens == want, f"request {i}"
+    # the same through an engine whose recorded steps can be counted: one graph per batch size
+    # (two sequences, then one when the shorter has ended), whatever the number of batches
+    from bitnet_c_b200.engine import ModelEngine, generate
+    from bitnet_c_b200.sampling import SamplingParams
+    cache = model.new_cache(max_tokens=256, max_seqs=2)
+    eng = ModelEngine(model, cache, SamplingParams(temperature=temperature, top_p=0.9, seed=77, repeat_penalty=penalty))
+    again = generate(eng, prompts, kw["max_new_tokens"], stop_ids=(), max_batch=2)
+    assert [c.tokens for c in again] == [c.tokens for c in got]
+    assert sorted(eng.runners) == [1, 2] and all(len(r.graphs) == 1 for r in eng.runners.values())
+
+
 @pytest.mark.parametrize("topp", [1.0, 0.9])
 def test_temperature_sampling_is_reproducible_and_follows_plain(models, topp):
     cfg, d, model, w = models["b"]
