@@ -76,6 +76,9 @@ class KvGroup:
     def reserve(self, slot: int, old_len: int, new_len: int) -> None:
         """Hold pages for positions [first needed, new_len)."""
         held = self.held.setdefault(slot, {})
+        last = (new_len - 1) // PAGE
+        if old_len > 0 and (old_len - 1) // PAGE == last and last in held:
+            return  # the new tokens lie in the page that holds the sequence's last token
         first = 0
         if self.request.window > 0:
             # the oldest key any new token needs: position old_len - window + 1

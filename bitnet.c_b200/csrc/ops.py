@@ -302,6 +302,29 @@ _FORCE_SPLITS = 0  # tests and experiments: a fixed number of blocks per sequenc
 # (more than eight take the path that merges through global memory and a ticket)
 
 
+def decode_splits(pages: int, blocks_per_split: int) -> int:
+    """How many blocks share one sequence's pages in ``attention_decode_fused``.
+
+    A block walks its pages one after another, about 0.75 us each; blocks that share a sequence
+    merge their results inside a thread-block cluster, which costs about as much as six pages.
+    So a split pays only when it shortens the walk by more than that: few sequences, or long
+    ones.  At most eight blocks per sequence (one cluster), and no more than 256 blocks in all:
+    clusters are placed within one GPC, and beyond that number a second wave of blocks starts.
+    ``pages`` is the bound the step was recorded for; sequences are taken to fill three
+    quarters of it.  Measured at 8 key/value heads of 128 (us, 520 positions, 1 against the
+    chosen number of splits): 1 sequence 10.1 / 6.6, 4: 10.4 / 8.8, 8: 11.2 / 11.2, 12: 11.9
+    (two splits 14.1, three 21.7), 16: 12.4 (two 14.7); at 2,000 positions 8 sequences
+    31.3 / 16.5, 16: 34.0 / 26.5."""
+    cap = max(1, min(pages, 8, 256 // max(1, blocks_per_split)))
+    filled = 0.75 * pages
+    best, best_cost = 1, filled
+    for s in range(2, cap + 1):
+        cost = min(float((pages + s - 1) // s), filled) + 6.0
+        if cost < best_cost:
+            best, best_cost = s, cost
+    return best
+
+
 def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch.Tensor, n_seqs: int, n_heads: int,
                            n_kv_heads: int, head_dim: int, scale: float, window: int, rotary_dims: int,
                            theta_scale: float, tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
@@ -327,13 +350,9 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         raise KernelError("attention_decode_fused: offsets run past the row")
     if out.shape[0] < n_seqs or out.shape[1] != n_heads * head_dim or tok_pos.shape[0] < n_seqs or qkv.shape[0] < n_seqs:
         raise KernelError("attention_decode_fused: out, qkv or tok_pos does not fit")
-    # Few sequences: several blocks per sequence so that many SMs read the cache, but no more
-    # blocks than two per SM, and at most eight per sequence: these merge their results inside
-    # a thread-block cluster.  Many sequences: one block per (sequence, head group) walks all its
-    # pages and no partial results are needed.
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     blocks_per_split = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-    want_splits = max(1, min(pages, 8, (2 * N_SMS) // blocks_per_split))
+    want_splits = decode_splits(pages, blocks_per_split)
     if _FORCE_SPLITS:
         want_splits = max(1, min(pages, _FORCE_SPLITS))
     pages_per_block = (pages + want_splits - 1) // want_splits
@@ -505,8 +524,8 @@ def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swigl
     return out
 
 
-def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
-           swiglu: bool = False, partial_sums: bool = False, sink: Optional[NormSink] = None):
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
+           partial_sums: bool = False, sink: Optional[NormSink] = None):
     """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
 
     ``x`` may be ``RowScaled`` (the output of a norm that a product's epilogue prepared).  With
@@ -518,8 +537,6 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_pa
     silu(gate) * up, ``[M, N / 2]``.  ``partial_sums``: return the float32 partial sums
     ``[parts, M, N]`` of a product that split its inner dimension instead of their sum
     (``add_rmsnorm`` can add them up); by default the product sums them itself.
-    ``allow_partials`` is accepted for callers that add the result to the residual and is
-    ignored.
     """
     _need(w, "w", dims=2)
     if x.shape[1] != w.shape[1] or len(x.shape) != 2:
@@ -531,7 +548,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_pa
     if sink is not None:
         if fast and USE_FUSED_NORM and not swiglu and tuple(sink.residual.shape) == (M, N):
             return linear_tc(x, w, sink=sink)
-        delta = linear(x, w, out_dtype=out_dtype, allow_partials=allow_partials, swiglu=swiglu)
+        delta = linear(x, w, out_dtype=out_dtype, swiglu=swiglu)
         normed = torch.empty((M, sink.residual.shape[1]), dtype=delta.dtype, device=delta.device)
         return add_rmsnorm(sink.residual, delta, sink.weight, sink.eps, normed)
     if isinstance(x, RowScaled):

@@ -171,19 +171,22 @@ class Model:
         seen = set()
         lengths = []
         V = self.spec.vocab_size
+        length_of = cache.length
         for s in seqs:
-            if s.slot in seen:
-                raise StepError(f"slot {s.slot} appears twice in one step")
-            seen.add(s.slot)
-            lengths.append(cache.length(s.slot))
-            if len(s.tokens) == 0:
-                raise StepError(f"slot {s.slot} brings no token")
-            for t in s.tokens:
-                if not 0 <= int(t) < V:
-                    raise StepError(f"token {t} is outside the vocabulary of {V}")
+            slot, toks = s.slot, s.tokens
+            if slot in seen:
+                raise StepError(f"slot {slot} appears twice in one step")
+            seen.add(slot)
+            lengths.append(length_of(slot))
+            n = len(toks)
+            if n == 0:
+                raise StepError(f"slot {slot} brings no token")
+            if not (0 <= min(toks) and max(toks) < V):
+                bad = next(t for t in toks if not 0 <= int(t) < V)
+                raise StepError(f"token {bad} is outside the vocabulary of {V}")
             for w in s.want:
-                if not 0 <= w < len(s.tokens):
-                    raise StepError(f"wanted place {w} is outside the {len(s.tokens)} tokens of slot {s.slot}")
+                if not 0 <= w < n:
+                    raise StepError(f"wanted place {w} is outside the {n} tokens of slot {slot}")
         return lengths
 
     def step(self, cache: Cache, seqs: Sequence[SeqStep]) -> Optional[torch.Tensor]:

@@ -64,7 +64,7 @@ class Attention(Mixer):
             ops.attention_decode_fused(qkv, s.q_dim, s.q_dim + s.kv_dim, out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                        s.softmax_scale, s.window, rotary_dims, theta_scale, ctx.tok_pos, ctx.slots,
                                        kv.page_table, kv.k, kv.v, ctx.max_len)
-            return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True, sink=sink)
+            return ops.linear(out, self.w_o, out_dtype=self.build.dtype, sink=sink)
         if kv.owner:
             qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)
             n_rot = s.n_heads + s.n_kv_heads
@@ -98,4 +98,4 @@ class Attention(Mixer):
             ops.attention_general(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                   s.softmax_scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
                                   kv.page_table, kv.k, kv.v)
-        return ops.linear(out, self.w_o, out_dtype=self.build.dtype, allow_partials=True, sink=sink)
+        return ops.linear(out, self.w_o, out_dtype=self.build.dtype, sink=sink)

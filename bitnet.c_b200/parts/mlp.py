@@ -39,4 +39,4 @@ class GatedMlp(FeedForward):
 
     def forward(self, h, ctx, sink=None):
         act = ops.linear(h, self.w_gate_up, out_dtype=self.build.dtype, swiglu=True)
-        return ops.linear(act, self.w_down, out_dtype=self.build.dtype, allow_partials=True, sink=sink)
+        return ops.linear(act, self.w_down, out_dtype=self.build.dtype, sink=sink)

@@ -1,0 +1,26 @@
+"""The number of blocks that share a sequence in decode attention (a host decision, no device)."""
+from bitnet_c_b200.csrc.ops import decode_splits
+
+
+def test_bounds_hold_for_every_size():
+    for pages in (1, 2, 3, 7, 8, 9, 16, 33, 64, 500):
+        for blocks in (1, 3, 8, 32, 64, 96, 128, 255, 256, 257, 320, 4096):
+            s = decode_splits(pages, blocks)
+            assert 1 <= s <= min(8, pages)
+            assert s == 1 or s * blocks <= 256
+
+
+def test_few_sequences_split_and_many_do_not():
+    kv_heads = 8
+    assert decode_splits(16, 1 * kv_heads) == 8
+    assert decode_splits(16, 4 * kv_heads) == 8
+    assert decode_splits(16, 8 * kv_heads) == 4
+    # two or three blocks per sequence cost more than they save at a thousand positions
+    assert decode_splits(16, 12 * kv_heads) == 1
+    assert decode_splits(16, 16 * kv_heads) == 1
+    # and pay at two thousand and more
+    assert decode_splits(32, 16 * kv_heads) == 2
+    assert decode_splits(64, 8 * kv_heads) == 4
+    assert decode_splits(64, 64 * kv_heads) == 1
+    # a short bound never splits: the merge costs more than the walk
+    assert decode_splits(4, 1) == 1
