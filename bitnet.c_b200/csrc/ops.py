@@ -308,18 +308,22 @@ def decode_splits(pages: int, blocks_per_split: int) -> int:
     A block walks its pages one after another, about 0.75 us each; blocks that share a sequence
     merge their results inside a thread-block cluster, which costs about as much as six pages.
     So a split pays only when it shortens the walk by more than that: few sequences, or long
-    ones.  At most eight blocks per sequence (one cluster), and no more than 256 blocks in all:
-    clusters are placed within one GPC, and beyond that number a second wave of blocks starts.
+    ones.  Up to eight blocks per sequence are one cluster; more (up to 32) merge through global
+    memory block by block, which costs as much as 0.7 pages more for every block and pays from
+    some 16,000 positions on for one or two sequences.  No more than 256 blocks in all: clusters are placed within one
+    GPC, and beyond that number a second wave of blocks starts.
     ``pages`` is the bound the step was recorded for; sequences are taken to fill three
     quarters of it.  Measured at 8 key/value heads of 128 (us, 520 positions, 1 against the
     chosen number of splits): 1 sequence 10.1 / 6.6, 4: 10.4 / 8.8, 8: 11.2 / 11.2, 12: 11.9
     (two splits 14.1, three 21.7), 16: 12.4 (two 14.7); at 2,000 positions 8 sequences
-    31.3 / 16.5, 16: 34.0 / 26.5."""
-    cap = max(1, min(pages, 8, 256 // max(1, blocks_per_split)))
+    31.3 / 16.5, 16: 34.0 / 26.5; one sequence of 64,000 positions: 8 splits 111, 32 splits 59."""
+    cap = max(1, min(pages, 256 // max(1, blocks_per_split)))
     filled = 0.75 * pages
     best, best_cost = 1, filled
-    for s in range(2, cap + 1):
-        cost = min(float((pages + s - 1) // s), filled) + 6.0
+    for s in (2, 3, 4, 5, 6, 7, 8, 12, 16, 24, 32):
+        if s > cap:
+            break
+        cost = min(float((pages + s - 1) // s), filled) + (6.0 if s <= 8 else 6.0 + 0.7 * s)
         if cost < best_cost:
             best, best_cost = s, cost
     return best

@@ -501,6 +501,7 @@ def _last_row_attention(q, k, v, scale, window):
     (2, 2, 256, 64, [257], 0), (40, 40, 64, 0, [100, 300], 0), (12, 1, 32, 32, [150, 40, 260], 17),
     (40, 40, 128, 128, [3000, 17, 2049], 0), (32, 8, 64, 64, [2303, 1], 0), (8, 2, 128, 128, [5000, 4097], 1024),
     (4, 2, 64, 40, [70, 200], 0),  # rotary dimensions that are no multiple of 16
+    (8, 1, 128, 128, [20000], 0),  # one long sequence: more blocks than a cluster holds, chosen by the policy
 ])
 @pytest.mark.parametrize("splits", [0, 3, 12])
 def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd, lens, window):
@@ -520,6 +521,18 @@ def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd,
     vs = [torch.randn(L, KV, hd, generator=g).to(torch.bfloat16) for L in lens]
     raw = (torch.randn(n_seq, H + 2 * KV, hd, generator=g) * 0.7).to(torch.bfloat16)  # the new token's q|k|v
     slots = list(range(n_seq))[::-1]
+    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(rd))) if rd else 1.0
+    pos = [L - 1 for L in lens]
+    for s, L in enumerate(lens):
+        if L < 1000:
+            continue
+        # among thousands of random keys a far one would hardly count: make the key at a third of
+        # the sequence point along the first query of each group, so that its value is the result
+        r = raw[s].double().numpy()
+        rot = plain_llama.apply_rope(r[None, :H], [pos[s]], theta, dims=rd)[0] if rd else r[:H]
+        for kh in range(KV):
+            qv = rot[kh * (H // KV)]
+            ks[s][L // 3, kh] = torch.from_numpy(qv / np.linalg.norm(qv) * 16.0 * hd ** 0.5 / np.linalg.norm(qv)).to(torch.bfloat16)
     for s, L in enumerate(lens):
         for p in range(L - 1):  # the last position is written by the kernel
             page = perm[slots[s], p // 64].item()
@@ -531,8 +544,6 @@ def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd,
         v[page, :, row + 1:] = float("inf")
     k_before, v_before = k.clone(), v.clone()
     out = torch.empty(n_seq, H * hd, dtype=torch.bfloat16, device=cuda_device)
-    scale = float(np.power(np.float32(theta), np.float32(-2.0) / np.float32(rd))) if rd else 1.0
-    pos = [L - 1 for L in lens]
     ops.attention_decode_fused(raw.reshape(n_seq, -1).contiguous().to(cuda_device), H * hd, (H + KV) * hd, out, n_seq,
                                H, KV, hd, hd ** -0.5, window, rd, scale,
                                torch.tensor(pos, dtype=torch.int32, device=cuda_device),
@@ -552,6 +563,9 @@ def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd,
         vfull = np.concatenate([vs[s][: L - 1].double().numpy(), r[None, H + KV:]])
         ref = _last_row_attention(rot[:H], kfull, vfull, hd ** -0.5, window)
         assert np.abs(got[s] - ref).max() < 2e-2, f"sequence {s}"
+        if L >= 1000 and not window:
+            for kh in range(KV):  # the marked key decides the first head of each group
+                assert np.abs(ref[kh * (H // KV)] - vfull[L // 3, kh]).max() < 0.1
     bits = lambda t: t.view(torch.int16)
     assert torch.equal(bits(k)[~touched], bits(k_before)[~touched]) and torch.equal(bits(v)[~touched], bits(v_before)[~touched])
     ops.check_tc_status(cuda_device)
