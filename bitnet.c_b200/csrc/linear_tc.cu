@@ -7,7 +7,7 @@
 //
 // A tile is 128 weight rows.  Weights with few rows have fewer tiles than the GPU has SMs, so the
 // inner dimension of a tile is split over a thread-block cluster of C blocks (C x tiles is about
-// the number of SMs): block r of the cluster multiplies k-blocks [r KB/C, (r+1) KB/C).  Each block
+// one and a half times the number of SMs): block r of the cluster multiplies k-blocks [r KB/C, (r+1) KB/C).  Each block
 // leaves its float32 partial tile in its own shared memory; after a cluster barrier every block
 // adds up, in rank order, a slice of the tile's rows read from all C blocks through distributed
 // shared memory and runs the epilogue on that slice.  Nothing goes through global memory, all
@@ -53,6 +53,8 @@
 #define TC_STAGES_FOR(MP) ((MP) == 16 ? 6 : ((MP) == 32 ? 5 : 4))
 // Threads of a block: producer warp, MMA warp, and four epilogue warps (one per TMEM lane
 // quadrant), eight for the widest accumulator (two warps share a quadrant, half the columns each).
+// (An accumulator of 128 columns with a ring of three stages was tried for 65 to 128 rows: the library
+// product is faster there, 3.1 against 3.7 ms for the products of 32 layers of width 4096.)
 #define TC_EPI_FOR(MP) ((MP) == 64 ? 256 : 128)
 #define TC_THREADS_FOR(MP) (64 + TC_EPI_FOR(MP))
 
@@ -164,7 +166,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   float* ss_chunk = row_scale + 64;            // [EPI / MP][MP]: partial sums on the way there
   float* partial = (float*)base;  // [MP][PSTRIDE]: partial[m][row], valid once all MMAs have read the ring
   float* item_sq = partial + MP * PSTRIDE;  // mode 3: the sum of squares of each epilogue item
-  static_assert((MP * PSTRIDE + 32 * 64) * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and item sums reuse the ring");
+  static_assert((MP * PSTRIDE + 32 * MP) * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and item sums reuse the ring");
   __shared__ int s_failed;
   __shared__ int s_acc_ok;
 
@@ -488,8 +490,13 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs&
   return BN_OK;
 }
 
+// Blocks per tile when the caller leaves the choice to the kernel: about 1.5 blocks per SM in all.
+// With one block per SM the bytes in flight (one ring each) do not cover the memory's latency, and
+// while a block runs its epilogue its SM fetches nothing; with more than some 250 blocks clusters no
+// longer fit in one wave.  Measured on the four products of a layer of width 4096 (32 layers, one
+// CUDA graph, 8 rows): 3/4/1/4 blocks per tile 2.79 ms, 5/7/1/7 2.58 ms, 6/8/1/8 2.76 ms.
 static int auto_cluster(int tiles, int k_blocks) {
-  int cluster = sm_count() / tiles;
+  int cluster = (sm_count() * 157 / 100 + tiles / 2) / tiles;
   int by_k = k_blocks / 4;  // at least four k-blocks per block
   if (cluster > by_k) cluster = by_k;
   if (cluster > 8) cluster = 8;
@@ -511,7 +518,7 @@ extern "C" int bn_linear_tc_auto_cluster(int N, int K) {
 // (tiles = ceil(N / 128); cluster must be given).  row_ss (or null): [ss_parts][ss_stride] sums of
 // squares of the rows of x as a mode-3 product left them; the result rows are then multiplied by
 // 1 / sqrt(sum / width + eps) with inv_width = 1 / width.  cluster: blocks that share a tile's
-// inner dimension, 1 to 8 (0: chosen so that cluster x tiles is about the number of SMs).  status:
+// inner dimension, 1 to 8 (0: chosen so that cluster x tiles is about one and a half times the number of SMs).  status:
 // one int on the device, left 0 unless a wait inside the kernel gave up.
 extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
                                int mode, int cluster, const float* row_ss, int ss_parts, int ss_stride, float inv_width,
