@@ -9,9 +9,12 @@
 // inner dimension of a tile is split over a thread-block cluster of C blocks (C x tiles is about
 // one and a half times the number of SMs): block r of the cluster multiplies k-blocks [r KB/C, (r+1) KB/C).  Each block
 // leaves its float32 partial tile in its own shared memory; after a cluster barrier every block
-// adds up, in rank order, a slice of the tile's rows read from all C blocks through distributed
-// shared memory and runs the epilogue on that slice.  Nothing goes through global memory, all
-// blocks of a tile finish together, and the order of the additions is fixed.
+// sends each other block the slice of rows that block owns, as one bulk copy from shared memory to
+// the owner's shared memory that completes on an mbarrier there (distributed shared memory; a
+// copy is posted and needs no round trip, where loads from another block's shared memory took 1
+// to 4 us per tile).  The owner adds up its C copies of the slice in rank order and runs the
+// epilogue on it.  Nothing goes through global memory, all blocks of a tile finish together, and
+// the order of the additions is fixed.
 //
 // A block of 192 threads:
 //   warp 0     one thread issues the TMA loads of W and x tiles into a ring of stages and arms each
@@ -52,15 +55,17 @@
 // kernel's blocks are finishing (programmatic dependent launch).
 #define TC_STAGES_FOR(MP) ((MP) == 16 ? 6 : ((MP) == 32 ? 5 : 4))
 // Threads of a block: producer warp, MMA warp, and four epilogue warps (one per TMEM lane
-// quadrant), eight for the widest accumulator (two warps share a quadrant, half the columns each).
+// quadrant), eight for the two wider accumulators (two warps share a quadrant, half the columns each;
+// sixteen would need more registers than two blocks per SM have).
 // (An accumulator of 128 columns with a ring of three stages was tried for 65 to 128 rows: the library
 // product is faster there, 3.1 against 3.7 ms for the products of 32 layers of width 4096.)
-#define TC_EPI_FOR(MP) ((MP) == 64 ? 256 : 128)
+#define TC_EPI_FOR(MP) ((MP) >= 32 ? 256 : 128)
 #define TC_THREADS_FOR(MP) (64 + TC_EPI_FOR(MP))
 
 #define TC_ERR_FULL_WAIT 1
 #define TC_ERR_EMPTY_WAIT 2
 #define TC_ERR_ACC_WAIT 3
+#define TC_ERR_SLICE_WAIT 6
 
 struct TcArgs {
   void* out;
@@ -81,67 +86,33 @@ struct TcArgs {
   unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
 };
 
-// First row (of 128) of the slice that cluster rank r reduces and stores: multiples of 16 so that
-// a gate row and its up row (8 apart) stay in one slice.
-__device__ __forceinline__ int slice_start(int r, int c) { return 16 * ((8 * r) / c); }
+// First row (of 128) of the slice that cluster rank r reduces and stores.  SwiGLU: multiples of 16,
+// so that a gate row and its up row (8 apart) stay in one slice; else multiples of 4.
+__device__ __host__ __forceinline__ int slice_start(int r, int c, int mode) {
+  return mode == 2 ? 16 * ((8 * r) / c) : 4 * ((32 * r) / c);
+}
+// The most rows any rank's slice has.
+__device__ __host__ __forceinline__ int slice_rows_max(int c, int mode) {
+  return mode == 2 ? 16 * ((8 + c - 1) / c) : 4 * ((32 + c - 1) / c);
+}
 
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Four consecutive floats of block `rank`'s shared memory, at the address that `local_addr` has here.
-__device__ __forceinline__ float4 ld_dsmem4(unsigned local_addr, unsigned rank) {
+// The address in block `rank`'s shared memory of what lies at `local_addr` here.
+__device__ __forceinline__ unsigned map_to_rank(unsigned local_addr, unsigned rank) {
   unsigned remote;
-  float4 v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
-  return v;
+  return remote;
 }
-// The sum over the cluster, in rank order, of such a group of four: all loads are issued before
-// the first is used.
-__device__ __forceinline__ float4 sum_dsmem4(unsigned local_addr, int C) {
-  float4 p[8];
-#pragma unroll
-  for (int q = 0; q < 8; ++q) p[q] = q < C ? ld_dsmem4(local_addr, q) : make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 s = p[0];
-#pragma unroll
-  for (int q = 1; q < 8; ++q) { s.x += p[q].x; s.y += p[q].y; s.z += p[q].z; s.w += p[q].w; }
-  return s;
+// `bytes` (a multiple of 16, both ends 16-byte aligned) from this block's shared memory into
+// another block's, completing on an mbarrier of that block.
+__device__ __forceinline__ void push_to_rank(unsigned remote_dst, unsigned local_src, unsigned bytes, unsigned remote_bar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(remote_dst), "r"(local_src), "r"(bytes), "r"(remote_bar) : "memory");
 }
-// The loads of such a sum alone, so that the loads of two sums can be in flight together.
-__device__ __forceinline__ void load_dsmem4_set(unsigned local_addr, int C, float4* p) {
-#pragma unroll
-  for (int q = 0; q < 8; ++q) p[q] = q < C ? ld_dsmem4(local_addr, q) : make_float4(0.f, 0.f, 0.f, 0.f);
-}
-__device__ __forceinline__ float4 sum_set(const float4* p) {
-  float4 s = p[0];
-#pragma unroll
-  for (int q = 1; q < 8; ++q) { s.x += p[q].x; s.y += p[q].y; s.z += p[q].z; s.w += p[q].w; }
-  return s;
-}
-// Four consecutive floats of the tile summed over the cluster; a cluster of one reads its own
-// shared memory directly.
-__device__ __forceinline__ float4 part4(const float* partial, unsigned pbase, int off, int C) {
-  if (C == 1) return *reinterpret_cast<const float4*>(partial + off);
-  return sum_dsmem4(pbase + (unsigned)off * 4, C);
-}
-__device__ __forceinline__ void store4(void* out, int out_dtype, size_t idx, float4 v, int valid) {
-  // idx..idx+3 are consecutive elements; `valid` of them exist
-  if (valid == 4 && out_dtype == BN_BF16 && (idx & 3) == 0) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-    uint2 raw;
-    raw.x = *reinterpret_cast<unsigned*>(&a);
-    raw.y = *reinterpret_cast<unsigned*>(&b);
-    *reinterpret_cast<uint2*>((__nv_bfloat16*)out + idx) = raw;
-  } else if (valid == 4 && out_dtype == BN_F32 && (idx & 3) == 0) {
-    *reinterpret_cast<float4*>((float*)out + idx) = v;
-  } else {
-    float e[4] = {v.x, v.y, v.z, v.w};
-    for (int i = 0; i < valid; ++i) store_from_f32(out, out_dtype, idx + i, e[i]);
-  }
-}
-
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 template <int MP>  // batch columns of the accumulator: 16, 32 or 64
 __global__ void __launch_bounds__(TC_THREADS_FOR(MP))
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
@@ -151,8 +122,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
   constexpr int EPI = TC_EPI_FOR(MP);          // epilogue threads
-  constexpr int PSTRIDE = TC_BM + 4;           // floats per batch column of the partial tile in shared memory
-  static_assert(MP * PSTRIDE * 4 <= TC_STAGES * STAGE_BYTES, "the partial tile reuses the ring");
+  constexpr int MPS = MP + 4;  // floats per weight row of the partial tile in shared memory (padded: no bank conflicts)
+  // the partial tile, the slices received from the other blocks (at most 192 rows) and, in mode 3,
+  // the squares of this block's slice reuse the ring
+  static_assert((TC_BM + 192) * MPS * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and received slices reuse the ring");
   constexpr unsigned TMEM_COLS = MP < 32 ? 32 : MP;
   // instruction descriptor: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both
   // K-major, N >> 3 at bit 17, M >> 4 at bit 24
@@ -161,12 +134,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   // the same offset in every block of the cluster (dynamic shared memory starts at the same address)
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned long long* bars = (unsigned long long*)(base + TC_STAGES * STAGE_BYTES);
-  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 1);
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * TC_STAGES + 2);
   float* row_scale = (float*)(tmem_slot + 2);  // [64]: 1 / rms of the input rows (when row_ss is given)
   float* ss_chunk = row_scale + 64;            // [EPI / MP][MP]: partial sums on the way there
-  float* partial = (float*)base;  // [MP][PSTRIDE]: partial[m][row], valid once all MMAs have read the ring
-  float* item_sq = partial + MP * PSTRIDE;  // mode 3: the sum of squares of each epilogue item
-  static_assert((MP * PSTRIDE + 32 * MP) * 4 <= TC_STAGES * STAGE_BYTES, "partial tile and item sums reuse the ring");
+  float* partial = (float*)base;  // [128][MPS]: partial[row][m], valid once all MMAs have read the ring
+  float* recv = partial + TC_BM * MPS;  // [C - 1][slot_rows][MPS]: this block's slice as the other blocks computed it
   __shared__ int s_failed;
   __shared__ int s_acc_ok;
 
@@ -175,6 +147,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int kb0 = (int)((long long)rank * a.k_blocks / C), kb1 = (int)((long long)(rank + 1) * a.k_blocks / C);
   const int n_kb = kb1 - kb0;
   const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES), acc_bar = smem_u32(bars + 2 * TC_STAGES);
+  const unsigned slice_bar = acc_bar + 8;  // completes when the other blocks' copies of this block's slice have landed
+  const int r0 = slice_start(rank, C, a.mode), rows = slice_start(rank + 1, C, a.mode) - r0;
+  const int slot_rows = slice_rows_max(C, a.mode);
+  float* item_sq = recv + (C - 1) * slot_rows * MPS;  // mode 3: [M][rows] squares of the new residual values
+  constexpr int W = MP == 16 ? 1 : 4;  // batch rows per epilogue item (see part two)
+  // mode 3: the residual values and the gain of a thread's first item, fetched while the products run
+  float first_old[W];
+  float first_gain = 0.f;
+#pragma unroll
+  for (int i = 0; i < W; ++i) first_old[i] = 0.f;
 
   if (tid == 0) {
     s_failed = 0;
@@ -186,6 +168,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_init(empty0 + 8 * s, 1);
     }
     mbar_init(acc_bar, 1);
+    mbar_init(slice_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -225,8 +208,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, 0);
       }
-      if (failed) s_failed = 1;
       if (tracing) a.trace[3] = global_timer();  // all loads issued
+      if (failed) s_failed = 1;
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -268,6 +251,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         row_scale[t] = 1.0f / sqrtf(tot * a.inv_width + a.eps);
       }
     }
+    if (a.mode == 3) {
+      pdl_wait();
+      const int t = tid - 64;
+      const int mg = t / rows, nl = t - mg * rows, n = tile * TC_BM + r0 + nl;
+      if (mg * W < a.M && n < a.N) {
+        first_gain = load_as_f32(a.gain, a.gain_dtype, (size_t)n);
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          if (mg * W + i < a.M) first_old[i] = ((const float*)a.out)[(size_t)(mg * W + i) * a.ldo + n];
+      }
+    }
     if (warp == 2 && lane == 0) {
       int ok = mbar_wait(acc_bar, 0, a.status, TC_ERR_ACC_WAIT) ? 1 : 0;
       if (!ok) s_failed = 1;
@@ -289,138 +283,179 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       for (int c = 0; c < COLS; ++c) v[c] = 0.f;
     }
     // every MMA has completed, so nothing reads the ring any more: it now holds the partial tile,
-    // batch column by batch column (consecutive threads write consecutive addresses)
+    // weight row by weight row (a thread writes its row's columns as groups of four)
 #pragma unroll
-    for (int c = 0; c < COLS; ++c) partial[(c0 + c) * PSTRIDE + row] = v[c];
+    for (int c = 0; c < COLS; c += 4)
+      *reinterpret_cast<float4*>(partial + row * MPS + c0 + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+    // the bulk copies below read these values through the asynchronous proxy
+    if (C > 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // what this block is about to receive: its slice from each other block
+    if (tid == 64 && C > 1) mbar_expect_tx(slice_bar, (unsigned)((C - 1) * rows * MPS * 4));
   }
 
-  // ---- all blocks of the cluster have their partial tiles in shared memory
+  // ---- every block of the cluster has its partial tile in shared memory and reads its ring no more
   __syncwarp();
-  cluster_sync_all();
+  if (C > 1) {
+    cluster_sync_all();
+    if (tid == 64) {
+      // each other block gets the rows it owns, as this block computed them; slot: this block's
+      // rank among the others.  Start with the next rank so that the copies spread over the blocks.
+      for (int i = 1; i < C; ++i) {
+        const int d = (rank + i) % C;
+        const int d0 = slice_start(d, C, a.mode), drows = slice_start(d + 1, C, a.mode) - d0;
+        const int slot = rank < d ? rank : rank - 1;
+        push_to_rank(map_to_rank(smem_u32(recv + slot * slot_rows * MPS), d), smem_u32(partial + d0 * MPS),
+                     (unsigned)(drows * MPS * 4), map_to_rank(slice_bar, d));
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
 
   if (warp >= 2) {
     // part two: this block's slice of the rows, summed over the cluster in rank order, then stored.
-    // Consecutive threads take consecutive rows (output columns), so stores coalesce.
+    // Consecutive threads take consecutive rows (output columns), so global accesses coalesce.
     pdl_wait();  // before the first global write of this thread
     const int t = tid - 64;
-    const int r0 = slice_start(rank, C), rows = slice_start(rank + 1, C) - r0;
-    const unsigned pbase = smem_u32(partial);
-    if (a.mode == 0) {
-      // item = (batch row m, group of four weight rows): four consecutive output columns
-      const int groups = rows / 4, total = groups * a.M;
-      if constexpr (MP == 16) {
-        for (int e = t; e < total; e += EPI) {
-          int m = e / groups, rl = (e - m * groups) * 4;
-          int n = tile * TC_BM + r0 + rl;
-          if (n >= a.N) continue;
-          float4 sum = part4(partial, pbase, m * PSTRIDE + r0 + rl, C);
-          if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
-          store4(a.out, a.out_dtype, (size_t)m * a.ldo + n, sum, min(4, a.N - n));
-        }
-      } else {
-      // wider accumulators: two items per turn, the loads of both in flight together
-      for (int e = t; e < total; e += 2 * EPI) {
-        int m[2], n[2];
-        float4 sum[2];
-        if (C == 1) {
+    if (C > 1 && t == 0 && !mbar_wait(slice_bar, 0, a.status, TC_ERR_SLICE_WAIT)) s_failed = 1;
+    // the slices have landed, and (also in a cluster of one) every warp has written its part of the partial tile
+    asm volatile("bar.sync 1, %0;" ::"n"(EPI) : "memory");
+    // One item is a row of the slice and W batch rows: (nl, mg) with batch rows W mg .. W mg + W - 1;
+    // items are numbered mg * rows + nl and a thread takes every EPI-th of them (the division once,
+    // then steps).  With many batch rows the epilogue is bound by the instructions it issues: four
+    // values per load.  With few there are fewer such items than threads and the longest chain of
+    // dependent instructions counts: one value per item.  The blocks' copies of the slice start at
+    // these shared-memory addresses, in rank order:
+    unsigned copy[8];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int eu = min(e + EPI * u, total - 1);
-            m[u] = eu / groups;
-            const int rl = (eu - m[u] * groups) * 4;
-            n[u] = tile * TC_BM + r0 + rl;
-            sum[u] = *reinterpret_cast<const float4*>(partial + m[u] * PSTRIDE + r0 + rl);
-          }
-        } else {
-          float4 p[2][8];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int eu = min(e + EPI * u, total - 1);
-            m[u] = eu / groups;
-            const int rl = (eu - m[u] * groups) * 4;
-            n[u] = tile * TC_BM + r0 + rl;
-            load_dsmem4_set(pbase + (unsigned)((m[u] * PSTRIDE + r0 + rl) * 4), C, p[u]);
-          }
-          sum[0] = sum_set(p[0]);
-          sum[1] = sum_set(p[1]);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (e + EPI * u >= total || n[u] >= a.N) continue;
-          float4 v = sum[u];
-          if (a.row_ss != nullptr) { const float rs = row_scale[m[u]]; v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs; }
-          store4(a.out, a.out_dtype, (size_t)m[u] * a.ldo + n[u], v, min(4, a.N - n[u]));
-        }
+    for (int q = 0; q < 8; ++q)
+      copy[q] = smem_u32(q == rank ? partial + r0 * MPS : recv + (q < rank ? q : q - 1) * slot_rows * MPS);
+    auto load_copy = [&](unsigned addr, float* v) {
+      if constexpr (W == 4)
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(addr));
+      else
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(addr));
+    };
+    auto slice_values = [&](int nl, int mg, float* v) {
+      const unsigned off = (unsigned)(nl * MPS + mg * W) * 4u;
+      if (C == 1) {  // predicated-off loads and additions would still take issue slots
+        load_copy(copy[0] + off, v);
+        return;
       }
+      float p[8][W];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < C) load_copy(copy[q] + off, p[q]);
+#pragma unroll
+      for (int i = 0; i < W; ++i) v[i] = p[0][i];
+#pragma unroll
+      for (int q = 1; q < 8; ++q)
+        if (q < C) {
+#pragma unroll
+          for (int i = 0; i < W; ++i) v[i] += p[q][i];
+        }
+    };
+    const int mgroups = (a.M + W - 1) / W;
+    if (a.mode == 0) {
+      const int dm = EPI / rows, dn = EPI - dm * rows;
+      int mg = t / rows, nl = t - mg * rows;
+      while (mg < mgroups) {
+        const int n = tile * TC_BM + r0 + nl;
+        if (n < a.N) {
+          float v[W];
+          slice_values(nl, mg, v);
+#pragma unroll
+          for (int i = 0; i < W; ++i) {
+            const int m = mg * W + i;
+            if (m < a.M) store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + n, a.row_ss != nullptr ? v[i] * row_scale[m] : v[i]);
+          }
+        }
+        mg += dm; nl += dn;
+        if (nl >= rows) { nl -= rows; ++mg; }
       }
     } else if (a.mode == 3) {
       // out is the float32 residual [M, ldo]: add, write back, hand on residual * gain, and leave
-      // this slice's sum of squares per row (items in a fixed order, then one thread per row)
-      const int groups = rows / 4;
+      // this slice's sum of squares per row (the squares in a fixed place each, then one thread
+      // per batch row adds them in order)
       float* res = (float*)a.out;
-      for (int e = t; e < groups * a.M; e += EPI) {
-        int m = e / groups, rl = (e - m * groups) * 4;
-        int n = tile * TC_BM + r0 + rl;
-        float sq = 0.f;
-        if (n < a.N) {
-          float4 sum = part4(partial, pbase, m * PSTRIDE + r0 + rl, C);
-          if (a.row_ss != nullptr) { const float rs = row_scale[m]; sum.x *= rs; sum.y *= rs; sum.z *= rs; sum.w *= rs; }
-          const int valid = min(4, a.N - n);
-          float v[4] = {sum.x, sum.y, sum.z, sum.w};
-          float* rp = res + (size_t)m * a.ldo + n;
-          float gv[4] = {0.f, 0.f, 0.f, 0.f};
+      const int dm = EPI / rows, dn = EPI - dm * rows;
+      int mg = t / rows, nl = t - mg * rows;
+      bool first = true;
+      while (mg < mgroups) {
+        const int n = tile * TC_BM + r0 + nl;
+        float sq[W];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (i < valid) {
-              v[i] += rp[i];
-              rp[i] = v[i];
-              gv[i] = v[i] * load_as_f32(a.gain, a.gain_dtype, (size_t)(n + i));
-              sq += v[i] * v[i];
+        for (int i = 0; i < W; ++i) sq[i] = 0.f;
+        if (n < a.N) {
+          float v[W];
+          slice_values(nl, mg, v);
+          const float gain = first ? first_gain : load_as_f32(a.gain, a.gain_dtype, (size_t)n);
+#pragma unroll
+          for (int i = 0; i < W; ++i) {
+            const int m = mg * W + i;
+            if (m < a.M) {
+              float* rp = res + (size_t)m * a.ldo + n;
+              const float nv = (first ? first_old[i] : *rp) + (a.row_ss != nullptr ? v[i] * row_scale[m] : v[i]);
+              *rp = nv;
+              a.xg[(size_t)m * a.N + n] = __float2bfloat16_rn(nv * gain);
+              sq[i] = nv * nv;
             }
           }
-          store4(a.xg, BN_BF16, (size_t)m * a.N + n, make_float4(gv[0], gv[1], gv[2], gv[3]), valid);
         }
-        item_sq[e] = sq;
+#pragma unroll
+        for (int i = 0; i < W; ++i) item_sq[(mg * W + i) * rows + nl] = sq[i];
+        first = false;
+        mg += dm; nl += dn;
+        if (nl >= rows) { nl -= rows; ++mg; }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(EPI) : "memory");
       for (int m = t; m < a.M; m += EPI) {
         float ss = 0.f;
-        for (int gq = 0; gq < groups; ++gq) ss += item_sq[m * groups + gq];
+        for (int i = 0; i < rows; i += 4) {  // slices are multiples of four rows
+          const float4 q4 = *reinterpret_cast<const float4*>(item_sq + m * rows + i);
+          ss += q4.x; ss += q4.y; ss += q4.z; ss += q4.w;
+        }
         a.ss_out[(size_t)(tile * C + rank) * a.ss_out_stride + m] = ss;
       }
     } else {
       // rows 16j..16j+7 of a tile are gate rows, rows 16j+8..16j+15 the up rows of the same indices;
-      // item = (batch row m, four gate rows and their up rows): four consecutive activations
-      const int groups = rows / 8;
-      for (int e = t; e < groups * a.M; e += EPI) {
-        int m = e / groups, gq = e - m * groups;
-        int rg = r0 + (gq >> 1) * 16 + (gq & 1) * 4;  // first of the four gate rows within the tile
-        int n = tile * TC_BM + rg;
-        if (n >= a.N) continue;
-        float4 g = part4(partial, pbase, m * PSTRIDE + rg, C), u = part4(partial, pbase, m * PSTRIDE + rg + 8, C);
-        if (a.row_ss != nullptr) {
-          const float rs = row_scale[m];
-          g.x *= rs; g.y *= rs; g.z *= rs; g.w *= rs;
-          u.x *= rs; u.y *= rs; u.z *= rs; u.w *= rs;
+      // item = (gate row, W batch rows); consecutive gate rows are consecutive activations.  The
+      // exponential and the division are the fast ones (relative error about 2^-21, far below the
+      // bfloat16 the activations are stored in).
+      const int gates = rows / 2;
+      const int dm = EPI / gates, dj = EPI - dm * gates;
+      int mg = t / gates, j = t - mg * gates;
+      while (mg < mgroups) {
+        const int nl = (j >> 3) * 16 + (j & 7);  // the gate row within the slice
+        const int n = tile * TC_BM + r0 + nl;
+        if (n < a.N) {
+          float g[W], u[W];
+          slice_values(nl, mg, g);
+          slice_values(nl + 8, mg, u);
+          const int col = (n >> 4) * 8 + (n & 7);
+#pragma unroll
+          for (int i = 0; i < W; ++i) {
+            const int m = mg * W + i;
+            if (m < a.M) {
+              const float rs = a.row_ss != nullptr ? row_scale[m] : 1.0f;
+              const float gv = g[i] * rs, uv = u[i] * rs;
+              store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + col, __fdividef(gv, 1.0f + __expf(-gv)) * uv);
+            }
+          }
         }
-        float4 act;
-        act.x = g.x / (1.0f + expf(-g.x)) * u.x;
-        act.y = g.y / (1.0f + expf(-g.y)) * u.y;
-        act.z = g.z / (1.0f + expf(-g.z)) * u.z;
-        act.w = g.w / (1.0f + expf(-g.w)) * u.w;
-        int i = (n >> 4) * 8 + (n & 7);
-        store4(a.out, a.out_dtype, (size_t)m * a.ldo + i, act, 4);  // N is a multiple of 16: all four exist
+        mg += dm; j += dj;
+        if (j >= gates) { j -= gates; ++mg; }
       }
     }
     if (tracing && warp == 2 && lane == 0) a.trace[5] = global_timer();  // epilogue done
   }
 
-  __syncwarp();
-  cluster_sync_all();  // no block leaves while another still reads its partial tile
+  // No block reads another's shared memory, and every copy into this block has landed (the wait on
+  // slice_bar above); what is left before leaving is that this block's own copies have read their source.
+  if (tid == 64 && C > 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (s_failed) {
-    // a wait gave up: loads that were issued may still be landing in this block's shared memory
+    // a wait gave up: loads and copies that were issued may still be landing in this block's shared memory
     unsigned long long t0 = global_timer();
     while (global_timer() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
@@ -464,7 +499,7 @@ template <int MP>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int cluster, int tiles,
                      cudaStream_t stream) {
   constexpr int TC_STAGES = TC_STAGES_FOR(MP);
-  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 1) * 8 + 16 + (64 + 256) * 4 + 1024;
+  size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + MP * TC_BK * 2) + (2 * TC_STAGES + 2) * 8 + 16 + (64 + 256) * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -541,6 +576,15 @@ extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_
   if (cluster > k_blocks) {
     if (mode == 3) return BN_ERR_BAD_ARG;  // the caller sized ss_out for the cluster it named
     cluster = k_blocks;
+  }
+  {
+    // the partial tile, the received slices and (mode 3) the squares must fit in the ring they reuse
+    const int stages = TC_STAGES_FOR(mp == 16 ? 16 : (mp == 32 ? 32 : 64));
+    const long long ring = (long long)stages * (TC_BM * TC_BK * 2 + mp * TC_BK * 2);
+    const int max_rows = slice_rows_max(cluster, mode);
+    long long need = (long long)(TC_BM + (cluster - 1) * max_rows) * (mp + 4) * 4;
+    if (mode == 3) need += (long long)(M + 3) * max_rows * 4;
+    if (need > ring) return BN_ERR_BAD_ARG;
   }
   CUtensorMap mw, mx;
   if (!tma_map_bf16_rows(&mw, w, N, K, TC_BM) || !tma_map_bf16_rows(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
