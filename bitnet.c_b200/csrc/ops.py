@@ -434,7 +434,8 @@ def check_tc_status(device) -> None:
         what = {1: "linear_tc: a stage never filled (TMA load)", 2: "linear_tc: a stage was never released (MMA commit)",
                 3: "linear_tc: the accumulator never completed",
                 4: "attention_decode_tc: a cache page never arrived (TMA load)",
-                5: "attention_prefill_tc: a wait inside the kernel gave up"}.get(code, f"code {code}")
+                5: "attention_prefill_tc: a wait inside the kernel gave up",
+                6: "linear_tc: a slice of partial sums from another block of the cluster never arrived"}.get(code, f"code {code}")
         raise KernelError(f"{what}; the result of that launch is not valid")
 
 
