@@ -453,38 +453,30 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     dt_cluster_sync();
     if (tr) tr[8] = global_timer();
     const unsigned a_ml = smem_u32(ml_fin), a_o = smem_u32(o_fin);
-    float* wz = ml_part;  // [16][8]: each split's weight, divided by the total sum (ml_part is free now)
-    if (tid < G) {
-      float mz[8], lz[8], m = -INFINITY;
-#pragma unroll
-      for (int z = 0; z < 8; ++z) {
-        const bool on = z >= z_lo && z <= z_hi;
-        mz[z] = on ? dt_ld_dsmem(a_ml + (unsigned)(tid * 2) * 4, (unsigned)z) : -INFINITY;
-        lz[z] = on ? dt_ld_dsmem(a_ml + (unsigned)(tid * 2 + 1) * 4, (unsigned)z) : 0.f;
-        m = fmaxf(m, mz[z]);
-      }
-      float den = 0.f;
-#pragma unroll
-      for (int z = 0; z < 8; ++z) {
-        mz[z] = (mz[z] == -INFINITY) ? 0.f : exp2f(mz[z] - m);
-        den += mz[z] * lz[z];
-      }
-#pragma unroll
-      for (int z = 0; z < 8; ++z) wz[tid * 8 + z] = mz[z] / den;
-    }
-    __syncthreads();
     const int n_act = z_hi - z_lo + 1, mine = (int)blockIdx.z - z_lo;
     const int total = G * head_dim, per = (total + n_act - 1) / n_act;
     for (int i = mine * per + tid; i < min(total, (mine + 1) * per); i += DT_THREADS) {
       int g = i / head_dim, d = i - g * head_dim;
-      float v[8];
+      // every split's maximum, sum and value of this element in one round of remote loads (a thread
+      // works out the weights of its row itself: a second round would cost more than the arithmetic)
+      float mz[8], lz[8], v[8], m = -INFINITY;
 #pragma unroll
-      for (int z = 0; z < 8; ++z)
-        v[z] = (z >= z_lo && z <= z_hi) ? dt_ld_dsmem(a_o + (unsigned)(g * HD + d) * 4, (unsigned)z) : 0.f;
-      float num = 0.f;
+      for (int z = 0; z < 8; ++z) {
+        const bool on = z >= z_lo && z <= z_hi;
+        mz[z] = on ? dt_ld_dsmem(a_ml + (unsigned)(g * 2) * 4, (unsigned)z) : -INFINITY;
+        lz[z] = on ? dt_ld_dsmem(a_ml + (unsigned)(g * 2 + 1) * 4, (unsigned)z) : 0.f;
+        v[z] = on ? dt_ld_dsmem(a_o + (unsigned)(g * HD + d) * 4, (unsigned)z) : 0.f;
+      }
 #pragma unroll
-      for (int z = 0; z < 8; ++z) num += wz[g * 8 + z] * v[z];
-      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num);
+      for (int z = 0; z < 8; ++z) m = fmaxf(m, mz[z]);
+      float den = 0.f, num = 0.f;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        const float w = (mz[z] == -INFINITY) ? 0.f : exp2f(mz[z] - m);
+        den += w * lz[z];
+        num += w * v[z];
+      }
+      a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num / den);
     }
     if (tr) tr[10] = global_timer();
     dt_cluster_sync();  // no block leaves while another still reads its result
