@@ -7,8 +7,8 @@
 //
 // A tile is 128 weight rows.  Weights with few rows have fewer tiles than the GPU has SMs, so the
 // inner dimension of a tile is split over a thread-block cluster of C blocks (C x tiles is about
-// one and a half times the number of SMs): block r of the cluster multiplies k-blocks [r KB/C, (r+1) KB/C).  Each block
-// leaves its float32 partial tile in its own shared memory; after a cluster barrier every block
+// one and a half times the number of SMs): block r of the cluster multiplies k-blocks
+// [r KB/C, (r+1) KB/C).  Each block leaves its float32 partial tile in its own shared memory; after a cluster barrier every block
 // sends each other block the slice of rows that block owns, as one bulk copy from shared memory to
 // the owner's shared memory that completes on an mbarrier there (distributed shared memory; a
 // copy is posted and needs no round trip, where loads from another block's shared memory took 1
@@ -16,14 +16,14 @@
 // epilogue on it.  Nothing goes through global memory, all blocks of a tile finish together, and
 // the order of the additions is fixed.
 //
-// A block of 192 threads:
+// A block of 192 threads (320 with the wider accumulators):
 //   warp 0     one thread issues the TMA loads of W and x tiles into a ring of stages and arms each
 //              stage's "full" mbarrier with the bytes to expect;
 //   warp 1     allocates tensor memory; one thread waits for "full", issues four MMAs per stage,
 //              commits them to the stage's "empty" mbarrier and at the end to "accumulator full";
 //   warps 2-5  wait for the accumulator, move it from tensor memory to shared memory
-//              (tcgen05.ld, one weight row per thread) and, after the cluster barrier, reduce and
-//              store with consecutive threads on consecutive output columns.
+//              (tcgen05.ld, one weight row per thread), send and receive the slices, add them up
+//              and store with consecutive threads on consecutive output columns.
 // Tiles are 128-byte swizzled both by TMA and in the MMA's shared-memory descriptors.  No register
 // ever holds a weight, so the bytes in flight per SM are the ring's size (about 100 KB); a block
 // uses less than half of an SM's shared memory so that a block of the next kernel fits beside it.
@@ -112,7 +112,6 @@ __device__ __forceinline__ void push_to_rank(unsigned remote_dst, unsigned local
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(remote_dst), "r"(local_src), "r"(bytes), "r"(remote_bar) : "memory");
 }
-__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 template <int MP>  // batch columns of the accumulator: 16, 32 or 64
 __global__ void __launch_bounds__(TC_THREADS_FOR(MP))
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
