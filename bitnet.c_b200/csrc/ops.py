@@ -37,7 +37,12 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
 
 
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device as a raw handle (asked of torch's C layer directly:
+    ``torch.cuda.current_stream()`` builds a Python object per call, several microseconds of a launch)."""
+    try:
+        return c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
+    except AttributeError:  # a torch without these entry points
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:

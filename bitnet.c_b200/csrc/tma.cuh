@@ -7,6 +7,7 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#include <mutex>
 
 #define TMA_WAIT_NS 2000000000ull  // two seconds
 
@@ -94,17 +95,57 @@ static bool tma_map_bf16_rows(CUtensorMap* map, const void* ptr, unsigned long l
                               int box_rows) {
   return tma_map_bf16_strided(map, ptr, rows, cols, cols, box_rows);
 }
+// Encoded maps are kept: a map is a pure function of its arguments, weights and caches are
+// described again at every launch, and the driver call that encodes one costs a microsecond or two
+// of a launch that is otherwise ten.  A small direct-mapped table per library; a slot that holds
+// another key is overwritten.
+struct TmaMapSlot {
+  bool used;
+  int kind, box_rows;
+  const void* ptr;
+  unsigned long long a, b, c;
+  CUtensorMap map;
+};
+#define TMA_MAP_SLOTS 1024
+static TmaMapSlot g_tma_maps[TMA_MAP_SLOTS];
+static std::mutex g_tma_maps_lock;
+static unsigned tma_map_slot(int kind, const void* ptr, unsigned long long a, unsigned long long b, unsigned long long c,
+                             int box_rows) {
+  unsigned long long h = (unsigned long long)(uintptr_t)ptr * 0x9E3779B97F4A7C15ull;
+  h ^= (a + 0x7F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
+  h ^= (b * 31 + c * 131 + (unsigned long long)box_rows * 7 + (unsigned long long)kind) * 0x94D049BB133111EBull;
+  return (unsigned)(h >> 40) % TMA_MAP_SLOTS;
+}
+static bool tma_map_lookup(int kind, const void* ptr, unsigned long long a, unsigned long long b, unsigned long long c,
+                           int box_rows, CUtensorMap* out) {
+  std::lock_guard<std::mutex> hold(g_tma_maps_lock);
+  const TmaMapSlot& s = g_tma_maps[tma_map_slot(kind, ptr, a, b, c, box_rows)];
+  if (!s.used || s.kind != kind || s.ptr != ptr || s.a != a || s.b != b || s.c != c || s.box_rows != box_rows) return false;
+  *out = s.map;
+  return true;
+}
+static void tma_map_keep(int kind, const void* ptr, unsigned long long a, unsigned long long b, unsigned long long c,
+                         int box_rows, const CUtensorMap* map) {
+  std::lock_guard<std::mutex> hold(g_tma_maps_lock);
+  TmaMapSlot& s = g_tma_maps[tma_map_slot(kind, ptr, a, b, c, box_rows)];
+  s.used = true; s.kind = kind; s.ptr = ptr; s.a = a; s.b = b; s.c = c; s.box_rows = box_rows; s.map = *map;
+}
+
 static bool tma_map_bf16_strided(CUtensorMap* map, const void* ptr, unsigned long long rows, unsigned long long cols,
                                  unsigned long long row_stride, int box_rows) {
+  if (tma_map_lookup(0, ptr, rows, cols, row_stride, box_rows, map)) return true;
   PFN_cuTensorMapEncodeTiled enc = tma_encoder();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  tma_map_keep(0, ptr, rows, cols, row_stride, box_rows, map);
+  return true;
 }
 
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
@@ -118,13 +159,17 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map
 // (layout in shared memory as for tma_map_bf16_rows).  Coordinates: (column, row in page, page).
 static bool tma_map_bf16_pages(CUtensorMap* map, const void* ptr, unsigned long long pages,
                                unsigned long long rows_per_page, unsigned long long cols, int box_rows) {
+  if (tma_map_lookup(1, ptr, pages, rows_per_page, cols, box_rows, map)) return true;
   PFN_cuTensorMapEncodeTiled enc = tma_encoder();
   if (!enc) return false;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows_per_page, (cuuint64_t)pages};
   cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows_per_page * cols * 2};
   cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  tma_map_keep(1, ptr, pages, rows_per_page, cols, box_rows, map);
+  return true;
 }
