@@ -47,7 +47,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const unsigned s_v = s_k + 2 * TILE_BYTES;     // two stages
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int seq = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x], h = blockIdx.y;
+  // blocks start in the order of their index, heads fastest: tiles are listed by rising work (the
+  // keys they see), the last ones start first over all heads, and the query heads of one key/value
+  // head run side by side
+  const int blk = gridDim.y - 1 - blockIdx.y;
+  const int seq = tile_seq[blk], row0 = tile_row0[blk], h = blockIdx.x;
   const int kvh = h / (n_heads / n_kv_heads);
   const int start = seq_start[seq], n_new = seq_start[seq + 1] - start, pos0 = seq_pos0[seq];
   const int* pt = page_table + (size_t)slots[seq] * pt_stride;
@@ -236,7 +240,8 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
-  dim3 grid(n_tiles, n_heads);
+  if (n_tiles > 65535) return BN_ERR_BAD_ARG;
+  dim3 grid(n_heads, n_tiles);
   BN_LAUNCH((attention_prefill_kernel<HD>), grid, PF_THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim,
       scale * 1.4426950408889634f, window, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,

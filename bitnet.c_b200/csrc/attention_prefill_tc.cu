@@ -110,8 +110,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int blk = gridDim.x - 1 - blockIdx.x;  // later tiles of a sequence see more keys: start them first
-  const int seq = a.tile_seq[blk], row0 = a.tile_row0[blk], h = blockIdx.y;
+  // Blocks start in the order of their index, heads fastest: the last tiles of a sequence see the
+  // most keys and start first, over all heads, so that the short tiles fill the tail; and the query
+  // heads that share a key/value head run side by side and find its pages in the L2.
+  const int blk = gridDim.y - 1 - blockIdx.y;
+  const int seq = a.tile_seq[blk], row0 = a.tile_row0[blk], h = blockIdx.x;
   const int head_dim = a.head_dim;
   const int kvh = h / (a.n_heads / a.n_kv_heads);
   const int start = a.seq_start[seq], n_new = a.seq_start[seq + 1] - start, pos0 = a.seq_pos0[seq];
@@ -397,7 +400,8 @@ static int launch_pt(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
-  dim3 grid(n_tiles, a.n_heads);
+  if (n_tiles > 65535) return BN_ERR_BAD_ARG;
+  dim3 grid(a.n_heads, n_tiles);
   BN_LAUNCH((attention_prefill_tc_kernel<HD, KS, VS>), grid, PT_THREADS, smem, stream, mq, mk, mv, a);
   return BN_OK;
 }

@@ -59,9 +59,11 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
     new = [len(s.tokens) for s in seqs]
     T = sum(new)
     n_rows = sum(len(s.want) for s in seqs)
-    tiles = [(i, r) for i, c in enumerate(new) for r in range(0, c, TILE_ROWS)]
+    # tiles by rising work (the positions a tile's queries see): the prefill attention kernels start
+    # the last of the list first, so that the short ones fill the tail of the launch
+    tiles = sorted(((i, r) for i, c in enumerate(new) for r in range(0, c, TILE_ROWS)), key=lambda t: lengths[t[0]] + t[1])
     n_tiles = len(tiles)
-    wide = [(i, r) for i, c in enumerate(new) for r in range(0, c, WIDE_TILE_ROWS)]
+    wide = sorted(((i, r) for i, c in enumerate(new) for r in range(0, c, WIDE_TILE_ROWS)), key=lambda t: lengths[t[0]] + t[1])
     n_wide = len(wide)
     buf = np.empty(3 * T + 3 * n + 1 + n_rows + 2 * n_tiles + 2 * n_wide, dtype=np.int32)
     tokens, tok_seq, tok_pos = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
