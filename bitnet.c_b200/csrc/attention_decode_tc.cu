@@ -540,11 +540,17 @@ extern "C" int bn_attention_decode_tc_trace_read(unsigned long long* host, int n
   return cudaMemcpy(host, g_dt_trace, (size_t)n * 8 * 16 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
 
+// Dynamic shared memory of a block: alignment slack, the ring of key and value pages, the query
+// tile, the new key and value, the warps' and the block's maxima and sums, the ring's mbarriers,
+// the rotation table and the warps' weights.
+template <int HD, int DT_STAGES>
+static constexpr size_t dt_smem_bytes() {
+  return 1024 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + (size_t)DT_ROWS * HD * 2 + 2 * HD * 2 +
+         (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float) + DT_STAGES * 8 + HD * sizeof(float) + 4 * DT_ROWS * sizeof(float);
+}
 template <int HD, int DT_STAGES>
 static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
-  size_t smem = 1024 + (size_t)DT_STAGES * 2 * BN_PAGE * HD * 2 + (size_t)DT_ROWS * HD * 2 + 2 * HD * 2 +
-                (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float) + DT_STAGES * 8 + HD * sizeof(float) +
-                4 * DT_ROWS * sizeof(float);
+  size_t smem = dt_smem_bytes<HD, DT_STAGES>();
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<HD, DT_STAGES>,
@@ -561,11 +567,35 @@ static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs
   BN_LAUNCH((attention_decode_tc_kernel<HD, DT_STAGES>), grid, DT_THREADS, smem, stream, mk, mv, a);
   return BN_OK;
 }
-// Short runs (at most two pages per block) take the two-stage ring: less shared memory, more
-// blocks per SM, and both pages are requested at once anyway.
+// How many blocks of a ring depth fit on the device at once (asked of the runtime once per kernel).
+template <int HD, int DT_STAGES>
+static long long dt_slots() {
+  static long long slots = 0;
+  if (!slots) {
+    size_t smem = dt_smem_bytes<HD, DT_STAGES>();
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaFuncSetAttribute(attention_decode_tc_kernel<HD, DT_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tc_kernel<HD, DT_STAGES>, DT_THREADS, smem) != cudaSuccess ||
+        cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || per_sm <= 0 || sms <= 0)
+      slots = 2 * 148;
+    else
+      slots = (long long)per_sm * sms;
+  }
+  return slots;
+}
+// Ring depth.  Short runs (at most two pages per block) take two stages: both pages are requested
+// at once anyway.  Otherwise three stages keep a block's pages coming, but two let a third block
+// share the SM (shared memory is the limit at head size 128): when that saves a wave of blocks it
+// wins although each block runs about an eighth slower (40 heads of 128, 2,000 positions, 8
+// sequences = 320 blocks: 77 us with three stages in two waves, 53 us with two stages in one).
 template <int HD>
 static int launch_dt(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
   if (a.pages_per_block <= 2) return launch_dt2<HD, 2>(mk, mv, a, grid, stream);
+  const long long blocks = (long long)grid.x * grid.y * grid.z;
+  const long long s3 = dt_slots<HD, 3>(), s2 = dt_slots<HD, 2>();
+  const long long w3 = (blocks + s3 - 1) / s3, w2 = (blocks + s2 - 1) / s2;
+  if (w2 * 115 < w3 * 100) return launch_dt2<HD, 2>(mk, mv, a, grid, stream);
   return launch_dt2<HD, 3>(mk, mv, a, grid, stream);
 }
 
