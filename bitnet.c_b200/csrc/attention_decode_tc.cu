@@ -37,6 +37,7 @@
 #include "mma.cuh"
 
 #define DT_THREADS 128
+#define DT_SPLIT_MIN_PAGES 8  // a sequence with fewer visible pages is not split (the merge would cost more than the walk)
 #define DT_ROWS 16  // query heads per block (the MMA's 16 rows)
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in the query tile, whose rows hold HD bfloat16 (XOR swizzle).
@@ -126,9 +127,14 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   // pages that hold a visible key, and this block's run of them
   const int p_lo = lo / BN_PAGE, p_hi = pos / BN_PAGE;
-  const int my_lo = max(p_lo, (int)blockIdx.z * a.pages_per_block);
-  const int my_hi = min(p_hi, (int)(blockIdx.z + 1) * a.pages_per_block - 1);
-  const int z_lo = p_lo / a.pages_per_block, z_hi = p_hi / a.pages_per_block;  // splits with a visible page
+  // The blocks of a sequence share its visible pages evenly (as many as the launch gives each
+  // sequence, whatever the bound it was sized for); a sequence too short for a split to pay is the
+  // first block's alone.
+  const int vis = p_hi - p_lo + 1;
+  const int ppb = vis < DT_SPLIT_MIN_PAGES ? vis : min(a.pages_per_block, (vis + (int)gridDim.z - 1) / (int)gridDim.z);
+  const int my_lo = p_lo + (int)blockIdx.z * ppb;
+  const int my_hi = min(p_hi, my_lo + ppb - 1);
+  const int z_lo = 0, z_hi = (vis - 1) / ppb;  // splits with a visible page
   const bool alone = (z_lo == z_hi);
   const bool clustered = a.cluster != 0 && !alone;  // the same for every block of the cluster
   if (my_lo > my_hi) {

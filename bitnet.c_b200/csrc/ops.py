@@ -311,24 +311,26 @@ def decode_splits(pages: int, blocks_per_split: int) -> int:
     """How many blocks share one sequence's pages in ``attention_decode_fused``.
 
     A block walks its pages one after another, about 0.75 us each; blocks that share a sequence
-    merge their results inside a thread-block cluster, which costs about as much as six pages.
+    merge their results inside a thread-block cluster, which costs about as much as five pages.
     So a split pays only when it shortens the walk by more than that: few sequences, or long
     ones.  Up to eight blocks per sequence are one cluster; more (up to 32) merge through global
     memory block by block, which costs as much as 0.7 pages more for every block and pays from
-    some 16,000 positions on for one or two sequences.  No more than 256 blocks in all: clusters are placed within one
-    GPC, and beyond that number a second wave of blocks starts.
-    ``pages`` is the bound the step was recorded for; sequences are taken to fill three
-    quarters of it.  Measured at 8 key/value heads of 128 (us, 520 positions, 1 against the
-    chosen number of splits): 1 sequence 10.1 / 6.6, 4: 10.4 / 8.8, 8: 11.2 / 11.2, 12: 11.9
-    (two splits 14.1, three 21.7), 16: 12.4 (two 14.7); at 2,000 positions 8 sequences
-    31.3 / 16.5, 16: 34.0 / 26.5; one sequence of 64,000 positions: 8 splits 111, 32 splits 59."""
+    some 16,000 positions on for one or two sequences.  No more than 256 blocks in all: clusters
+    are placed within one GPC, and beyond that number a second wave of blocks starts.
+    ``pages`` is the bound the step was recorded for; sequences are taken to fill three quarters
+    of it, and the kernel shares a sequence's pages evenly among its blocks whatever the bound.
+    Measured at 8 key/value heads of 128 (us, 520 positions, 1 against the chosen number of
+    splits): 1 sequence 10.3 / 5.5, 4: 10.6 / 7.6, 8: 11.4 / 10.2, 12: 12.2 / 11.2 (three
+    splits 18.6), 16: 12.6 / 12.2 (four 20.1), 24: 13.6 (two 15.7); at 2,000 positions 8
+    sequences 31.7 / 15.6, 16: 34.9 / 26.0; one sequence of 64,000 positions: 8 splits 111, 32
+    splits 59."""
     cap = max(1, min(pages, 256 // max(1, blocks_per_split)))
     filled = 0.75 * pages
     best, best_cost = 1, filled
     for s in (2, 3, 4, 5, 6, 7, 8, 12, 16, 24, 32):
         if s > cap:
             break
-        cost = min(float((pages + s - 1) // s), filled) + (6.0 if s <= 8 else 6.0 + 0.7 * s)
+        cost = float(-(-int(filled) // s)) + (5.0 if s <= 8 else 5.0 + 0.7 * s)
         if cost < best_cost:
             best, best_cost = s, cost
     return best
