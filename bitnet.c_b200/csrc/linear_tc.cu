@@ -156,11 +156,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int slot_rows = slice_rows_max(C, a.mode);
   float* item_sq = recv + (C - 1) * slot_rows * MPS;  // mode 3: [M][rows] squares of the new residual values
   constexpr int W = MP == 16 ? 1 : 4;  // batch rows per epilogue item (see part two)
-  // mode 3: the residual values and the gain of a thread's first item, fetched while the products run
-  float first_old[W];
-  float first_gain = 0.f;
+  // mode 3: the residual values and the gains of a thread's first items, fetched while the products run
+  constexpr int PRE = 2;  // so many items per thread (few threads have more)
+  float pre_old[PRE][W], pre_gain[PRE];
 #pragma unroll
-  for (int i = 0; i < W; ++i) first_old[i] = 0.f;
+  for (int k = 0; k < PRE; ++k) {
+    pre_gain[k] = 0.f;
+#pragma unroll
+    for (int i = 0; i < W; ++i) pre_old[k][i] = 0.f;
+  }
 
   if (tid == 0) {
     s_failed = 0;
@@ -258,12 +262,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (a.mode == 3) {
       pdl_wait();
       const int t = tid - 64;
-      const int mg = t / rows, nl = t - mg * rows, n = tile * TC_BM + r0 + nl;
-      if (mg * W < a.M && n < a.N) {
-        first_gain = load_as_f32(a.gain, a.gain_dtype, (size_t)n);
+      const int dm = EPI / rows, dn = EPI - dm * rows;
+      int mg = t / rows, nl = t - mg * rows;
 #pragma unroll
-        for (int i = 0; i < W; ++i)
-          if (mg * W + i < a.M) first_old[i] = ((const float*)a.out)[(size_t)(mg * W + i) * a.ldo + n];
+      for (int k = 0; k < PRE; ++k) {
+        const int n = tile * TC_BM + r0 + nl;
+        if (mg * W < a.M && n < a.N) {
+          pre_gain[k] = load_as_f32(a.gain, a.gain_dtype, (size_t)n);
+#pragma unroll
+          for (int i = 0; i < W; ++i)
+            if (mg * W + i < a.M) pre_old[k][i] = ((const float*)a.out)[(size_t)(mg * W + i) * a.ldo + n];
+        }
+        mg += dm; nl += dn;
+        if (nl >= rows) { nl -= rows; ++mg; }
       }
     }
     if (warp == 2 && lane == 0) {
@@ -383,8 +394,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       float* res = (float*)a.out;
       const int dm = EPI / rows, dn = EPI - dm * rows;
       int mg = t / rows, nl = t - mg * rows;
-      bool first = true;
-      while (mg < mgroups) {
+      // one item; old and gain: its residual values and gain if they were fetched ahead
+      auto residual_item = [&](int mg, int nl, const float* old, float gain_ahead) {
         const int n = tile * TC_BM + r0 + nl;
         float sq[W];
 #pragma unroll
@@ -392,13 +403,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         if (n < a.N) {
           float v[W];
           slice_values(nl, mg, v);
-          const float gain = first ? first_gain : load_as_f32(a.gain, a.gain_dtype, (size_t)n);
+          const float gain = old != nullptr ? gain_ahead : load_as_f32(a.gain, a.gain_dtype, (size_t)n);
 #pragma unroll
           for (int i = 0; i < W; ++i) {
             const int m = mg * W + i;
             if (m < a.M) {
               float* rp = res + (size_t)m * a.ldo + n;
-              const float nv = (first ? first_old[i] : *rp) + (a.row_ss != nullptr ? v[i] * row_scale[m] : v[i]);
+              const float nv = (old != nullptr ? old[i] : *rp) + (a.row_ss != nullptr ? v[i] * row_scale[m] : v[i]);
               *rp = nv;
               a.xg[(size_t)m * a.N + n] = __float2bfloat16_rn(nv * gain);
               sq[i] = nv * nv;
@@ -407,7 +418,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
 #pragma unroll
         for (int i = 0; i < W; ++i) item_sq[(mg * W + i) * rows + nl] = sq[i];
-        first = false;
+      };
+#pragma unroll
+      for (int k = 0; k < PRE; ++k) {
+        if (mg < mgroups) residual_item(mg, nl, pre_old[k], pre_gain[k]);
+        mg += dm; nl += dn;
+        if (nl >= rows) { nl -= rows; ++mg; }
+      }
+      while (mg < mgroups) {
+        residual_item(mg, nl, nullptr, 0.f);
         mg += dm; nl += dn;
         if (nl >= rows) { nl -= rows; ++mg; }
       }
