@@ -37,6 +37,19 @@ def test_greedy_generation_matches_plain_in_float32(models):
     assert [g.tokens for g in again] == [g.tokens for g in got]
 
 
+def test_the_order_of_the_requests_changes_no_tokens(models):
+    """A request's tokens depend neither on its place in the batch nor on its neighbours' lengths
+    (float32, greedy): reversed, and with a long stranger between them."""
+    cfg, d, model, w = models["b"]
+    prompts = [random_tokens(40 + i, n, 384) for i, n in enumerate([17, 1, 40, 70, 3])]
+    base = bn.generate(model, prompts, max_new_tokens=10)
+    rev = bn.generate(model, prompts[::-1], max_new_tokens=10)
+    assert [g.tokens for g in rev][::-1] == [g.tokens for g in base]
+    mixed = [prompts[2], random_tokens(99, 130, 384), prompts[0], prompts[4]]
+    got = bn.generate(model, mixed, max_new_tokens=10)
+    assert got[0].tokens == base[2].tokens and got[2].tokens == base[0].tokens and got[3].tokens == base[4].tokens
+
+
 def test_stop_ids_and_unequal_lengths(models):
     cfg, d, model, w = models["b"]
     prompts = [random_tokens(10 + i, n, 384) for i, n in enumerate([17, 1, 40])]
