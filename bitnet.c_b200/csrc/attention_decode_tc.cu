@@ -84,6 +84,9 @@ struct DtArgs {
   float* part_ml;  // [n_seqs][n_heads][splits][2]: maximum (in the scaled log2 domain) and sum
   int pages_per_block;
   int cluster;     // 1: the splits of a sequence are one thread-block cluster and merge through distributed shared memory
+  const int* items;  // null, or for each blockIdx.x what it works on: sequence | split << 16 | splits << 24, or -1 for
+                     // nothing.  The grid then has no z; clusters of `group` blocks run along x, and a cluster
+                     // holds either the splits of one sequence or `group` sequences that are not split.
   int* tickets;    // [n_seqs][gridDim.y], zero before and after
   __nv_bfloat16* out;
   int out_stride;
@@ -94,7 +97,7 @@ __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DtArgs a) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned long long* tr = (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? a.trace + 16 * blockIdx.z : nullptr;
+  unsigned long long* tr = (a.trace && a.items == nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? a.trace + 16 * blockIdx.z : nullptr;
   if (tr) tr[0] = global_timer();
   constexpr int CHUNKS = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, BOXES = HD / 64;
   constexpr int PAGE_BYTES = BN_PAGE * HD * 2;       // one page of keys (or values) of one head
@@ -115,7 +118,17 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const unsigned s_q = smem_u32(q_tile), s_st = smem_u32(stages), full0 = smem_u32(bars);
   __shared__ int s_last;
 
-  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // which sequence, which of its splits, of how many
+  int b = blockIdx.x, zi = blockIdx.z, nz = gridDim.z;
+  if (a.items != nullptr) {
+    const int item = a.items[blockIdx.x];
+    if (item < 0) {  // padding: the whole cluster is, or its other blocks work alone
+      pdl_wait();
+      return;
+    }
+    b = item & 0xFFFF; zi = (item >> 16) & 0xFF; nz = (item >> 24) & 0x7F;
+  }
   const int g4 = lane >> 2, t4 = lane & 3;
   const int head_dim = a.head_dim, n_kv_heads = a.n_kv_heads, n_heads = a.n_heads;
   const int group = n_heads / n_kv_heads;
@@ -131,8 +144,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   // sequence, whatever the bound it was sized for); a sequence too short for a split to pay is the
   // first block's alone.
   const int vis = p_hi - p_lo + 1;
-  const int ppb = vis < DT_SPLIT_MIN_PAGES ? vis : min(a.pages_per_block, (vis + (int)gridDim.z - 1) / (int)gridDim.z);
-  const int my_lo = p_lo + (int)blockIdx.z * ppb;
+  const int ppb = vis < DT_SPLIT_MIN_PAGES ? vis : min(a.pages_per_block, (vis + nz - 1) / nz);
+  const int my_lo = p_lo + zi * ppb;
   const int my_hi = min(p_hi, my_lo + ppb - 1);
   const int z_lo = 0, z_hi = (vis - 1) / ppb;  // splits with a visible page
   const bool alone = (z_lo == z_hi);
@@ -146,7 +159,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     return;
   }
   const int n_pages = my_hi - my_lo + 1;
-  const int n_splits = gridDim.z;
+  const int n_splits = nz;
   const int* pt = a.page_table + (size_t)a.slots[b] * a.pt_stride;
   const bool has_new = (p_hi >= my_lo && p_hi <= my_hi);  // the new token's page is in this run
   const int new_row = pos - p_hi * BN_PAGE;
@@ -447,7 +460,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (alone)  // the only split of this sequence: normalise and store
       a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(acc / ml_fin[g * 2 + 1]);
     else if (clustered) o_fin[g * HD + d] = acc;
-    else a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + blockIdx.z) * head_dim + d] = acc;
+    else a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + zi) * head_dim + d] = acc;
   }
   if (alone) {
     if (tr) tr[8] = global_timer();
@@ -459,7 +472,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     dt_cluster_sync();
     if (tr) tr[8] = global_timer();
     const unsigned a_ml = smem_u32(ml_fin), a_o = smem_u32(o_fin);
-    const int n_act = z_hi - z_lo + 1, mine = (int)blockIdx.z - z_lo;
+    const int n_act = z_hi - z_lo + 1, mine = zi - z_lo;
     const int total = G * head_dim, per = (total + n_act - 1) / n_act;
     for (int i = mine * per + tid; i < min(total, (mine + 1) * per); i += DT_THREADS) {
       int g = i / head_dim, d = i - g * head_dim;
@@ -489,7 +502,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     return;
   }
   if (tid < G) {
-    size_t oo = (((size_t)b * n_heads + h0 + tid) * n_splits + blockIdx.z) * 2;
+    size_t oo = (((size_t)b * n_heads + h0 + tid) * n_splits + zi) * 2;
     a.part_ml[oo] = ml_fin[tid * 2];
     a.part_ml[oo + 1] = ml_fin[tid * 2 + 1];
   }
@@ -555,7 +568,7 @@ static constexpr size_t dt_smem_bytes() {
          (4 * DT_ROWS * 2 + DT_ROWS * 2) * sizeof(float) + DT_STAGES * 8 + HD * sizeof(float) + 4 * DT_ROWS * sizeof(float);
 }
 template <int HD, int DT_STAGES>
-static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
+static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, dim3 cluster, cudaStream_t stream) {
   size_t smem = dt_smem_bytes<HD, DT_STAGES>();
   static bool configured = false;
   if (!configured) {
@@ -566,7 +579,7 @@ static int launch_dt2(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs
   }
   if (a.cluster) {
     cudaError_t e = bn_launch_cluster(attention_decode_tc_kernel<HD, DT_STAGES>, grid, dim3(DT_THREADS), smem, stream,
-                                      dim3(1, 1, grid.z), mk, mv, a);
+                                      cluster, mk, mv, a);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     return BN_OK;
   }
@@ -596,13 +609,13 @@ static long long dt_slots() {
 // wins although each block runs about an eighth slower (40 heads of 128, 2,000 positions, 8
 // sequences = 320 blocks: 77 us with three stages in two waves, 53 us with two stages in one).
 template <int HD>
-static int launch_dt(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, cudaStream_t stream) {
-  if (a.pages_per_block <= 2) return launch_dt2<HD, 2>(mk, mv, a, grid, stream);
+static int launch_dt(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs& a, dim3 grid, dim3 cluster, cudaStream_t stream) {
+  if (a.pages_per_block <= 2) return launch_dt2<HD, 2>(mk, mv, a, grid, cluster, stream);
   const long long blocks = (long long)grid.x * grid.y * grid.z;
   const long long s3 = dt_slots<HD, 3>(), s2 = dt_slots<HD, 2>();
   const long long w3 = (blocks + s3 - 1) / s3, w2 = (blocks + s2 - 1) / s2;
-  if (w2 * 115 < w3 * 100) return launch_dt2<HD, 2>(mk, mv, a, grid, stream);
-  return launch_dt2<HD, 3>(mk, mv, a, grid, stream);
+  if (w2 * 115 < w3 * 100) return launch_dt2<HD, 2>(mk, mv, a, grid, cluster, stream);
+  return launch_dt2<HD, 3>(mk, mv, a, grid, cluster, stream);
 }
 
 // qkv: [n_seqs, q_stride] bfloat16 rows with the raw query heads first, the key heads at element
@@ -615,13 +628,25 @@ static int launch_dt(const CUtensorMap& mk, const CUtensorMap& mv, const DtArgs&
 // The caches are [n_cache_pages, n_kv_heads, 64, head_dim], contiguous and 16-byte aligned.  status:
 // one int on the device, left as it is unless a page load never completed (then 4, and the output
 // of that launch is not valid).
-extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, int v_off, void* out, int out_stride,
-                                      int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
-                                      int rotary_dims, float theta_scale, const int* tok_pos, const int* slots,
-                                      const int* page_table, int pt_stride, void* k_cache, void* v_cache,
-                                      int n_cache_pages, int* status, float* part_o, float* part_ml, int n_splits, int pages_per_block, int* tickets,
-                                      int n_tickets, cudaStream_t stream) {
+//
+// With items (n_items ints on the device, a multiple of group; group 1 to 8): block x of the grid
+// works on what items[x] names, sequence | split << 16 | splits << 24, or on nothing (-1).  Clusters
+// of `group` blocks run along x; a cluster must hold either the `group` splits of one sequence, in
+// order, or sequences that are not split (splits = 1) and padding.  n_splits and pages_per_block
+// are not used then.  This is how a batch of unequal lengths gets more blocks for its long
+// sequences than for its short ones, and its long ones started first.
+static int dt_run(const void* qkv, int q_stride, int k_off, int v_off, void* out, int out_stride,
+                  int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                  int rotary_dims, float theta_scale, const int* tok_pos, const int* slots,
+                  const int* page_table, int pt_stride, void* k_cache, void* v_cache,
+                  int n_cache_pages, int* status, float* part_o, float* part_ml, int n_splits, int pages_per_block, int* tickets,
+                  int n_tickets, const int* items, int n_items, int item_group, cudaStream_t stream) {
   if (n_seqs <= 0) return BN_OK;
+  if (items != nullptr) {
+    if (n_items <= 0 || item_group < 1 || item_group > 8 || n_items % item_group || n_seqs > 65535) return BN_ERR_BAD_ARG;
+    n_splits = item_group;
+    pages_per_block = 1 << 20;
+  }
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || n_splits <= 0 ||
       pages_per_block <= 0 || window < 0 || !part_o || !part_ml || !tickets || !status || n_cache_pages <= 0 ||
       (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) || rotary_dims < 0 ||
@@ -643,12 +668,39 @@ extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, 
   if (g_dt_trace && g_dt_trace_n < g_dt_trace_cap && n_splits <= 8) a.trace = g_dt_trace + (size_t)8 * 16 * (g_dt_trace_n++);
   a.cluster = (n_splits > 1 && n_splits <= 8) ? 1 : 0;  // few splits: one cluster per (sequence, head group)
   a.pages_per_block = pages_per_block; a.tickets = tickets; a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
-  dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits);
+  a.items = items;
+  dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits), cluster(1, 1, n_splits);
+  if (items != nullptr) {
+    a.trace = nullptr;
+    grid = dim3(n_items, n_kv_heads * gblocks, 1);
+    cluster = dim3(item_group, 1, 1);
+  }
   CUtensorMap mk, mv;
   if (!tma_map_bf16_pages(&mk, k_cache, n_cache_pages, (unsigned long long)n_kv_heads * BN_PAGE, head_dim, BN_PAGE) ||
       !tma_map_bf16_pages(&mv, v_cache, n_cache_pages, (unsigned long long)n_kv_heads * BN_PAGE, head_dim, BN_PAGE))
     return BN_ERR_BAD_ARG;
-  if (head_dim <= 64) return launch_dt<64>(mk, mv, a, grid, stream);
-  if (head_dim <= 128) return launch_dt<128>(mk, mv, a, grid, stream);
-  return launch_dt<256>(mk, mv, a, grid, stream);
+  if (head_dim <= 64) return launch_dt<64>(mk, mv, a, grid, cluster, stream);
+  if (head_dim <= 128) return launch_dt<128>(mk, mv, a, grid, cluster, stream);
+  return launch_dt<256>(mk, mv, a, grid, cluster, stream);
+}
+extern "C" int bn_attention_decode_tc(const void* qkv, int q_stride, int k_off, int v_off, void* out, int out_stride,
+                                      int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                      int rotary_dims, float theta_scale, const int* tok_pos, const int* slots,
+                                      const int* page_table, int pt_stride, void* k_cache, void* v_cache,
+                                      int n_cache_pages, int* status, float* part_o, float* part_ml, int n_splits, int pages_per_block, int* tickets,
+                                      int n_tickets, cudaStream_t stream) {
+  return dt_run(qkv, q_stride, k_off, v_off, out, out_stride, n_seqs, n_heads, n_kv_heads, head_dim, scale, window, rotary_dims,
+                theta_scale, tok_pos, slots, page_table, pt_stride, k_cache, v_cache, n_cache_pages, status, part_o, part_ml,
+                n_splits, pages_per_block, tickets, n_tickets, nullptr, 0, 0, stream);
+}
+extern "C" int bn_attention_decode_tc_items(const void* qkv, int q_stride, int k_off, int v_off, void* out, int out_stride,
+                                            int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                            int rotary_dims, float theta_scale, const int* tok_pos, const int* slots,
+                                            const int* page_table, int pt_stride, void* k_cache, void* v_cache,
+                                            int n_cache_pages, int* status, float* part_o, float* part_ml, int* tickets,
+                                            int n_tickets, const int* items, int n_items, int item_group, cudaStream_t stream) {
+  if (!items) return BN_ERR_BAD_ARG;
+  return dt_run(qkv, q_stride, k_off, v_off, out, out_stride, n_seqs, n_heads, n_kv_heads, head_dim, scale, window, rotary_dims,
+                theta_scale, tok_pos, slots, page_table, pt_stride, k_cache, v_cache, n_cache_pages, status, part_o, part_ml,
+                1, 1, tickets, n_tickets, items, n_items, item_group, stream);
 }

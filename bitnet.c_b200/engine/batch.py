@@ -48,6 +48,10 @@ class StepContext:
     tile_row0: Optional[torch.Tensor] = None  # [n_tiles] int32: its first row within the sequence's new tokens
     wide_tile_seq: Optional[torch.Tensor] = None  # the same for blocks of 128 new tokens
     wide_tile_row0: Optional[torch.Tensor] = None
+    # a decode step of unequal lengths: which block of a kernel over the cache works on what
+    # (``ops.decode_items``), in groups of ``decode_item_group``; None: every sequence alike
+    decode_items: Optional[torch.Tensor] = None
+    decode_item_group: int = 0
     host_new: List[int] = field(default_factory=list)  # the same facts on the host, for parts that
     host_pos0: List[int] = field(default_factory=list)  # loop over sequences there
     host_slots: List[int] = field(default_factory=list)

@@ -42,6 +42,14 @@ class DecodeRunner:
                                slots=self.slots, seq_start=ar, seq_pos0=self.tok_pos, rows=ar[:B], max_new=1,
                                max_len=cache.max_positions, decode=True, rows_all=True)
         self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
+        # A batch of unequal lengths gives its long sequences more blocks of the kernels over the
+        # cache than its short ones and starts them first (``ops.decode_items``).  Whether, and in
+        # groups of how many, is decided when a bucket's step is recorded (the grid's shape is
+        # part of the recording); the list itself is data and follows the lengths.
+        self.blocks_per_seq = model.decode_blocks_per_sequence()
+        self.items = torch.full((4 * B,), -1, dtype=torch.int32, device=dev)
+        self.item_group = {}  # length bucket -> group size of its work list, 0: none
+        self.host_items: Optional[List[int]] = None
         self.graphs = {}  # length bucket -> recorded graph
         self.pool = pool
         self.warmed = False
@@ -75,6 +83,7 @@ class DecodeRunner:
         while bucket < max(positions) + 1:
             bucket *= 2
         self.ctx.max_len = min(bucket, self.cache.max_positions)
+        self._work_list(positions)
         if not self.warmed:
             # the first step runs directly: kernels and libraries finish their lazy set-up,
             # which must not happen under capture
@@ -96,6 +105,31 @@ class DecodeRunner:
         self.host_pos = [p + 1 for p in positions]
         self.expect_tokens = None  # known once the caller has read ``sampled``
         return self.sampled
+
+    def _work_list(self, positions: Sequence[int]) -> None:
+        """Bring the work list of this step's bucket up to date (the grid's shape was fixed when the
+        bucket was first met)."""
+        from ..cache.pages import PAGE
+        from ..csrc import ops
+        bucket, B = self.ctx.max_len, self.batch
+        pages = [p // PAGE + 1 for p in positions]
+        group = self.item_group.get(bucket)
+        if group is None:
+            plan = ops.decode_items(pages, self.blocks_per_seq) if self.blocks_per_seq and self.warmed else None
+            if not self.warmed:
+                group = 0  # the step that runs unrecorded decides nothing
+            else:
+                group = self.item_group[bucket] = plan[0] if plan else 0
+        if not group:
+            self.ctx.decode_items, self.ctx.decode_item_group = None, 0
+            return
+        items = ops.decode_items(pages, self.blocks_per_seq, group=group, capacity=group * B)[1]
+        if items != self.host_items:
+            host = torch.from_numpy(np.asarray(items, dtype=np.int32)).pin_memory()
+            self.items[:group * B].copy_(host, non_blocking=True)
+            self.host_items = items
+            self.h2d_bytes += host.numel() * 4
+        self.ctx.decode_items, self.ctx.decode_item_group = self.items[:group * B], group
 
     def note_sampled(self, tokens: Sequence[int]) -> None:
         """The ids the last step sampled, as read by the host: if the next step feeds exactly these,

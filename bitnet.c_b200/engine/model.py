@@ -78,6 +78,11 @@ class Model:
             return bool(getattr(part, "graph_safe", False)) and all(ok(c) for c in part.children().values())
         return all(ok(b) for b in self.blocks) and ok(self.final_norm)
 
+    def decode_blocks_per_sequence(self) -> int:
+        """The most thread blocks any part launches per sequence in a decode step (0: no part takes
+        a work list); what ``DecodeRunner`` sizes a batch's work list by."""
+        return max((b.decode_blocks_per_sequence() for b in self.blocks), default=0)
+
     def kernel_families(self) -> List[str]:
         fams = ["embed", "linear"]
         for blk in self.blocks:

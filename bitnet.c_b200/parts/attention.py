@@ -51,6 +51,12 @@ class Attention(Mixer):
         s = self.spec
         return KvRequest(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
 
+    def decode_blocks_per_sequence(self) -> int:
+        s = self.spec
+        if self.build.dtype != torch.bfloat16 or getattr(self.position, "rotary_params", None) is None:
+            return 0  # the one-launch decode kernel is not used
+        return s.n_kv_heads * ((s.n_heads // s.n_kv_heads + 15) // 16)
+
     def forward(self, h, ctx, kv, state, sink=None):
         s = self.spec
         n = h.shape[0]
@@ -63,7 +69,8 @@ class Attention(Mixer):
             rotary_dims, theta_scale = fusable()
             ops.attention_decode_fused(qkv, s.q_dim, s.q_dim + s.kv_dim, out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                        s.softmax_scale, s.window, rotary_dims, theta_scale, ctx.tok_pos, ctx.slots,
-                                       kv.page_table, kv.k, kv.v, ctx.max_len)
+                                       kv.page_table, kv.k, kv.v, ctx.max_len, items=ctx.decode_items,
+                                       item_group=ctx.decode_item_group)
             return ops.linear(out, self.w_o, out_dtype=self.build.dtype, sink=sink)
         if kv.owner:
             qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)

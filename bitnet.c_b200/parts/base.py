@@ -90,6 +90,12 @@ class Part:
     def children(self) -> Dict[str, "Part"]:
         return {}
 
+    def decode_blocks_per_sequence(self) -> int:
+        """How many thread blocks a decode step's kernel over the cache launches per sequence (before
+        any split), or 0 if this part has no such kernel or takes no work list (``StepContext.
+        decode_items``).  The engine sizes a batch's work list by the largest answer."""
+        return max((c.decode_blocks_per_sequence() for c in self.children().values()), default=0)
+
     def all_kernels(self) -> Tuple[str, ...]:
         seen = list(self.kernels)
         for c in self.children().values():

@@ -503,13 +503,15 @@ def _last_row_attention(q, k, v, scale, window):
     (4, 2, 64, 40, [70, 200], 0),  # rotary dimensions that are no multiple of 16
     (8, 1, 128, 128, [20000], 0),  # one long sequence: more blocks than a cluster holds, chosen by the policy
 ])
-@pytest.mark.parametrize("splits", [0, 3, 12])
+@pytest.mark.parametrize("splits", [0, 3, 12, "list1", "list2", "list4"])
 def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd, lens, window):
     """The one-launch decode attention against plain rotary + attention: the new key and value must land
     in the cache (rotated / as they are) and the result must see them.  ``splits``: blocks per
     sequence, 0 = chosen from the batch; up to eight merge inside a thread-block cluster, more
-    through global memory and a ticket."""
-    monkeypatch.setattr(ops, "_FORCE_SPLITS", splits)
+    through global memory and a ticket.  "listN": a work list in groups of N (``ops.decode_items``):
+    the sequences with more than 1/N of the longest one's pages get N blocks, the others one."""
+    work_list = int(splits[4:]) if isinstance(splits, str) else 0
+    monkeypatch.setattr(ops, "_FORCE_SPLITS", 0 if work_list else splits)
     g = torch.Generator().manual_seed(23)
     theta = 10000.0
     n_seq = len(lens)
@@ -544,11 +546,16 @@ def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd,
         v[page, :, row + 1:] = float("inf")
     k_before, v_before = k.clone(), v.clone()
     out = torch.empty(n_seq, H * hd, dtype=torch.bfloat16, device=cuda_device)
+    extra = {}
+    if work_list:
+        group, items = ops.decode_items([p // 64 + 1 for p in pos], KV * ((H // KV + 15) // 16), group=work_list)
+        assert group == work_list and len(items) % group == 0 and sorted(i & 0xFFFF for i in items if i >= 0 and not (i >> 16) & 0xFF) == list(range(n_seq))
+        extra = {"items": torch.tensor(items, dtype=torch.int32, device=cuda_device), "item_group": group}
     ops.attention_decode_fused(raw.reshape(n_seq, -1).contiguous().to(cuda_device), H * hd, (H + KV) * hd, out, n_seq,
                                H, KV, hd, hd ** -0.5, window, rd, scale,
                                torch.tensor(pos, dtype=torch.int32, device=cuda_device),
                                torch.tensor(slots, dtype=torch.int32, device=cuda_device), perm.to(cuda_device), k, v,
-                               max(lens))
+                               max(lens), **extra)
     got = out.double().cpu().numpy().reshape(n_seq, H, hd)
     touched = torch.zeros_like(k, dtype=torch.bool)
     for s, L in enumerate(lens):
