@@ -366,17 +366,24 @@ def decode_items(seq_pages, blocks_per_seq: int, group: Optional[int] = None, ca
         limit = -(-longest // s)
         return [b for b in range(n) if seq_pages[b] > limit]
 
+    def fits(s: int) -> bool:
+        k = len(long_ones(s))
+        return (s * k + n - k) * blocks_per_seq <= DECODE_ITEM_BLOCKS
+
+    uneven = longest >= 12 and longest * n >= 1.5 * total
     if group is None and _FORCE_ITEM_GROUP:
         group = _FORCE_ITEM_GROUP
-    if group is None:
-        if n * blocks_per_seq <= 128 or longest < 12 or longest * n < 1.5 * total:
+        chosen = long_ones(group) if group > 1 else []
+    elif group is None:
+        sizes = [s for s in (2, 3, 4) if fits(s)]
+        if n * blocks_per_seq <= 128 or not uneven or not sizes:
             return None
-        fits = [s for s in (2, 3, 4)
-                if (s * len(long_ones(s)) + n - len(long_ones(s))) * blocks_per_seq <= DECODE_ITEM_BLOCKS]
-        if not fits:
-            return None
-        group = max(fits)
-    chosen = long_ones(group) if group > 1 else []
+        group = max(sizes)
+        chosen = long_ones(group)
+    else:
+        # the grid's shape is given; if the batch has meanwhile become even, or splitting its long
+        # sequences would now take too many blocks, nothing is split and the list only orders
+        chosen = long_ones(group) if group > 1 and (_FORCE_ITEM_GROUP or (uneven and fits(group))) else []
     is_long = set(chosen)
     items = []
     for b in sorted(chosen, key=lambda b: -seq_pages[b]):
