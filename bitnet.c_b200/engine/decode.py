@@ -49,7 +49,9 @@ class DecodeRunner:
         self.blocks_per_seq = model.decode_blocks_per_sequence()
         self.items = torch.full((4 * B,), -1, dtype=torch.int32, device=dev)
         self.item_group = {}  # length bucket -> group size of its work list, 0: none
-        self.host_items: Optional[List[int]] = None
+        self.host_items: Optional[List[int]] = None  # what the device buffer holds
+        self.items_for = None  # (bucket, page counts) that ``next_items`` was made for
+        self.next_items: List[int] = []
         self.graphs = {}  # length bucket -> recorded graph
         self.pool = pool
         self.warmed = False
@@ -123,7 +125,10 @@ class DecodeRunner:
         if not group:
             self.ctx.decode_items, self.ctx.decode_item_group = None, 0
             return
-        items = ops.decode_items(pages, self.blocks_per_seq, group=group, capacity=group * B)[1]
+        if (bucket, pages) != self.items_for:  # the list depends on the page counts only
+            self.items_for = (bucket, pages)
+            self.next_items = ops.decode_items(pages, self.blocks_per_seq, group=group, capacity=group * B)[1]
+        items = self.next_items
         if items != self.host_items:
             host = torch.from_numpy(np.asarray(items, dtype=np.int32)).pin_memory()
             self.items[:group * B].copy_(host, non_blocking=True)
