@@ -122,6 +122,8 @@ class DecodeRunner:
                 group = 0  # the step that runs unrecorded decides nothing
             else:
                 group = self.item_group[bucket] = plan[0] if plan else 0
+                if group * B > self.items.numel():
+                    raise ValueError(f"a work list in groups of {group} does not fit the buffer of {self.items.numel()} entries")
         if not group:
             self.ctx.decode_items, self.ctx.decode_item_group = None, 0
             return
