@@ -103,13 +103,132 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def reference_arm():
-    """The reference is a C11 project with a Makefile and no Python packaging; an offline
-    ``pip install --target baseline/_ref`` of its source tree therefore installs nothing."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "artalis-io/bitnet.c is a C/Makefile project without setup.py or pyproject.toml: "
-                                     "the offline pip install into baseline/_ref fails, and it has no safetensors or "
-                                     "random-weights loader to run this model with"}))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_SOURCE = "/root/reference"
+REF_PREFILL_BUDGET_S = 200.0  # the 2,048-token prompt is left out if the 512-token one says it would take longer
+REF_CUDA_NOTE = ("its CUDA backend cannot be built: nvcc 12.9 stops on src/gpu_cuda.cu with 119 errors in the source "
+                 "itself (BnCudaBlockQ8_1 used at line 104 before its definition at line 179, 115 calls that pass "
+                 "'&ctx->runtime_policy' where a 'const BnBackendRuntimePolicy *' is expected, an undefined identifier "
+                 "'gpu' at line 18869, a call with too few arguments at line 15883)")
+
+
+def _cpu_stamp():
+    """What the reference's objects were built for: its Makefile compiles with -march=native."""
+    flags = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    flags = line
+                    break
+    except OSError:
+        pass
+    import hashlib
+    return hashlib.sha256(flags.encode()).hexdigest()[:16]
+
+
+def build_reference():
+    """An unmodified copy of the reference under baseline/_ref, built with its own Makefile (CPU
+    engine: ``make bitnet``), and this repository's harness linked against its objects.  Returns
+    the harness's path; raises RuntimeError with the reason if something is missing or fails."""
+    import glob
+    import shutil
+    if not os.path.isfile(os.path.join(REF_DIR, "Makefile")):
+        if not os.path.isfile(os.path.join(REF_SOURCE, "Makefile")):
+            raise RuntimeError("no copy of artalis-io/bitnet.c under baseline/_ref and none to copy from")
+        shutil.copytree(REF_SOURCE, REF_DIR, dirs_exist_ok=True)
+    stamp_path = os.path.join(REF_DIR, ".built_for_cpu")
+    stamp = _cpu_stamp()
+    built = os.path.isfile(stamp_path) and open(stamp_path).read().strip() == stamp
+    exe = os.path.join(ROOT, "baseline", "_ref", "ref_harness")
+    env = dict(os.environ, NVCC="/usr/local/cuda/bin/nvcc")
+    if not built:
+        subprocess.run(["make", "clean"], cwd=REF_DIR, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        r = subprocess.run(["make", "bitnet", f"-j{max(2, os.cpu_count() or 2)}"], cwd=REF_DIR, env=env,
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("the reference's 'make bitnet' failed: " + r.stdout.strip().splitlines()[-1][:200])
+    harness_src = os.path.join(ROOT, "baseline", "ref_harness.c")
+    if not built or not os.path.isfile(exe) or os.path.getmtime(exe) < os.path.getmtime(harness_src):
+        objs = [o for o in glob.glob(os.path.join(REF_DIR, "src", "**", "*.o"), recursive=True)
+                if not o.endswith(os.sep + "main.o")]
+        r = subprocess.run([os.environ.get("CC", "gcc"), "-O2", "-std=c11", "-D_GNU_SOURCE", "-I", os.path.join(REF_DIR, "include"),
+                            "-I", os.path.join(REF_DIR, "src"), harness_src, *objs, "-lm", "-lpthread", "-o", exe],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("linking the harness against the reference's objects failed: " + r.stdout.strip()[-300:])
+        with open(stamp_path, "w") as f:
+            f.write(stamp + "\n")
+    return exe
+
+
+def reference_arm(args):
+    """The same metric from artalis-io/bitnet.c itself, unmodified, through its public calls
+    (bn_session_create, bn_prefill, bn_prompt_cache_*, bn_transformer_forward, bn_sampler_sample),
+    on the same sizes with random BF16 weights.  It runs on the host's cores: the reference is a
+    CPU-first engine and the CUDA backend of this checkout does not compile."""
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    try:
+        exe = build_reference()
+    except (RuntimeError, OSError) as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)[:400]}))
+        return 0
+    cfg = dict(LLAMA_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    warmup = max(3, args.warmup)
+    B = args.batch
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cmd = [exe] + [str(v) for v in (
+        cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"], cfg["num_attention_heads"],
+        cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"], cfg["max_position_embeddings"],
+        cfg["rope_theta"], cfg["rms_norm_eps"], B, PROMPT_LEN, args.steps, warmup,
+        0 if args.skip_points else PREFILL_TOKENS, threads, REF_PREFILL_BUDGET_S * 1e3)]
+    t0 = time.perf_counter()
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    if r.returncode != 0:
+        print(json.dumps({"impl": "reference", "unavailable": f"the harness exited with {r.returncode}: "
+                          + (r.stderr.strip().splitlines() or ["no message"])[-1][:300]}))
+        return 0
+    res = json.loads(r.stdout.strip().splitlines()[-1])
+    steps_ms = sorted(res["step_ms"])
+    total_ms = sum(steps_ms)
+    value = B * len(steps_ms) / (total_ms / 1e3)
+    out = {
+        "metric": f"decode tokens/s at batch {B} (Llama-3.1-8B sizes, bf16)", "value": round(value, 3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(total_ms / len(steps_ms), 3),
+        "ms_per_step_median": round(steps_ms[len(steps_ms) // 2], 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 weights, float32 activations and cache",
+        "data": "synthetic", "impl": "reference",
+        "config": {"model": "llama-3.1-8b-sizes-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": B, "seq_len": cfg["max_position_embeddings"], "prompt_len": PROMPT_LEN,
+                   "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied": False,
+                   "parallelism": "single-gpu", "l2": "inputs larger than any cache (15 GB of weights per forward)",
+                   "peaks": "none"},
+        "device": f"host CPU, {res['threads']} threads: the reference's CPU engine; " + REF_CUDA_NOTE,
+        "batching": "one BnSession per request, each stepped once per decode step; the prompt is run once by "
+                    "bn_prefill and restored into the other sessions by the reference's prompt cache "
+                    "(all but the last token, which differs per request)",
+        "e2e": {"value": round(value, 3), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "host engine: token ids never leave the host; the timed loop includes the greedy choice"},
+        "gpu_launches": 0,
+        "clocks": {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no GPU work in this arm"},
+        "prompt_prefill": {"tokens": PROMPT_LEN, "ms": round(res["prompt_ms"], 1),
+                           "value": round(PROMPT_LEN / (res["prompt_ms"] / 1e3), 2)},
+        "wall_s": round(time.perf_counter() - t0, 1),
+    }
+    if res.get("prefill_ms", -1) > 0:
+        out["prefill"] = {"value": round(res["prefill_tokens"] / (res["prefill_ms"] / 1e3), 2), "tokens": res["prefill_tokens"],
+                          "ms": round(res["prefill_ms"], 1)}
+    if res.get("b1_step_ms"):
+        b1 = sorted(res["b1_step_ms"])
+        out["points"] = {"decode_b1": round(1e3 * len(b1) / sum(b1), 3)}
+    print(json.dumps(out))
     return 0
 
 
@@ -273,7 +392,7 @@ def main():
     ap.add_argument("--workload", choices=["1b", "13b"], help="run the generation workload of another size set instead")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
