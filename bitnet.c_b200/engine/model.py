@@ -126,32 +126,17 @@ class Model:
     @classmethod
     def from_random(cls, config: Dict[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0",
                     matrix_std: float = 0.02, norm_std: float = 0.1) -> "Model":
-        """A model of ``config`` (config.json keys) with random weights made on the device: matrices
-        N(0, matrix_std), norm gains 1 + N(0, norm_std).  For sizes whose weights would be too
-        large to write to a folder first; the values are those of torch's CUDA generator, not of
-        ``write_random_model``."""
+        """A model of ``config`` (config.json keys) with the weights of ``write_random_model(folder,
+        config, seed, dtype)`` drawn on the device instead of written to a folder and loaded: the
+        same seeded generator (``weights.random_init``), for sizes whose file would be large."""
+        from ..weights import random_parameters
         arch = architecture_of(config)
         cfg = arch.read_config(config)
         model = cls(arch.to_spec(cfg), dtype=dtype, device=device, arch=arch, config=cfg)
         require_cuda(model.device)
         kernel_build.ensure_built(model.kernel_families())
-        g = torch.Generator(device=model.device).manual_seed(seed)
-        tensors: Dict[str, torch.Tensor] = {}
-        for path, p in model.parameter_table().items():
-            if p.integer:
-                tensors[path] = torch.zeros(p.shape, dtype=torch.int32, device=model.device)
-                continue
-            mean, std = (1.0, norm_std) if p.init == "ones" else (0.0, matrix_std if p.init == "normal" else 0.0)
-            t = torch.empty(p.shape, dtype=model.dtype, device=model.device)
-            flat = t.view(-1)
-            step = 1 << 26
-            for a in range(0, flat.numel(), step):
-                n = min(step, flat.numel() - a)
-                if std:
-                    flat[a:a + n] = torch.randn(n, generator=g, device=model.device, dtype=torch.float32) * std + mean
-                else:
-                    flat[a:a + n] = mean
-            tensors[path] = t
+        tensors = {path: t for path, _name, t in random_parameters(model.spec, arch.tensor_name, seed, model.dtype,
+                                                                   matrix_std, norm_std, model.device)}
         return model.bind(tensors)
 
     # ---- cache ----------------------------------------------------------------------------

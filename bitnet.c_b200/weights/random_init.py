@@ -8,6 +8,7 @@ reference has no such mode (its models are GGUF files only, src/main.c:110-168).
 from __future__ import annotations
 
 import json
+import math
 import os
 from typing import Any, Dict
 
@@ -57,10 +58,49 @@ def standard_normal(seed: int, name: str, count: int, start: int = 0) -> np.ndar
     return z.astype(np.float32)
 
 
-def random_tensor(seed: int, name: str, shape, mean: float, std: float, dtype: torch.dtype) -> torch.Tensor:
+def _signed(x: int) -> int:
+    """The 64-bit pattern ``x`` as a signed integer (torch has no unsigned 64-bit arithmetic;
+    signed products and sums wrap to the same bits)."""
+    x &= _MASK64
+    return x - (1 << 64) if x >> 63 else x
+
+
+def _lsr(x: torch.Tensor, n: int) -> torch.Tensor:
+    """Logical right shift of int64 bit patterns."""
+    return (x >> n) & ((1 << (64 - n)) - 1)
+
+
+def standard_normal_on(device, seed: int, name: str, count: int, start: int = 0) -> torch.Tensor:
+    """``standard_normal`` restated in torch, for tensors too large to draw on the host: the same
+    function of ``(seed, name, index)``, evaluated on ``device``.  The integer part is bit-exact;
+    the float64 logarithm and cosine are the device's, so a value may differ from the host's in
+    its last float32 bit now and then."""
+    key = _signed(stream_key(seed, name))
+    idx = torch.arange(start, start + count, dtype=torch.int64, device=device)
+    x = idx * _signed(int(_GOLDEN)) + key
+    x = (x ^ _lsr(x, 30)) * _signed(int(_M1))
+    x = (x ^ _lsr(x, 27)) * _signed(int(_M2))
+    h = x ^ _lsr(x, 31)
+    u1 = (_lsr(h, 40).to(torch.float64) + 1.0) * (1.0 / 16777216.0)
+    u2 = (_lsr(h, 16) & 0xFFFFFF).to(torch.float64) * (1.0 / 16777216.0)
+    z = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(2.0 * math.pi * u2)
+    return z.to(torch.float32)
+
+
+def random_tensor(seed: int, name: str, shape, mean: float, std: float, dtype: torch.dtype, device=None) -> torch.Tensor:
+    """Tensor ``name`` under ``seed``: mean + std * standard normal, computed in float32 and then
+    rounded to ``dtype``.  Without ``device`` the values are drawn on the host with NumPy; with one
+    they are drawn there (``standard_normal_on``) and the tensor stays there."""
     n = int(np.prod(shape)) if len(shape) else 1
     if std == 0.0:
-        return torch.full(tuple(shape), mean, dtype=dtype)
+        return torch.full(tuple(shape), mean, dtype=dtype, device=device)
+    if device is not None:
+        out_t = torch.empty(n, dtype=dtype, device=device)
+        step = 1 << 24
+        for s in range(0, n, step):
+            c = min(step, n - s)
+            out_t[s:s + c] = standard_normal_on(device, seed, name, c, s) * std + mean
+        return out_t.reshape(tuple(shape))
     out = np.empty(n, dtype=np.float32)
     step = 1 << 22
     for s in range(0, n, step):
@@ -69,15 +109,33 @@ def random_tensor(seed: int, name: str, shape, mean: float, std: float, dtype: t
     return torch.from_numpy(out).reshape(tuple(shape)).to(dtype)
 
 
+def random_parameters(spec, tensor_name, seed: int, dtype: torch.dtype, matrix_std: float = 0.02,
+                      norm_std: float = 0.1, device=None):
+    """Yield ``(path, name, tensor)`` for every parameter of a model of ``spec``: matrices and the
+    embedding N(0, matrix_std), norm gains 1 + N(0, norm_std), integer tables zero.  The values
+    depend on the seed and on the tensor's name in the file only."""
+    from ..engine.model import parameter_table
+    for path, p in parameter_table(spec).items():
+        name = tensor_name(path)
+        if p.init == "ones":
+            yield path, name, random_tensor(seed, name, p.shape, 1.0, norm_std, dtype, device)
+        elif p.init == "normal":
+            yield path, name, random_tensor(seed, name, p.shape, 0.0, matrix_std, dtype, device)
+        elif p.init == "zeros":
+            yield path, name, torch.zeros(p.shape, dtype=torch.int32 if p.integer else dtype, device=device)
+        else:
+            raise ValueError(f"parameter '{path}' has unknown init '{p.init}'")
+
+
 def write_random_model(folder: str, config: Dict[str, Any], seed: int, dtype: str = "bfloat16",
-                       matrix_std: float = 0.02, norm_std: float = 0.1) -> str:
+                       matrix_std: float = 0.02, norm_std: float = 0.1, device=None) -> str:
     """Write ``config.json`` and ``model.safetensors`` for ``config`` under ``folder``.
 
     Matrices and the embedding are N(0, matrix_std); norm gains are 1 + N(0, norm_std).
-    ``dtype`` is the storage type of the file: ``bfloat16`` or ``float32``.
+    ``dtype`` is the storage type of the file: ``bfloat16`` or ``float32``.  ``device``: draw the
+    values there instead of on the host (large models; see ``standard_normal_on``).
     """
     from ..config import architecture_of
-    from ..engine.model import parameter_table
     from .safetensors_io import write_safetensors
 
     store = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
@@ -87,16 +145,8 @@ def write_random_model(folder: str, config: Dict[str, Any], seed: int, dtype: st
     os.makedirs(folder, exist_ok=True)
 
     def tensors():
-        for path, p in parameter_table(spec).items():
-            name = arch.tensor_name(path)
-            if p.init == "ones":
-                yield name, random_tensor(seed, name, p.shape, 1.0, norm_std, store)
-            elif p.init == "normal":
-                yield name, random_tensor(seed, name, p.shape, 0.0, matrix_std, store)
-            elif p.init == "zeros":
-                yield name, torch.zeros(p.shape, dtype=torch.int32 if p.integer else store)
-            else:
-                raise ValueError(f"parameter '{path}' has unknown init '{p.init}'")
+        for _path, name, t in random_parameters(spec, arch.tensor_name, seed, store, matrix_std, norm_std, device):
+            yield name, t
 
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors(),
                       metadata={"format": "pt", "seed": str(seed)})

@@ -11,6 +11,7 @@ for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    config.addinivalue_line("markers", "slow: takes tens of seconds (models of real layer sizes)")
 
 
 @pytest.fixture(scope="session")

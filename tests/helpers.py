@@ -23,10 +23,36 @@ def bf16_bound(plain_logits: np.ndarray) -> float:
     return 3.0 * 2.0 ** -8 * max(1.0, float(np.abs(plain_logits).max()))
 
 
-def make_model_dir(tmp_path, cfg: dict, seed: int, storage: str) -> str:
+BF16_GAP_FACTOR = 3.0
+
+
+def sharp_std(cfg: dict) -> float:
+    """The matrix scale of the "sharp" variant of a tiny configuration: 1 / sqrt(width).
+
+    With the stock N(0, 0.02) matrices a tiny model's attention scores are all near zero and
+    attention is a running mean: rotation, softmax scale and the weighting of the keys then move
+    the logits by less than bfloat16 rounding does.  With this scale queries and keys have
+    components of size ~1, the scores of a row spread over 2 to 4 and logits reach 3 to 5, so
+    that a missing rotation, a wrong softmax scale, a dropped key or a wrong key/value head moves
+    them by 0.7 to 6 (tests/test_sharp_models.py asserts it)."""
+    return float(cfg["hidden_size"]) ** -0.5
+
+
+def measured_bf16_bound(cfg: dict, w, tokens, ref: np.ndarray = None) -> float:
+    """Bound for a bfloat16 engine on one request of a sharp model: BF16_GAP_FACTOR times the gap
+    between the plain implementation and the plain implementation with every stored activation
+    rounded to bfloat16 (``round_fn``).  The engine rounds at a few more places than that and adds
+    in other orders; a factor of three of one such set of roundings covers it, and the faults a
+    test is there to catch are another factor of three to thirty beyond."""
+    ref = plain_llama.forward(cfg, w, tokens) if ref is None else ref
+    rounded = plain_llama.forward(cfg, w, tokens, round_fn=plain_llama.to_bf16)
+    return BF16_GAP_FACTOR * float(np.abs(ref - rounded).max())
+
+
+def make_model_dir(tmp_path, cfg: dict, seed: int, storage: str, matrix_std: float = 0.02) -> str:
     from bitnet_c_b200.weights import write_random_model
     d = os.path.join(str(tmp_path), f"model_{seed}_{storage}")
-    write_random_model(d, cfg, seed, dtype=storage)
+    write_random_model(d, cfg, seed, dtype=storage, matrix_std=matrix_std)
     return d
 
 
@@ -85,6 +111,28 @@ def trace_batches(batches: Sequence[Dict[str, Tuple[List[int], int]]]) -> List[S
     return steps
 
 
+def trace_chunks(reqs: Dict[str, List[int]], pieces: Sequence[int] = (1, 7, 64, 130), stagger: int = 1) -> List[Step]:
+    """Every request in pieces of ``pieces`` tokens (taken in turn, each request starting at
+    another place of the list), request i joining at step ``i * stagger``: steps then mix a fresh
+    prompt, a continuation of many tokens behind cached ones and a continuation of one token."""
+    ids = list(reqs)
+    at = {r: 0 for r in ids}
+    steps, n = [], 0
+    while any(at[r] < len(reqs[r]) for r in ids):
+        st = {"step": n, "entries": [], "end": []}
+        for i, r in enumerate(ids):
+            if n < i * stagger or at[r] >= len(reqs[r]):
+                continue
+            toks = reqs[r][at[r]:at[r] + pieces[(n + i) % len(pieces)]]
+            st["entries"].append({"id": r, "tokens": toks, "want": list(range(len(toks)))})
+            at[r] += len(toks)
+            if at[r] >= len(reqs[r]):
+                st["end"].append(r)
+        steps.append(st)
+        n += 1
+    return steps
+
+
 def replay(model, cache, steps: List[Step]) -> Dict[str, Dict[int, np.ndarray]]:
     """Run steps through Model.step in process; returns id -> position -> logits."""
     from bitnet_c_b200.engine import SeqStep
@@ -139,10 +187,11 @@ def plain_logits(model_dir: str, reqs: Dict[str, List[int]]) -> Dict[str, np.nda
 
 
 def compare(got: Dict[str, Dict[int, np.ndarray]], want: Dict[str, np.ndarray], tol_fn, what: str) -> float:
+    """``tol_fn``: a function of a request's plain logits, or a dict from request id to its bound."""
     worst = 0.0
     for rid, per_pos in got.items():
         ref = want[rid]
-        tol = tol_fn(ref)
+        tol = tol_fn[rid] if isinstance(tol_fn, dict) else tol_fn(ref)
         for p, l in sorted(per_pos.items()):
             err = float(np.abs(l.astype(np.float64) - ref[p]).max())
             worst = max(worst, err)

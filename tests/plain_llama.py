@@ -21,7 +21,9 @@ import numpy as np
 
 
 # ---- reading a model folder (own reader: the library's loader is not used here) ----------------
-def read_safetensors(path: str) -> Dict[str, np.ndarray]:
+def read_safetensors(path: str, keep=np.float64) -> Dict[str, np.ndarray]:
+    """Every tensor of the file as ``keep`` (float64; float32 for models of real layer sizes,
+    whose products are then taken row block by row block in float64, see ``linear``)."""
     out: Dict[str, np.ndarray] = {}
     with open(path, "rb") as f:
         (hlen,) = struct.unpack("<Q", f.read(8))
@@ -34,21 +36,32 @@ def read_safetensors(path: str) -> Dict[str, np.ndarray]:
         raw = np.frombuffer(data, dtype=np.uint8, count=e - b, offset=b)
         dt = info["dtype"]
         if dt == "F32":
-            a = raw.view(np.float32).astype(np.float64)
+            a = raw.view(np.float32).astype(keep)
         elif dt == "BF16":
-            a = (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+            a = (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32).astype(keep)
         elif dt == "F16":
-            a = raw.view(np.float16).astype(np.float64)
+            a = raw.view(np.float16).astype(keep)
         else:
             raise ValueError(f"{name}: dtype {dt}")
         out[name] = a.reshape(info["shape"])
     return out
 
 
-def read_model(folder: str):
+def read_model(folder: str, keep=np.float64):
     with open(os.path.join(folder, "config.json")) as f:
         cfg = json.load(f)
-    return cfg, read_safetensors(os.path.join(folder, "model.safetensors"))
+    return cfg, read_safetensors(os.path.join(folder, "model.safetensors"), keep)
+
+
+def linear(h: np.ndarray, w: np.ndarray) -> np.ndarray:
+    """y = h W^T with W [out, in] row-major, float64 products and sums (src/quant/f32_scalar.c:4-32).
+    A matrix kept in float32 is widened 8,192 rows at a time, so that no float64 copy of it exists."""
+    if w.dtype == np.float64:
+        return h @ w.T
+    out = np.empty((h.shape[0], w.shape[0]), dtype=np.float64)
+    for r in range(0, w.shape[0], 8192):
+        out[:, r:r + 8192] = h @ w[r:r + 8192].astype(np.float64).T
+    return out
 
 
 def to_bf16(a: np.ndarray) -> np.ndarray:
@@ -131,7 +144,7 @@ def silu(z: np.ndarray) -> np.ndarray:
 
 def swiglu(h: np.ndarray, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray) -> np.ndarray:
     """y = W_down (silu(W_gate h) * (W_up h)) (src/transformer/cpu.c:1247-1303)."""
-    return (silu(h @ w_gate.T) * (h @ w_up.T)) @ w_down.T
+    return linear(silu(linear(h, w_gate)) * linear(h, w_up), w_down)
 
 
 def attention_block(h, w, prefix, cfg, positions, round_fn=None):
@@ -142,13 +155,13 @@ def attention_block(h, w, prefix, cfg, positions, round_fn=None):
     hd = cfg.get("head_dim") or cfg["hidden_size"] // H
     r = round_fn or (lambda a: a)
     T = h.shape[0]
-    q = r(h @ w[prefix + "self_attn.q_proj.weight"].T).reshape(T, H, hd)
-    k = r(h @ w[prefix + "self_attn.k_proj.weight"].T).reshape(T, KV, hd)
-    v = r(h @ w[prefix + "self_attn.v_proj.weight"].T).reshape(T, KV, hd)
+    q = r(linear(h, w[prefix + "self_attn.q_proj.weight"])).reshape(T, H, hd)
+    k = r(linear(h, w[prefix + "self_attn.k_proj.weight"])).reshape(T, KV, hd)
+    v = r(linear(h, w[prefix + "self_attn.v_proj.weight"])).reshape(T, KV, hd)
     theta = float(cfg.get("rope_theta") or 10000.0)
     q, k = r(apply_rope(q, positions, theta)), r(apply_rope(k, positions, theta))
     a = r(attention(q, k, v, hd ** -0.5, int(cfg.get("sliding_window") or 0))).reshape(T, H * hd)
-    return r(a @ w[prefix + "self_attn.o_proj.weight"].T)
+    return r(linear(a, w[prefix + "self_attn.o_proj.weight"]))
 
 
 def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: Sequence[int], round_fn=None) -> np.ndarray:
@@ -168,11 +181,11 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: Sequence[int], round_fn
         h = r(rmsnorm(x, w[p + "input_layernorm.weight"], eps))
         x = x + attention_block(h, w, p, cfg, positions, round_fn)
         h = r(rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps))
-        gu_g, gu_u = r(h @ w[p + "mlp.gate_proj.weight"].T), r(h @ w[p + "mlp.up_proj.weight"].T)
-        x = x + r(r(silu(gu_g) * gu_u) @ w[p + "mlp.down_proj.weight"].T)
+        gu_g, gu_u = r(linear(h, w[p + "mlp.gate_proj.weight"])), r(linear(h, w[p + "mlp.up_proj.weight"]))
+        x = x + r(linear(r(silu(gu_g) * gu_u), w[p + "mlp.down_proj.weight"]))
     h = r(rmsnorm(x, w["model.norm.weight"], eps))
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
-    return h @ head.T
+    return linear(h, head)
 
 
 # ---- sampling (src/sampler.c) ---------------------------------------------------------------------

@@ -8,8 +8,9 @@ import numpy as np
 import pytest
 
 import bitnet_c_b200 as bn
-from helpers import (TOL_F32, bf16_bound, collect_trace_output, compare, make_model_dir, plain_logits,
-                     random_tokens, replay, steps_to_jsonl, trace_batches, trace_tail, trace_whole)
+import plain_llama
+from helpers import (TOL_F32, bf16_bound, collect_trace_output, compare, make_model_dir, measured_bf16_bound, plain_logits,
+                     random_tokens, replay, sharp_std, steps_to_jsonl, trace_batches, trace_chunks, trace_tail, trace_whole)
 from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
@@ -20,11 +21,19 @@ CASES = {
     "c": (TINY_C, 33, [70, 300, 64, 513, 97]),
     "d": (TINY_D, 44, [700, 130, 1, 260, 64, 500]),
 }
+# the same four with matrices of scale 1/sqrt(width) ("sharp", helpers.sharp_std): attention scores
+# spread over several units, so that rotation, softmax scale and which key gets which weight all
+# show in the logits far above bfloat16 rounding
+CASES.update({k + "_sharp": (cfg, seed + 1000, lens) for k, (cfg, seed, lens) in list(CASES.items())})
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def tol_for(dtype):
-    return (lambda ref: TOL_F32) if dtype == "float32" else bf16_bound
+def tol_for(setup):
+    """float32: 1e-4 on the stock models, 1e-4 relative to the largest logit on the sharp ones
+    (their logits reach 5); bfloat16: the stock bound, or per request the measured rounding gap."""
+    if setup["dtype"] == "float32":
+        return lambda ref: TOL_F32 * max(1.0, float(np.abs(ref).max()))
+    return setup["bf16_bounds"] if setup["sharp"] else bf16_bound
 
 
 def storage_for(dtype):
@@ -36,17 +45,25 @@ def storage_for(dtype):
 def setup(request, tmp_path_factory, cuda_device):
     case, dtype = request.param
     cfg, seed, lens = CASES[case]
-    d = make_model_dir(tmp_path_factory.mktemp("m"), cfg, seed, storage_for(dtype))
+    sharp = case.endswith("_sharp")
+    d = make_model_dir(tmp_path_factory.mktemp("m"), cfg, seed, storage_for(dtype),
+                       matrix_std=sharp_std(cfg) if sharp else 0.02)
     reqs = {f"r{i}": random_tokens(seed * 100 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)}
     model = bn.load_model(d, dtype=dtype)
-    return dict(case=case, dtype=dtype, cfg=cfg, dir=d, reqs=reqs, model=model, plain=plain_logits(d, reqs))
+    plain = plain_logits(d, reqs)
+    bounds = None
+    if sharp and dtype == "bfloat16":
+        pcfg, w = plain_llama.read_model(d)
+        bounds = {r: measured_bf16_bound(pcfg, w, t, plain[r]) for r, t in reqs.items()}
+    return dict(case=case, dtype=dtype, cfg=cfg, dir=d, reqs=reqs, model=model, plain=plain, sharp=sharp,
+                bf16_bounds=bounds)
 
 
 def test_each_request_alone_and_whole(setup):
     m = setup["model"]
     cache = m.new_cache(max_tokens=2048)
     got = replay(m, cache, trace_whole(setup["reqs"]))
-    compare(got, setup["plain"], tol_for(setup["dtype"]), "whole")
+    compare(got, setup["plain"], tol_for(setup), "whole")
     assert all(len(got[r]) == len(t) for r, t in setup["reqs"].items())
 
 
@@ -54,7 +71,7 @@ def test_last_32_tokens_one_by_one(setup):
     m = setup["model"]
     cache = m.new_cache(max_tokens=2048)
     got = replay(m, cache, trace_tail(setup["reqs"], 32))
-    compare(got, setup["plain"], tol_for(setup["dtype"]), "tail decode")
+    compare(got, setup["plain"], tol_for(setup), "tail decode")
     assert all(len(got[r]) == len(t) for r, t in setup["reqs"].items())
 
 
@@ -68,11 +85,37 @@ def test_unequal_batches_with_reused_slots(setup):
                {r: (reqs[r], d[i]) for i, r in enumerate(ids) if i % 2 == 1}]
     cache = m.new_cache(max_tokens=1024, max_seqs=3)
     got = replay(m, cache, trace_batches(batches))
-    compare(got, setup["plain"], tol_for(setup["dtype"]), "batches")
+    compare(got, setup["plain"], tol_for(setup), "batches")
     # once more in the same cache: every slot and page now holds another request's old data
     got = replay(m, cache, trace_batches(batches[::-1]))
-    compare(got, setup["plain"], tol_for(setup["dtype"]), "batches, second round")
+    compare(got, setup["plain"], tol_for(setup), "batches, second round")
     assert cache.slots.n_free == cache.slots.n_slots
+
+
+def test_continuation_chunks_mixed_with_fresh_prompts_and_single_tokens(setup):
+    """Requests fed in pieces of 1, 7, 64 and 130 tokens, one more request joining at every step:
+    steps mix a fresh prompt, many new tokens behind cached ones (the reference's prefill with
+    pos0 > 0, src/transformer/prefill.c:2494-2552, test/test_prefill.c:76-169) and single tokens."""
+    m = setup["model"]
+    steps = trace_chunks(setup["reqs"])
+    kinds = set()
+    seen = {}
+    for st in steps:
+        here = set()
+        for e in st["entries"]:
+            p0, n = seen.get(e["id"], 0), len(e["tokens"])
+            here.add("fresh" if p0 == 0 and n > 1 else "many behind cached" if p0 > 0 and n > 1 else "one")
+            seen[e["id"]] = p0 + n
+        if len(here) > 1:
+            kinds |= here
+    assert kinds == {"fresh", "many behind cached", "one"}  # the trace does mix them within steps
+    cache = m.new_cache(max_tokens=4096)
+    got = replay(m, cache, steps)
+    compare(got, setup["plain"], tol_for(setup), "chunks")
+    assert all(len(got[r]) == len(t) for r, t in setup["reqs"].items())
+    # and once more with other pieces in the cache the first pass left behind
+    got = replay(m, cache, trace_chunks(setup["reqs"], pieces=(130, 2, 63, 1, 65), stagger=2))
+    compare(got, setup["plain"], tol_for(setup), "chunks, second round")
 
 
 def test_trace_run_program(setup, tmp_path):
@@ -91,4 +134,17 @@ def test_trace_run_program(setup, tmp_path):
     done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
     assert done == [f"done {s['step']}" for s in steps]
     got = collect_trace_output(steps, str(out), setup["cfg"]["vocab_size"])
-    compare(got, setup["plain"], tol_for(setup["dtype"]), "trace_run")
+    compare(got, setup["plain"], tol_for(setup), "trace_run")
+
+
+def test_a_model_drawn_on_the_device_is_the_model_of_the_folder(tmp_path, cuda_device):
+    """``Model.from_random`` draws on the device what ``write_random_model`` writes: one generator."""
+    import torch
+    d = make_model_dir(tmp_path, TINY_B, 9, "bfloat16")
+    a = bn.load_model(d, dtype="bfloat16")
+    b = bn.Model.from_random(TINY_B, seed=9, dtype="bfloat16")
+    assert torch.equal(a.embedding, b.embedding) and a.head is a.embedding and b.head is b.embedding
+    for x, y in zip(a.blocks, b.blocks):
+        for u, v in ((x.mixer.w_qkv, y.mixer.w_qkv), (x.mixer.w_o, y.mixer.w_o), (x.ffn.w_gate_up, y.ffn.w_gate_up),
+                     (x.ffn.w_down, y.ffn.w_down), (x.mixer_norm.weight, y.mixer_norm.weight)):
+            assert u.dtype == v.dtype and (u != v).float().mean().item() < 1e-4

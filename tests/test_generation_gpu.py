@@ -10,7 +10,7 @@ import pytest
 
 import bitnet_c_b200 as bn
 import plain_llama
-from helpers import TOL_F32, bf16_bound, make_model_dir, random_tokens
+from helpers import TOL_F32, bf16_bound, make_model_dir, measured_bf16_bound, random_tokens, sharp_std
 from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
@@ -194,6 +194,38 @@ def test_decoding_across_the_recorded_graphs_length_buckets(tmp_path, cuda_devic
         slack = 2 * TOL_F32 if dtype == "float32" else 2 * bf16_bound(ref)
         for i, t in enumerate(g.tokens):
             assert ref[i, t] >= ref[i].max() - slack, f"step {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case,n_requests", [("a", 20), ("c", 20), ("a", 70), ("c", 70)])
+def test_decode_batches_of_twenty_and_seventy_sequences(tmp_path, cuda_device, dtype, case, n_requests):
+    """Decode steps of 20 and of 70 sequences of unequal lengths through the entry point (in
+    bfloat16 the products' accumulators are 32 and 64 sequences wide inside the recorded step, and
+    beyond 64 sequences they go to the library), on sharp models: every emitted token must be the
+    plain implementation's choice at its place, or within the rounding bound of it.  Requests
+    end at different steps, so the batch shrinks through many sizes."""
+    cfg = {"a": TINY_A, "c": TINY_C}[case]
+    d = make_model_dir(tmp_path, cfg, 900 + n_requests, "float32" if dtype == "float32" else "bfloat16",
+                       matrix_std=sharp_std(cfg))
+    model = bn.load_model(d, dtype=dtype)
+    pcfg, w = plain_llama.read_model(d)
+    rng = np.random.default_rng(n_requests)
+    top = 60 if case == "a" else 200
+    lens = [int(x) for x in rng.integers(1, top, size=n_requests)]
+    new = [int(x) for x in rng.integers(3, 14, size=n_requests)]
+    prompts = [random_tokens(7000 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)]
+    got = bn.generate(model, prompts, max_new_tokens=new, stop_ids=[])
+    assert [len(g.tokens) for g in got] == new
+    exact = 0
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        toks = list(p) + g.tokens[:-1]
+        ref = plain_llama.forward(pcfg, w, toks)
+        slack = 2 * TOL_F32 * float(np.abs(ref).max()) if dtype == "float32" else measured_bf16_bound(pcfg, w, toks, ref)
+        for j, t in enumerate(g.tokens):
+            row = ref[len(p) - 1 + j]
+            assert row[t] >= row.max() - 2 * slack, f"request {i} (prompt of {len(p)}), new token {j}"
+            exact += int(t == int(np.argmax(row)))
+    assert exact >= 0.97 * sum(new)  # nearly all are the plain argmax itself
 
 
 @pytest.mark.parametrize("group", [1, 2, 3])

@@ -317,6 +317,7 @@ def test_linear_mma_swiglu_epilogue(cuda_device, M, I, K):
 @pytest.mark.parametrize("H,KV,hd,lens,window", [
     (4, 2, 16, [1, 5, 64, 130], 0), (3, 1, 48, [200, 129, 128], 0), (32, 8, 128, [700, 3], 0),
     (2, 2, 256, [257], 0), (40, 40, 64, [100, 300], 0), (12, 1, 32, [150, 40, 260], 17), (4, 4, 80, [513], 130),
+    (32, 1, 64, [300, 70], 0), (40, 1, 128, [200, 513], 0), (80, 2, 64, [140, 66], 0),  # 32 and 40 query heads on one key/value head
 ])
 def test_attention_decode(cuda_device, H, KV, hd, lens, window):
     """One new token per sequence over scattered pages; a far key is made to dominate one row."""
@@ -502,6 +503,8 @@ def _last_row_attention(q, k, v, scale, window):
     (40, 40, 128, 128, [3000, 17, 2049], 0), (32, 8, 64, 64, [2303, 1], 0), (8, 2, 128, 128, [5000, 4097], 1024),
     (4, 2, 64, 40, [70, 200], 0),  # rotary dimensions that are no multiple of 16
     (8, 1, 128, 128, [20000], 0),  # one long sequence: more blocks than a cluster holds, chosen by the policy
+    # more than 16 query heads on one key/value head: two and three blocks of 16 rows per head
+    (32, 1, 64, 64, [300, 70, 1100], 0), (40, 1, 128, 128, [200, 513], 0), (80, 2, 64, 64, [140, 1030], 0),
 ])
 @pytest.mark.parametrize("splits", [0, 3, 12, "list1", "list2", "list4"])
 def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd, lens, window):

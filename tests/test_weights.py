@@ -11,7 +11,7 @@ import bitnet_c_b200  # noqa: F401
 from bitnet_c_b200.config import LlamaConfig, architecture
 from bitnet_c_b200.engine import parameter_table
 from bitnet_c_b200.weights import (SafetensorsError, SafetensorsFile, WeightsError, load_weights, standard_normal,
-                                   write_random_model, write_safetensors)
+                                   standard_normal_on, write_random_model, write_safetensors)
 import plain_llama
 from tiny_configs import TINY_A, TINY_B
 
@@ -69,6 +69,20 @@ def test_same_seed_same_bytes_other_seed_other_bytes(tmp_path):
     n = w["model.norm.weight"]
     assert abs(n.mean() - 1.0) < 0.05 and 0.05 < n.std() < 0.15
     assert "lm_head.weight" not in w  # tied
+
+
+def test_the_generator_restated_in_torch_gives_the_same_values(tmp_path):
+    """``standard_normal_on`` (what large models are drawn with, on the device) is the same function
+    of (seed, name, index) as the NumPy generator; a model folder written through it holds the
+    same bytes."""
+    a = standard_normal(11, "model.layers.1.mlp.up_proj.weight", 1 << 18, start=(1 << 33) + 5)
+    b = standard_normal_on("cpu", 11, "model.layers.1.mlp.up_proj.weight", 1 << 18, start=(1 << 33) + 5).numpy()
+    assert (a != b).mean() < 1e-4 and np.abs(a - b).max() < 1e-6
+    x = write_random_model(str(tmp_path / "host"), TINY_A, seed=4, dtype="bfloat16")
+    y = write_random_model(str(tmp_path / "torch"), TINY_A, seed=4, dtype="bfloat16", device="cpu")
+    _c, wx = plain_llama.read_model(x)
+    _c, wy = plain_llama.read_model(y)
+    assert sorted(wx) == sorted(wy) and all(np.array_equal(wx[k], wy[k]) for k in wx)
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
