@@ -29,6 +29,18 @@ from tiny_configs import TINY_A, TINY_B  # noqa: E402
 import plain_llama  # noqa: E402
 
 CASES = {"tiny_a": (TINY_A, 1234, 12), "tiny_b": (TINY_B, 4321, 40)}
+# sampler settings run over the stored logits: temperature, top_p, repeat_penalty, logit_scale, seed, window.
+# The tiny models' logits are of size 0.3; the scale makes distributions from nearly flat to peaked.
+SAMPLER_SETTINGS = [
+    (0.0, 0.9, 1.0, 1.0, 42, 64),     # greedy
+    (0.0, 0.9, 1.3, 1.0, 42, 8),      # greedy with a repeat penalty over a short window
+    (0.8, 1.0, 1.0, 1.0, 1234, 64),   # plain multinomial walk, nearly flat
+    (0.8, 0.0, 1.0, 6.0, 7, 64),      # top_p 0 also means no nucleus; peaked
+    (1.0, 0.9, 1.0, 4.0, 99, 64),     # nucleus
+    (0.5, 0.5, 1.0, 3.0, 0, 64),      # nucleus, seed 0 (becomes 42)
+    (0.7, 0.95, 1.1, 6.0, 5, 64),     # nucleus with a repeat penalty
+    (1.5, 0.3, 1.2, 8.0, 31337, 4),   # narrow nucleus, short window
+]
 
 
 def main() -> None:
@@ -69,11 +81,18 @@ def main() -> None:
         inp, outp = os.path.join(work, name + ".in"), os.path.join(work, name + ".out")
         with open(inp, "wb") as f:
             f.write(b"".join(parts))
-        subprocess.run([exe, inp, outp], check=True)
+        setp, idp = os.path.join(work, name + ".settings"), os.path.join(work, name + ".ids")
+        with open(setp, "wb") as f:
+            f.write(np.array([len(SAMPLER_SETTINGS)], np.int32).tobytes())
+            for t, p_, rp, sc, sd, win in SAMPLER_SETTINGS:
+                f.write(np.array([t, p_, rp, sc], np.float32).tobytes() + np.array([sd, win], np.int32).tobytes())
+        subprocess.run([exe, inp, outp, setp, idp], check=True)
         raw = np.fromfile(outp, dtype=np.float32)
         V = cfg["vocab_size"]
+        ids = np.fromfile(idp, dtype=np.int32).reshape(len(SAMPLER_SETTINGS), n_tokens)
         np.savez(os.path.join(HERE, name + ".npz"), config=json.dumps(cfg), seed=seed, tokens=tokens,
-                 forward_logits=raw[: n_tokens * V].reshape(n_tokens, V), prefill_logits=raw[n_tokens * V:])
+                 forward_logits=raw[: n_tokens * V].reshape(n_tokens, V), prefill_logits=raw[n_tokens * V:],
+                 sampler_settings=np.array(SAMPLER_SETTINGS, np.float64), sampler_ids=ids)
         print(name, "written;", "max |logit|", float(np.abs(raw).max()))
     shutil.rmtree(work)
 

@@ -13,11 +13,19 @@
  * then output_norm and (if not tied) output.
  * Output file: float32 [n_tokens, vocab] from token-by-token forward, then float32 [vocab]
  * from the prefill of the whole prompt.
+ *
+ * With a third and fourth argument it also runs the reference's sampler (src/sampler.c) over
+ * the token-by-token logits.  Settings file: int32 n, then n records of float32 {temperature,
+ * top_p, repeat_penalty, logit_scale} and int32 {seed, window}.  For each setting a sampler is
+ * made (bn_sampler_init, bn_sampler_set_repeat_penalty when the penalty is above 1), the prompt's
+ * tokens are accepted as src/main.c:1648 does, and for every position t one id is drawn from
+ * logits[t] * logit_scale and accepted.  Output: int32 [n, n_tokens].
  */
 #include "model.h"
 #include "session.h"
 #include "transformer.h"
 #include "gguf.h"
+#include "sampler.h"
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -32,7 +40,7 @@ static BnQWeight qw(float *data, int rows, int cols) {
 }
 
 int main(int argc, char **argv) {
-    if (argc != 3) { fprintf(stderr, "usage: %s in.bin out.bin\n", argv[0]); return 2; }
+    if (argc != 3 && argc != 5) { fprintf(stderr, "usage: %s in.bin out.bin [settings.bin ids.bin]\n", argv[0]); return 2; }
     FILE *f = fopen(argv[1], "rb");
     if (!f) { perror("open"); return 1; }
     fseek(f, 0, SEEK_END); long size = ftell(f); fseek(f, 0, SEEK_SET);
@@ -82,10 +90,12 @@ int main(int argc, char **argv) {
     FILE *o = fopen(argv[2], "wb");
     BnSession *s = bn_session_create(&m, NULL);
     if (!s) { fprintf(stderr, "session create failed\n"); return 1; }
+    float *all = malloc((size_t)T * V * sizeof(float));
     for (int t = 0; t < T; t++) {
         float *logits = bn_transformer_forward(&m, s, tokens[t], t);
         if (!logits) { fprintf(stderr, "forward failed at %d\n", t); return 1; }
         fwrite(logits, sizeof(float), V, o);
+        memcpy(all + (size_t)t * V, logits, (size_t)V * sizeof(float));
     }
     bn_session_reset(s, &m);
     float *pl = bn_transformer_prefill(&m, s, tokens, T, 0);
@@ -93,5 +103,28 @@ int main(int argc, char **argv) {
     fwrite(pl, sizeof(float), V, o);
     fclose(o);
     bn_session_free(s, NULL);
+    if (argc == 5) {
+        FILE *sf = fopen(argv[3], "rb");
+        FILE *idf = fopen(argv[4], "wb");
+        int n = 0;
+        if (!sf || !idf || fread(&n, sizeof(int), 1, sf) != 1) { fprintf(stderr, "settings unreadable\n"); return 1; }
+        float *buf = malloc((size_t)V * sizeof(float));
+        for (int i = 0; i < n; i++) {
+            float f[4]; int k[2];
+            if (fread(f, sizeof(float), 4, sf) != 4 || fread(k, sizeof(int), 2, sf) != 2) { fprintf(stderr, "settings short\n"); return 1; }
+            BnSampler sp;
+            if (bn_sampler_init(&sp, V, f[0], f[1], (uint64_t)k[0]) != 0) return 1;
+            if (f[2] > 1.0f) bn_sampler_set_repeat_penalty(&sp, f[2], k[1]);
+            for (int t = 0; t < T; t++) bn_sampler_accept(&sp, tokens[t]);
+            for (int t = 0; t < T; t++) {
+                for (int v = 0; v < V; v++) buf[v] = all[(size_t)t * V + v] * f[3];
+                int id = bn_sampler_sample(&sp, buf);
+                bn_sampler_accept(&sp, id);
+                fwrite(&id, sizeof(int), 1, idf);
+            }
+            bn_sampler_free(&sp);
+        }
+        fclose(sf); fclose(idf);
+    }
     return 0;
 }
