@@ -66,6 +66,10 @@ class LlamaConfig:
                 raise ConfigError(
                     f"config.json: rope_scaling={scaling!r} is not supported "
                     "(the reference applies no RoPE scaling, src/model_arch.c:322-338)")
+        if d.get("sliding_window"):
+            raise ConfigError(
+                f"config.json: sliding_window={d['sliding_window']!r} is not supported: this architecture attends "
+                "to every earlier position (src/transformer/gqa_scalar.c:61-121)")
         for key in ("attention_bias", "mlp_bias"):
             if d.get(key):
                 raise ConfigError(f"config.json: {key}=true is not supported for this architecture")

@@ -8,6 +8,7 @@
 #include "argmax_noalloc.h"
 #include <math.h>
 #include <stdint.h>
+#include <mutex>
 
 #define NA_BLOCKS 64  // blocks per row
 #define NA_MAX_DEVICES 64
@@ -83,8 +84,10 @@ __global__ void argmax_noalloc_kernel(const float* __restrict__ logits, int ld, 
   if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
 }
 
-// Device address of g_scratch on each device, looked up on the first call there.
+// Device address of g_scratch on each device, looked up on the first call there (under the lock:
+// two host threads may make their first call at once).
 static NaScratch* g_scratch_addr[NA_MAX_DEVICES];
+static std::mutex g_setup_lock;
 
 extern "C" int bn_argmax_noalloc(const float* logits, int ld, int n_rows, int vocab, int* out, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
@@ -92,13 +95,22 @@ extern "C" int bn_argmax_noalloc(const float* logits, int ld, int n_rows, int vo
   if (n_rows > BN_ARGMAX_NOALLOC_MAX_ROWS) return BN_ARGMAX_NOALLOC_TOO_MANY_ROWS;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NA_MAX_DEVICES) return BN_ARGMAX_NOALLOC_NO_DEVICE_ADDRESS;
-  NaScratch* scratch = g_scratch_addr[dev];
-  if (!scratch) {
-    // set-up, once per device, with that device current: the symbol's address on this device
-    void* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, g_scratch);
-    if (e != cudaSuccess || !p) return BN_ARGMAX_NOALLOC_NO_DEVICE_ADDRESS;
-    scratch = g_scratch_addr[dev] = (NaScratch*)p;
+  // the scratch used is the current device's copy: the logits must live there too (asking where a
+  // pointer lives allocates nothing)
+  cudaPointerAttributes where;
+  if (cudaPointerGetAttributes(&where, logits) != cudaSuccess) { cudaGetLastError(); return 1; }
+  if (where.type == cudaMemoryTypeDevice && where.device != dev) return BN_ARGMAX_NOALLOC_WRONG_DEVICE;
+  NaScratch* scratch;
+  {
+    std::lock_guard<std::mutex> hold(g_setup_lock);
+    scratch = g_scratch_addr[dev];
+    if (!scratch) {
+      // set-up, once per device, with that device current: the symbol's address on this device
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_scratch);
+      if (e != cudaSuccess || !p) return BN_ARGMAX_NOALLOC_NO_DEVICE_ADDRESS;
+      scratch = g_scratch_addr[dev] = (NaScratch*)p;
+    }
   }
   // the array keeps the last call's contents; the tickets must start at zero
   cudaError_t e = cudaMemsetAsync(scratch->tickets, 0, sizeof(int) * n_rows, stream);

@@ -25,6 +25,10 @@
  *    point is ever called.
  *  - The first call on a device looks up the device address of that array (once per device,
  *    with that device current).  Make this first call before any stream capture begins.
+ *  - Call it with the device current on which logits, out and the stream live: the scratch used
+ *    is the current device's.  Logits that live on another device are refused with
+ *    BN_ARGMAX_NOALLOC_WRONG_DEVICE and nothing is launched.  Host threads may make their first
+ *    calls at the same time; the set-up is done under a lock.
  *  - The entry point calls no cudaMalloc, cudaFree or other allocating routine.
  *  - All calls on a device share the one array, and it keeps what the last call left in it.
  *    The part that must start at zero (the ticket counters) is cleared on the stream at the
@@ -34,8 +38,9 @@
  *
  * Returns 0 on success, 1 for bad arguments (null pointers, vocab <= 0, ld < vocab),
  * BN_ARGMAX_NOALLOC_TOO_MANY_ROWS for too many rows, BN_ARGMAX_NOALLOC_NO_DEVICE_ADDRESS if the
- * scratch's device address could not be obtained, or 100 + the CUDA error code of a failed
- * clear or launch.
+ * scratch's device address could not be obtained, BN_ARGMAX_NOALLOC_WRONG_DEVICE if the logits
+ * live on another device than the current one, or 100 + the CUDA error code of a failed clear
+ * or launch.
  */
 #ifndef BN_ARGMAX_NOALLOC_H
 #define BN_ARGMAX_NOALLOC_H
@@ -45,6 +50,7 @@
 #define BN_ARGMAX_NOALLOC_MAX_ROWS 256
 #define BN_ARGMAX_NOALLOC_TOO_MANY_ROWS 3
 #define BN_ARGMAX_NOALLOC_NO_DEVICE_ADDRESS 4
+#define BN_ARGMAX_NOALLOC_WRONG_DEVICE 5
 
 #ifdef __cplusplus
 extern "C" {

@@ -79,7 +79,7 @@ struct DtArgs {
   __nv_bfloat16* k_cache;
   __nv_bfloat16* v_cache;
   int* status;     // 0, or DT_ERR_PAGE_WAIT when a page never arrived
-  unsigned long long* trace;  // debugging: timestamps of blocks (0, 0, z), 16 per block, or null
+  BN_TRACE_ONLY(unsigned long long* trace;)  // debugging: timestamps of blocks (0, 0, z), 16 per block, or null
   float* part_o;   // [n_seqs][n_heads][splits][head_dim]
   float* part_ml;  // [n_seqs][n_heads][splits][2]: maximum (in the scaled log2 domain) and sum
   int pages_per_block;
@@ -97,8 +97,8 @@ __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DtArgs a) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned long long* tr = (a.trace && a.items == nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? a.trace + 16 * blockIdx.z : nullptr;
-  if (tr) tr[0] = global_timer();
+  BN_TRACE_ONLY(unsigned long long* tr = (a.trace && a.items == nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? a.trace + 16 * blockIdx.z : nullptr;)
+  BN_TRACE_ONLY(if (tr) tr[0] = global_timer();)
   constexpr int CHUNKS = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, BOXES = HD / 64;
   constexpr int PAGE_BYTES = BN_PAGE * HD * 2;       // one page of keys (or values) of one head
   constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
@@ -182,7 +182,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     for (int st = 0; st < DT_STAGES; ++st)  // the whole ring is requested at once
       if (st < n_pages) request_page(my_lo + st, st);
   }
-  if (tr) tr[1] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[1] = global_timer();)
   // the rotation of this position, also before the wait: it depends on the position only
   const int half = a.rotary_dims >> 1;
   for (int i = tid; i < half; i += DT_THREADS) {
@@ -195,9 +195,9 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   // the new token's row (also before the wait)
   for (int p = tid; p < DT_ROWS * HD / 8; p += DT_THREADS) reinterpret_cast<uint4*>(q_tile)[p] = make_uint4(0u, 0u, 0u, 0u);
   for (int p = tid; p < 2 * HD / 8; p += DT_THREADS) reinterpret_cast<uint4*>(new_kv)[p] = make_uint4(0u, 0u, 0u, 0u);
-  if (tr) tr[2] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[2] = global_timer();)
   pdl_wait();  // the kernel before this one has completed: the q|k|v rows are there
-  if (tr) tr[3] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[3] = global_timer();)
   __syncthreads();
 
   // ---- queries of this head group (rotated, rounded to bfloat16, rows of the 16-row tile) and the
@@ -306,7 +306,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   constexpr bool Q_IN_REGS = HD <= 128;
   unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
   bool failed = false;
-  if (tr) tr[4] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[4] = global_timer();)
   for (int i = 0; i < n_pages; ++i) {
     const int stage = i % DT_STAGES;
     // one thread watches the stage's mbarrier, the others sleep at the block's barrier
@@ -314,7 +314,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (tid == 0) arrived = mbar_wait(full0 + 8 * stage, (unsigned)(i / DT_STAGES) & 1u, a.status, DT_ERR_PAGE_WAIT);
     // page i has landed for everyone; the stage of page i-1 is free; q and new_kv are written
     if (__syncthreads_or(arrived ? 0 : 1)) { failed = true; break; }
-    if (tr && i < 2) tr[5 + i] = global_timer();
+    BN_TRACE_ONLY(if (tr && i < 2) tr[5 + i] = global_timer();)
     if (tid == 0 && i >= 1 && i - 1 + DT_STAGES < n_pages) request_page(my_lo + i - 1 + DT_STAGES, (i - 1) % DT_STAGES);
     if (Q_IN_REGS && i == 0) {
 #pragma unroll
@@ -418,7 +418,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     }
     return;
   }
-  if (tr) tr[7] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[7] = global_timer();)
   __syncthreads();  // every warp is done with the stages: they now hold the warps' outputs
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -463,14 +463,14 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     else a.part_o[(((size_t)b * n_heads + h0 + g) * n_splits + zi) * head_dim + d] = acc;
   }
   if (alone) {
-    if (tr) tr[8] = global_timer();
+    BN_TRACE_ONLY(if (tr) tr[8] = global_timer();)
     return;
   }
   if (clustered) {
     // ---- every block's result is in its own shared memory: after the cluster's barrier each
     // active block adds up, in split order, a slice of the rows' dimensions read from all of them
     dt_cluster_sync();
-    if (tr) tr[8] = global_timer();
+    BN_TRACE_ONLY(if (tr) tr[8] = global_timer();)
     const unsigned a_ml = smem_u32(ml_fin), a_o = smem_u32(o_fin);
     const int n_act = z_hi - z_lo + 1, mine = zi - z_lo;
     const int total = G * head_dim, per = (total + n_act - 1) / n_act;
@@ -497,7 +497,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       }
       a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num / den);
     }
-    if (tr) tr[10] = global_timer();
+    BN_TRACE_ONLY(if (tr) tr[10] = global_timer();)
     dt_cluster_sync();  // no block leaves while another still reads its result
     return;
   }
@@ -517,7 +517,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (s_last) *t = 0;
   }
   __syncthreads();
-  if (tr) tr[9] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[9] = global_timer();)
   if (!s_last) return;
   __threadfence();
   if (tid < G) {
@@ -538,9 +538,10 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     for (int z = z_lo; z <= z_hi; ++z) num += exp2f(__ldcg(ml + 2 * z) - m) * __ldcg(po + (size_t)z * head_dim + d);
     a.out[(size_t)b * a.out_stride + (size_t)(h0 + g) * head_dim + d] = __float2bfloat16_rn(num / ml_fin[g * 2 + 1]);
   }
-  if (tr) tr[10] = global_timer();
+  BN_TRACE_ONLY(if (tr) tr[10] = global_timer();)
 }
 
+#ifdef BN_TRACE
 // Debugging aid: bn_attention_decode_tc_trace(n) makes the next n launches record timestamps of
 // their blocks (0, 0, z < 8) (device buffer allocated here; not used on the product path).
 static unsigned long long* g_dt_trace = nullptr;
@@ -558,6 +559,7 @@ extern "C" int bn_attention_decode_tc_trace_read(unsigned long long* host, int n
   if (!g_dt_trace || n > g_dt_trace_cap) return 1;
   return cudaMemcpy(host, g_dt_trace, (size_t)n * 8 * 16 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
+#endif
 
 // Dynamic shared memory of a block: alignment slack, the ring of key and value pages, the query
 // tile, the new key and value, the warps' and the block's maxima and sums, the ring's mbarriers,
@@ -664,14 +666,14 @@ static int dt_run(const void* qkv, int q_stride, int k_off, int v_off, void* out
   a.theta_scale = theta_scale; a.tok_pos = tok_pos; a.slots = slots; a.page_table = page_table; a.pt_stride = pt_stride;
   a.k_cache = (__nv_bfloat16*)k_cache; a.v_cache = (__nv_bfloat16*)v_cache; a.part_o = part_o; a.part_ml = part_ml;
   a.status = status;
-  a.trace = nullptr;
-  if (g_dt_trace && g_dt_trace_n < g_dt_trace_cap && n_splits <= 8) a.trace = g_dt_trace + (size_t)8 * 16 * (g_dt_trace_n++);
+  BN_TRACE_ONLY(a.trace = nullptr;)
+  BN_TRACE_ONLY(if (g_dt_trace && g_dt_trace_n < g_dt_trace_cap && n_splits <= 8) a.trace = g_dt_trace + (size_t)8 * 16 * (g_dt_trace_n++);)
   a.cluster = (n_splits > 1 && n_splits <= 8) ? 1 : 0;  // few splits: one cluster per (sequence, head group)
   a.pages_per_block = pages_per_block; a.tickets = tickets; a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
   a.items = items;
   dim3 grid(n_seqs, n_kv_heads * gblocks, n_splits), cluster(1, 1, n_splits);
   if (items != nullptr) {
-    a.trace = nullptr;
+    BN_TRACE_ONLY(a.trace = nullptr;)
     grid = dim3(n_items, n_kv_heads * gblocks, 1);
     cluster = dim3(item_group, 1, 1);
   }

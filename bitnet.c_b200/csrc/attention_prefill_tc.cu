@@ -59,7 +59,7 @@ struct PtArgs {
   const int* page_table;
   int pt_stride;
   int* status;
-  unsigned long long* trace;  // debugging: timestamps of block (0, 0), or null
+  BN_TRACE_ONLY(unsigned long long* trace;)  // debugging: timestamps of block (0, 0), or null
 };
 #define PT_TRACE_TILES 12  // per tile: 6 stamps of a softmax thread, 3 of the MMA thread
 
@@ -198,18 +198,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
     bool ok = __all_sync(0xffffffffu, pt_wait(q_full, 0, failed, a.status));
     const unsigned sq = smem_u32(q_smem);
-    const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && issuer;
+    BN_TRACE_ONLY(const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && issuer;)
     for (int j = 0; ok && j <= n_tiles; ++j) {
       if (j < n_tiles) {
         // S_j = Q K_j^T into score buffer j & 1
         const int s = j % KS, b = j & 1;
-        const bool trs = tracing && j < PT_TRACE_TILES;
+        BN_TRACE_ONLY(const bool trs = tracing && j < PT_TRACE_TILES;)
         ok = __all_sync(0xffffffffu, pt_wait(k_full0 + 8 * s, (unsigned)(j / KS) & 1u, failed, a.status));
         if (!ok) break;
-        if (trs) a.trace[j * 12 + 9] = global_timer();
+        BN_TRACE_ONLY(if (trs) a.trace[j * 12 + 9] = global_timer();)
         // (S_j reuses the buffer of S_{j-2} and P_{j-2}: P_{j-2} V_{j-2} was issued before and the
         // tensor pipe keeps the order)
-        if (trs) a.trace[j * 12 + 10] = global_timer();
+        BN_TRACE_ONLY(if (trs) a.trace[j * 12 + 10] = global_timer();)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned sk = smem_u32(k_smem + s * PAGE_BYTES);
         if (issuer) {
@@ -217,10 +217,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int ks = 0; ks < HD / 16; ++ks)
             umma_mma(tbase + b * PT_KEYS, umma_desc_k(sq + (ks >> 2) * Q_BOX + (ks & 3) * 32),
                    umma_desc_k(sk + (ks >> 2) * KV_BOX + (ks & 3) * 32), IDESC_S, ks ? 1u : 0u);
-          if (trs) a.trace[j * 12 + 11] = global_timer();
+          BN_TRACE_ONLY(if (trs) a.trace[j * 12 + 11] = global_timer();)
           umma_commit(k_empty0 + 8 * s);  // the key stage may be refilled
           umma_commit(s_full0 + 8 * b);
-          if (trs) a.trace[j * 12 + 6] = global_timer();
+          BN_TRACE_ONLY(if (trs) a.trace[j * 12 + 6] = global_timer();)
         }
         __syncwarp();
       }
@@ -231,8 +231,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                          pt_wait(v_full0 + 8 * s, (unsigned)(i / VS) & 1u, failed, a.status));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const bool tr = tracing && i < PT_TRACE_TILES;
-        if (tr) a.trace[i * 12 + 7] = global_timer();
+        BN_TRACE_ONLY(const bool tr = tracing && i < PT_TRACE_TILES;)
+        BN_TRACE_ONLY(if (tr) a.trace[i * 12 + 7] = global_timer();)
         const unsigned sv = smem_u32(v_smem + s * PAGE_BYTES);
         if (issuer) {
 #pragma unroll
@@ -241,7 +241,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                       (i | kk) ? 1u : 0u);
           umma_commit(v_empty0 + 8 * s);    // the value stage may be refilled
           umma_commit(pv_done);             // O holds the pages up to i
-          if (tr) a.trace[i * 12 + 8] = global_timer();
+          BN_TRACE_ONLY(if (tr) a.trace[i * 12 + 8] = global_timer();)
         }
         __syncwarp();
       }
@@ -258,14 +258,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1, tile = tile_lo + j;
-      const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 64 && j < PT_TRACE_TILES;
-      if (tr) a.trace[j * 12 + 0] = global_timer();
+      BN_TRACE_ONLY(const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 64 && j < PT_TRACE_TILES;)
+      BN_TRACE_ONLY(if (tr) a.trace[j * 12 + 0] = global_timer();)
       if (!pt_wait(s_full0 + 8 * b, (unsigned)(j >> 1) & 1u, failed, a.status)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (tr) a.trace[j * 12 + 1] = global_timer();
+      BN_TRACE_ONLY(if (tr) a.trace[j * 12 + 1] = global_timer();)
       float s[PT_KEYS];
       tmem_ld64(lane_addr + b * PT_KEYS, s);
-      if (tr) a.trace[j * 12 + 2] = global_timer();
+      BN_TRACE_ONLY(if (tr) a.trace[j * 12 + 2] = global_timer();)
       // mask, then the maximum of the raw scores (the scale is positive); four chains, not one
       const int k0 = tile * PT_KEYS;
       if (!(k0 >= qlo && k0 + PT_KEYS - 1 <= qpos)) {
@@ -308,9 +308,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ls[k & 3] += s[k];
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      if (tr) a.trace[j * 12 + 3] = global_timer();
+      BN_TRACE_ONLY(if (tr) a.trace[j * 12 + 3] = global_timer();)
       // P as bfloat16 into tensor memory, two keys per column, over the columns S came from
-      if (tr) a.trace[j * 12 + 4] = global_timer();
+      BN_TRACE_ONLY(if (tr) a.trace[j * 12 + 4] = global_timer();)
       {
         float pk[32];
 #pragma unroll
@@ -332,7 +332,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full0 + 8 * b);
-      if (tr) a.trace[j * 12 + 5] = global_timer();
+      BN_TRACE_ONLY(if (tr) a.trace[j * 12 + 5] = global_timer();)
     }
     // ---- epilogue: O / sum -> out
     if (ok && pt_wait(pv_done, (unsigned)(n_tiles - 1) & 1u, failed, a.status)) {
@@ -371,6 +371,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
+#ifdef BN_TRACE
 // Debugging aid: bn_attention_prefill_tc_trace(1) makes the next launch record timestamps of block
 // (0, 0) (device buffer allocated here; not used on the product path).
 static unsigned long long* g_pt_trace = nullptr;
@@ -388,6 +389,7 @@ extern "C" int bn_attention_prefill_tc_trace_read(unsigned long long* host) {
   if (!g_pt_trace) return 1;
   return cudaMemcpy(host, g_pt_trace, PT_TRACE_TILES * 12 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
+#endif
 
 template <int HD, int KS, int VS>
 static int launch_pt(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PtArgs& a, int n_tiles,
@@ -436,8 +438,8 @@ extern "C" int bn_attention_prefill_tc(const void* q, int q_stride, int n_tokens
   a.head_dim = head_dim; a.scale_log2e = scale * 1.4426950408889634f; a.window = window; a.tile_seq = tile_seq;
   a.tile_row0 = tile_row0; a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.slots = slots; a.page_table = page_table;
   a.pt_stride = pt_stride; a.status = status;
-  a.trace = nullptr;
-  if (g_pt_trace_armed) { a.trace = g_pt_trace; g_pt_trace_armed = false; }
+  BN_TRACE_ONLY(a.trace = nullptr;)
+  BN_TRACE_ONLY(if (g_pt_trace_armed) { a.trace = g_pt_trace; g_pt_trace_armed = false; })
   // shared memory per block: 64 KB and 96 KB, so that two blocks share an SM (tensor memory
   // allows no more: 256 columns each) and one block's softmax overlaps the other's products
   // (a third key stage at head size 128 was measured and changes nothing: the softmax is the pace)

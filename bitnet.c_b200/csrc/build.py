@@ -50,6 +50,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-shared",
 ]
 # No --use_fast_math: softmax, norms and rotation angles need exact expf and sincosf.
+# Further flags for builds of one's own (-DBN_TRACE: timestamp probes; -DBN_NO_PDL: no programmatic
+# dependent launch).  Set before anything is loaded; they enter the libraries' names.
+EXTRA_FLAGS: List[str] = []
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
@@ -97,7 +100,7 @@ def _digest(family: str) -> str:
     for fn in [SOURCES[family]] + headers:
         with open(os.path.join(_HERE, fn), "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + EXTRA_FLAGS).encode())
     return h.hexdigest()[:12]
 
 
@@ -113,7 +116,7 @@ def library_path(family: str) -> str:
 def _compile(family: str, out: str, log: List[str]) -> None:
     nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp, os.path.join(_HERE, SOURCES[family])]
+    cmd = [nvcc] + NVCC_FLAGS + EXTRA_FLAGS + ["-I", _HERE, "-o", tmp, os.path.join(_HERE, SOURCES[family])]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)

@@ -30,16 +30,22 @@
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-#include <cstdlib>
 #include <utility>
-static inline bool bn_pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("BN_NO_PDL");  // set to serialise kernels completely (for comparison)
-    on = (e && e[0] && e[0] != '0') ? 0 : 1;
-  }
-  return on != 0;
-}
+// Compile with -DBN_NO_PDL to serialise kernels completely (for comparisons; csrc/build.py's
+// EXTRA_FLAGS); nothing at run time switches it.
+#ifdef BN_NO_PDL
+static inline bool bn_pdl_enabled() { return false; }
+#else
+static inline bool bn_pdl_enabled() { return true; }
+#endif
+
+// Timestamp probes inside the TMA-fed kernels (where a block's time goes) exist only in builds
+// made with -DBN_TRACE; the default build has neither the stores nor the entry points.
+#ifdef BN_TRACE
+#define BN_TRACE_ONLY(...) __VA_ARGS__
+#else
+#define BN_TRACE_ONLY(...)
+#endif
 template <typename... KArgs, typename... Args>
 static inline cudaError_t bn_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     Args&&... args) {

@@ -83,7 +83,7 @@ struct TcArgs {
   float* ss_out;         // mode 3: [tiles * cluster][ss_out_stride] sums of squares of this block's slice of each row
   int ss_out_stride;
   int* status;     // 0, or the code of a wait that gave up
-  unsigned long long* trace;  // debugging: 8 timestamps of block 0 per launch, or null
+  BN_TRACE_ONLY(unsigned long long* trace;)  // debugging: 8 timestamps of block 0 per launch, or null
 };
 
 // First row (of 128) of the slice that cluster rank r reduces and stores.  SwiGLU: multiples of 16,
@@ -188,8 +188,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
-  const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-  if (tracing && tid == 0) a.trace[0] = global_timer();
+  BN_TRACE_ONLY(const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;)
+  BN_TRACE_ONLY(if (tracing && tid == 0) a.trace[0] = global_timer();)
   // the kernel that follows in the stream may start its own prologue now
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -202,9 +202,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
         tma_load_2d(smem_u32(base + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, tile * TC_BM);
       }
-      if (tracing) a.trace[1] = global_timer();
+      BN_TRACE_ONLY(if (tracing) a.trace[1] = global_timer();)
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      if (tracing) a.trace[2] = global_timer();
+      BN_TRACE_ONLY(if (tracing) a.trace[2] = global_timer();)
       bool failed = false;
       for (int i = 0; i < n_kb; ++i) {
         int s = i % TC_STAGES, round = i / TC_STAGES;
@@ -216,7 +216,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         tma_load_2d(dst + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, 0);
       }
-      if (tracing) a.trace[3] = global_timer();  // all loads issued
+      BN_TRACE_ONLY(if (tracing) a.trace[3] = global_timer();)  // all loads issued
       if (failed) s_failed = 1;
     }
   } else if (warp == 1) {
@@ -234,7 +234,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       }
       if (!failed) umma_commit(acc_bar);  // arrives when every MMA above is done
       if (failed) s_failed = 1;
-      if (tracing) a.trace[4] = global_timer();  // all MMAs issued
+      BN_TRACE_ONLY(if (tracing) a.trace[4] = global_timer();)  // all MMAs issued
     }
   } else {
     // ---- epilogue warps, part one: accumulator -> shared memory (TMEM lane quadrant warp % 4)
@@ -284,7 +284,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
     asm volatile("bar.sync 1, %0;" ::"n"(EPI) : "memory");
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tracing && tid == 64) a.trace[7] = global_timer();  // accumulator complete
+    BN_TRACE_ONLY(if (tracing && tid == 64) a.trace[7] = global_timer();)  // accumulator complete
     // with eight epilogue warps, warps 2-5 take the first half of the columns and 6-9 the second
     constexpr int COLS = MP * 128 / EPI;
     const int c0 = ((warp - 2) >> 2) * COLS;
@@ -469,7 +469,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         if (j >= gates) { j -= gates; ++mg; }
       }
     }
-    if (tracing && warp == 2 && lane == 0) a.trace[5] = global_timer();  // epilogue done
+    BN_TRACE_ONLY(if (tracing && warp == 2 && lane == 0) a.trace[5] = global_timer();)  // epilogue done
   }
 
   // No block reads another's shared memory, and every copy into this block has landed (the wait on
@@ -487,9 +487,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
-  if (tracing && tid == 32) a.trace[6] = global_timer();
+  BN_TRACE_ONLY(if (tracing && tid == 32) a.trace[6] = global_timer();)
 }
 
+#ifdef BN_TRACE
 // Debugging aid: bn_linear_tc_trace(n) makes the next n launches record timestamps of block 0
 // (device buffer allocated here; not used on the product path).
 static unsigned long long* g_trace = nullptr;
@@ -507,6 +508,7 @@ extern "C" int bn_linear_tc_trace_read(unsigned long long* host, int n) {
   if (!g_trace || n > g_trace_cap) return 1;
   return cudaMemcpy(host, g_trace, (size_t)n * 64, cudaMemcpyDeviceToHost) != cudaSuccess;
 }
+#endif
 
 static int sm_count() {
   static int n = 0;
@@ -616,8 +618,8 @@ extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_
   a.k_blocks = k_blocks; a.status = status;
   a.row_ss = row_ss; a.ss_parts = ss_parts; a.ss_stride = ss_stride; a.inv_width = inv_width; a.eps = eps;
   a.gain = gain; a.gain_dtype = gain_dtype; a.xg = (__nv_bfloat16*)xg; a.ss_out = ss_out; a.ss_out_stride = ss_out_stride;
-  a.trace = nullptr;
-  if (g_trace && g_trace_n < g_trace_cap) a.trace = g_trace + 8 * (g_trace_n++);
+  BN_TRACE_ONLY(a.trace = nullptr;)
+  BN_TRACE_ONLY(if (g_trace && g_trace_n < g_trace_cap) a.trace = g_trace + 8 * (g_trace_n++);)
   if (mp == 16) return launch_tc<16>(mw, mx, a, cluster, tiles, stream);
   if (mp == 32) return launch_tc<32>(mw, mx, a, cluster, tiles, stream);
   return launch_tc<64>(mw, mx, a, cluster, tiles, stream);

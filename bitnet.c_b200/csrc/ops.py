@@ -8,7 +8,6 @@ back to the CPU: tensors that are not on a CUDA device are refused.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Optional
 
@@ -464,7 +463,16 @@ MMA_MAX_ROWS = 64  # bfloat16: the streaming kernels (linear_tc.cu, linear_mma.c
 # product is faster beyond (5.5 against 5.8 ms for a decode step of 96 sequences at 32 layers of width 4096)
 TC_MAX_ROWS = MMA_MAX_ROWS
 USE_TCGEN05 = True  # small-batch bfloat16 products run on tcgen05 (linear_tc.cu); False: mma.sync (linear_mma.cu)
-N_SMS = 148
+_n_sms = {}
+
+
+def n_sms(device) -> int:
+    """Streaming multiprocessors of ``device`` (asked once)."""
+    key = torch.device(device).index or 0
+    if key not in _n_sms:
+        _n_sms[key] = int(torch.cuda.get_device_properties(key).multi_processor_count)
+    return _n_sms[key]
+
 
 
 _SCRATCH_FLOATS = 8 * 1024 * 1024  # 32 MB of split-K partial tiles, shared by all products of a device
@@ -482,10 +490,10 @@ def _split_scratch(device):
     return got
 
 
-def _mma_splits(M: int, N: int, K: int) -> int:
+def _mma_splits(M: int, N: int, K: int, sms: int) -> int:
     """How many ways the inner dimension is split so that about four blocks per SM stream weights."""
     blocks = (N + 63) // 64
-    want = 4 * N_SMS
+    want = 4 * sms
     if blocks >= want or blocks > _N_COUNTERS:
         return 1
     mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
@@ -559,8 +567,8 @@ class NormSink:
         self.residual, self.weight, self.eps = residual, weight, float(eps)
 
 
-USE_FUSED_NORM = not os.environ.get("BN_NO_FUSED_NORM")  # products of few rows add to the residual and prepare the
-# next norm in their epilogue (the variable switches it off for comparisons)
+USE_FUSED_NORM = True  # products of few rows add to the residual and prepare the next norm in their epilogue
+# (tests and comparisons set it to False)
 
 
 def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
@@ -656,7 +664,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
     if small:
         fn = _fn("linear_mma", "bn_linear_mma")
-        splits = _mma_splits(M, N, K)
+        splits = _mma_splits(M, N, K, n_sms(x.device))
         scratch, counters = _split_scratch(x.device)
         tail = (_ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters), c_int(counters.numel()), _stream())
         if swiglu:

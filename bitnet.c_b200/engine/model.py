@@ -152,8 +152,11 @@ class Model:
         """Raise if a kernel with bounded waits reported that a wait gave up since the last call
         (the results of that launch are not valid).  Synchronises with the device."""
         if self.device is not None and self.device.type == "cuda":
-            from ..csrc import ops
             ops.check_tc_status(self.device)
+            if self._bad_token is not None and int(self._bad_token.item()):
+                self._bad_token.zero_()
+                raise StepError("a token id outside the embedding table reached the device (its row was taken as "
+                                "zero); ids fed back on the device are not checked on the host")
 
     def check_step(self, cache: Cache, seqs: Sequence[SeqStep]) -> List[int]:
         if not seqs:
@@ -196,9 +199,14 @@ class Model:
             for s in reserved:  # give back what this step took
                 cache.unreserve(s.slot)
             raise
-        cache.sync()
-        ctx = pack_step(seqs, lengths, self.device)
-        logits = self.forward(cache, ctx)
+        try:
+            cache.sync()
+            ctx = pack_step(seqs, lengths, self.device)
+            logits = self.forward(cache, ctx)
+        except BaseException:
+            for s in seqs:  # the step did not happen: its pages go back, the lengths stay
+                cache.unreserve(s.slot)
+            raise
         for s in seqs:
             cache.advance(s.slot, len(s.tokens))
         return logits

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import json
 import os
+import warnings
 from typing import Callable, Dict, List, Mapping
 
 import torch
@@ -53,6 +54,10 @@ def _open_files(model_dir: str) -> List[SafetensorsFile]:
         shards = sorted(set(weight_map.values()))
         if not shards:
             raise WeightsError(model_dir, [], [], [], [f"'{index}' names no shard"])
+        absent = [s for s in shards if not os.path.isfile(os.path.join(model_dir, s))]
+        if absent:
+            raise WeightsError(model_dir, [], [], [], [f"'{index}' names shards that are not in the folder: "
+                                                       + ", ".join(absent)])
         return [SafetensorsFile(os.path.join(model_dir, s)) for s in shards]
     raise WeightsError(model_dir, [], [], [], ["no model.safetensors and no model.safetensors.index.json"])
 
@@ -102,10 +107,18 @@ def load_weights(model_dir: str, table: Mapping[str, "ParamSpec"], tensor_name: 
         if missing or unexpected or mismatched or dup:
             raise WeightsError(model_dir, missing, unexpected, mismatched, dup)
         out: Dict[str, torch.Tensor] = {}
+        wide: List[str] = []
         for n, path in wanted.items():
             t = where[n].read(n)
             keep = stored_dtype_to_kept(t.dtype, dtype, bool(table[path].integer))
+            if keep == torch.float32 and dtype == torch.bfloat16 and t.dim() >= 2:
+                wide.append(n)
             out[path] = t.to(device=device, dtype=keep).contiguous()
+        if wide:
+            # a tensor stored in 32-bit stays 32-bit; say what that costs instead of doing it silently
+            warnings.warn(f"'{model_dir}': {len(wide)} matrices are stored in 32-bit floating point and are kept so "
+                          f"in this bfloat16 model (first: {wide[0]}): they take twice the memory and their products "
+                          "run in float32 on the slower kernels; store them in bfloat16 to avoid that", stacklevel=2)
         return out
     finally:
         for f in files:

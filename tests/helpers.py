@@ -119,7 +119,7 @@ def trace_chunks(reqs: Dict[str, List[int]], pieces: Sequence[int] = (1, 7, 64, 
     at = {r: 0 for r in ids}
     steps, n = [], 0
     while any(at[r] < len(reqs[r]) for r in ids):
-        st = {"step": n, "entries": [], "end": []}
+        st = {"step": len(steps), "entries": [], "end": []}
         for i, r in enumerate(ids):
             if n < i * stagger or at[r] >= len(reqs[r]):
                 continue
@@ -128,7 +128,8 @@ def trace_chunks(reqs: Dict[str, List[int]], pieces: Sequence[int] = (1, 7, 64, 
             at[r] += len(toks)
             if at[r] >= len(reqs[r]):
                 st["end"].append(r)
-        steps.append(st)
+        if st["entries"]:  # nobody may be live between one request's end and the next one's start
+            steps.append(st)
         n += 1
     return steps
 

@@ -44,7 +44,7 @@ def test_spec_is_built_layer_by_layer():
     ("head_dim", 24, "multiple of 16"), ("head_dim", 512, "at most 256"), ("hidden_size", 60, "multiple of 8"),
     ("hidden_act", "gelu", "silu"), ("rope_scaling", {"rope_type": "llama3", "factor": 8.0}, "rope_scaling"),
     ("attention_bias", True, "attention_bias"), ("vocab_size", "256", "integer"), ("rms_norm_eps", -1.0, "positive"),
-    ("eos_token_id", 999, "outside"),
+    ("eos_token_id", 999, "outside"), ("sliding_window", 4096, "sliding_window"),
 ])
 def test_refusals_name_the_key(key, value, needle):
     d = dict(TINY_A)

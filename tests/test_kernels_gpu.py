@@ -268,8 +268,12 @@ def test_repeat_penalty(cuda_device):
 
 @pytest.mark.parametrize("M,N,K", [(1, 64, 128), (3, 50, 72), (8, 333, 4096), (9, 1000, 200), (16, 64, 1000),
                                    (33, 130, 264), (64, 272, 2048)])
-def test_linear_mma_store_and_partials(cuda_device, M, N, K):
-    """The tensor-core small-batch product: every row count up to 64, sizes that are no multiple of its tiles."""
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+def test_linear_small_batch_store_and_partials(cuda_device, monkeypatch, impl, M, N, K):
+    """The tensor-core small-batch products (tcgen05 in linear_tc.cu; mma.sync in linear_mma.cu, the
+    second implementation, reached with ``ops.USE_TCGEN05`` off): every row count up to 64, sizes
+    that are no multiple of their tiles."""
+    monkeypatch.setattr(ops, "USE_TCGEN05", impl == "tcgen05")
     g = torch.Generator().manual_seed(12)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(cuda_device)
@@ -295,7 +299,9 @@ def test_linear_mma_store_and_partials(cuda_device, M, N, K):
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 16, 64), (8, 176, 64), (20, 200, 120), (64, 256, 96)])
-def test_linear_mma_swiglu_epilogue(cuda_device, M, I, K):
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+def test_linear_small_batch_swiglu_epilogue(cuda_device, monkeypatch, impl, M, I, K):
+    monkeypatch.setattr(ops, "USE_TCGEN05", impl == "tcgen05")
     g = torch.Generator().manual_seed(13)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
     gate = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16).to(cuda_device)

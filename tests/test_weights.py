@@ -53,6 +53,11 @@ def test_a_tensor_stored_in_32_bit_stays_32_bit(tmp_path):
     assert w["final_norm.weight"].dtype == torch.float32 and w["blocks.0.mixer.q"].dtype == torch.bfloat16
     rewrite(d, lambda t: t.update({"model.norm.weight": t["model.norm.weight"].half()}))
     assert load(d, TINY_A)["final_norm.weight"].dtype == torch.bfloat16
+    # a whole file in 32-bit loaded as a bfloat16 model: kept, and said so
+    d32 = write_random_model(str(tmp_path / "m32"), TINY_A, seed=5, dtype="float32")
+    with pytest.warns(UserWarning, match="stored in 32-bit"):
+        w32 = load(d32, TINY_A)
+    assert all(t.dtype == torch.float32 for t in w32.values())
 
 
 def test_same_seed_same_bytes_other_seed_other_bytes(tmp_path):
@@ -157,3 +162,7 @@ def test_sharded_folder(tmp_path):
         json.dump({"weight_map": wm}, f)
     w = load(d, TINY_A)
     assert torch.equal(w["embedding.table"], tensors["model.embed_tokens.weight"])
+    # a shard that the index names and the folder lacks is a weights error that names it
+    os.remove(os.path.join(d, "model-00002-of-00002.safetensors"))
+    with pytest.raises(WeightsError, match="model-00002-of-00002.safetensors"):
+        load(d, TINY_A)

@@ -4,9 +4,9 @@ its exported symbol ``bn_argmax_noalloc``, with nothing but device pointers and 
 It is for callers that may not allocate device memory (a host program that owns the whole device
 through its own arena, a serving loop that has promised to make no allocator calls once it runs,
 a C caller without a tensor library): the scratch that the normal argmax gets from its caller lives
-in a fixed array inside the library.  The test compares it with the normal entry point on two
-calls in a row (the second finds the scratch as the first left it), at the row limit, and checks
-that more rows than the limit are refused.  This file sorts last on purpose, so that a run that
+in a fixed array inside the library.  The test compares it with the normal entry point and with
+NumPy's first maximum on calls in a row (each finds the scratch as the one before left it), at
+the row limit, and checks that more rows than the limit are refused.  This file sorts last on purpose, so that a run that
 stops at the first failure has run every other test before it.
 """
 import ctypes
@@ -49,6 +49,7 @@ def test_matches_the_normal_entry_point_on_two_calls_in_a_row(cuda_device):
         want = ops.argmax(logits)
         torch.cuda.synchronize()
         assert torch.equal(out, want)
+        assert out.cpu().numpy().tolist() == logits.cpu().numpy().argmax(1).tolist()  # NumPy: the first maximum
     assert out[0].item() == 77
 
 
@@ -60,3 +61,7 @@ def test_more_rows_than_the_limit_are_refused(cuda_device):
     torch.cuda.synchronize()
     assert (out == -1).all()  # nothing ran
     assert fn(None, 16, 1, 16, out.data_ptr(), None) == 1  # a null pointer is a bad argument
+    # and the refusals left the context usable
+    assert call(fn, logits[:3], out[:3]) == 0
+    torch.cuda.synchronize()
+    assert (out[:3] == 0).all()
