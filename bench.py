@@ -6,11 +6,17 @@
 Default workload: the layer sizes of Llama-3.1-8B with random weights (bfloat16), a batch of 8
 sequences with 512-token prompts in a cache sized for a context of 4096, K decode steps.
 Prints ONE JSON line.  ``value`` is decoded tokens per second, timed on the device with CUDA
-events; ``e2e`` is the same through the public Python entry point with host token ids in and
-out every step.  The line also carries the prefill of one 2,048-token prompt, the decode step's
-roofline fraction against the measured HBM bandwidth, and decode at batch 1 and 64.
+events; ``e2e`` is the same loop by the wall clock, through the public Python entry point with
+host token ids in and out every step.  The line also carries the mean and the median step, the
+prefill of one 2,048-token prompt, the decode step's roofline fraction against the measured HBM
+bandwidth, and further points: decode at batch 1 and 64, decode after prompts of 2,048 and 3,900
+tokens, the true 32-bit path (decode and prefill at a stated number of layers), and the
+generation workloads of the 1B and 13B size sets.
 A step reads all 15 GB of weights, far more than the 126 MB L2, so no L2 flush is needed
 between timed iterations (``config.l2`` says so).
+
+``--impl reference`` measures artalis-io/bitnet.c itself (unmodified, built from baseline/_ref with
+its own Makefile) on the same sizes through baseline/ref_harness.c.
 """
 import argparse
 import json
@@ -42,6 +48,7 @@ LLAMA_13B = {
     "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
 }
 PROMPT_LEN = 512
+FP32_LAYERS = 8  # layers of the float32 points (the sizes of each layer are the full ones)
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -252,7 +259,7 @@ def decode_read_bytes(model, cfg, batch, context_len):
     emb = model.embedding.numel() * model.embedding.element_size()
     w = weight_bytes(model) - (emb if model.head is not model.embedding else 0)
     w += batch * cfg["hidden_size"] * model.embedding.element_size() if model.head is not model.embedding else 0
-    kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * model.embedding.element_size()
     return w + batch * context_len * kv_per_token
 
 
@@ -264,8 +271,13 @@ def prefill_flops(cfg, T):
     return L * (per_layer + attn) + 2 * V * d
 
 
-def run_decode(bn, model, cfg, batch, steps, warmup, e2e=False, clock=None):
-    """Prefill ``batch`` prompts of PROMPT_LEN tokens, then time ``steps`` decode steps."""
+def run_decode(model, cfg, batch, steps, warmup, prompt_len=PROMPT_LEN, clock=None):
+    """Prefill ``batch`` prompts of ``prompt_len`` tokens, then time ``steps`` decode steps through
+    the public engine: every step's token ids go in from the host (copied from pinned memory even
+    where the device already holds them from its own sampling, which the library would skip) and
+    the sampled ids come back to the host.  One loop, two clocks: CUDA events around the steps
+    (device time) and the wall clock around the same steps (end to end); an event between steps
+    gives the per-step times."""
     import torch
     from bitnet_c_b200.engine import ModelEngine
     from bitnet_c_b200.engine.batch import SeqStep
@@ -273,19 +285,18 @@ def run_decode(bn, model, cfg, batch, steps, warmup, e2e=False, clock=None):
     from bitnet_c_b200.csrc import ops
 
     g = torch.Generator().manual_seed(1234 + batch)
-    prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
+    prompts = torch.randint(0, cfg["vocab_size"], (batch, prompt_len), generator=g).tolist()
     cache = model.new_cache(max_tokens=batch * cfg["max_position_embeddings"], max_seqs=batch)
-    # the end-to-end run copies every step's inputs from pinned host memory, also when the device
-    # already holds the same ids from its own sampling (the library would skip that copy)
-    eng = ModelEngine(model, cache, SamplingParams(temperature=0.0), always_upload=e2e)
+    eng = ModelEngine(model, cache, SamplingParams(temperature=0.0), always_upload=True)
     eng.start_batch(0, prompts)
     slots = [eng.open() for _ in range(batch)]
     rows = list(range(batch))
-    # prompts in groups of 8 so that the activations of 64 x 512 tokens need not live at once
+    # prompts in groups so that the activations of many long prompts need not live at once
+    group = max(1, 4096 // prompt_len)
     toks = []
-    for a in range(0, batch, 8):
-        idx = list(range(a, min(batch, a + 8)))
-        toks += eng.step_and_sample([SeqStep(slots[i], prompts[i], [PROMPT_LEN - 1]) for i in idx], idx)
+    for a in range(0, batch, group):
+        idx = list(range(a, min(batch, a + group)))
+        toks += eng.step_and_sample([SeqStep(slots[i], prompts[i], [prompt_len - 1]) for i in idx], idx)
 
     def one_step(t):
         return eng.step_and_sample([SeqStep(slots[i], [t[i]], [0]) for i in range(batch)], rows)
@@ -297,27 +308,29 @@ def run_decode(bn, model, cfg, batch, steps, warmup, e2e=False, clock=None):
     h2d_before = eng.h2d_bytes()
     if clock is not None:
         clock.start()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     t0 = time.perf_counter()
-    start.record()
-    for _ in range(steps):
+    marks[0].record()
+    for i in range(steps):
         toks = one_step(toks)
-    end.record()
+        marks[i + 1].record()
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
-    dev_ms = start.elapsed_time(end)
+    dev_ms = marks[0].elapsed_time(marks[-1])
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
     clocks = clock.stop() if clock is not None else None
     launches = ops.LAUNCHES
-    ctx_len = PROMPT_LEN + warmup + steps // 2
+    ctx_len = prompt_len + warmup + steps // 2
+    h2d = (eng.h2d_bytes() - h2d_before) // max(1, steps)
     for s in slots:
         eng.close(s)
-    del cache
+    del cache, eng
     torch.cuda.empty_cache()
-    return {"dev_ms": dev_ms, "wall_ms": wall_ms, "launches": launches, "clocks": clocks, "context": ctx_len,
-            "h2d": (eng.h2d_bytes() - h2d_before) // max(1, steps), "d2h": 4 * batch}
+    return {"dev_ms": dev_ms, "wall_ms": wall_ms, "median_ms": per_step[len(per_step) // 2], "launches": launches,
+            "clocks": clocks, "context": ctx_len, "h2d": h2d, "d2h": 4 * batch}
 
 
-def run_prefill(bn, model, cfg, warmup=3, iters=5):
+def run_prefill(model, cfg, warmup=3, iters=5):
     import torch
     from bitnet_c_b200.engine.batch import SeqStep
     g = torch.Generator().manual_seed(99)
@@ -341,42 +354,53 @@ def run_prefill(bn, model, cfg, warmup=3, iters=5):
     return times[len(times) // 2]
 
 
-def run_workload(name):
+WORKLOADS = {
+    # name: (configuration, prompt lengths or None for 64 drawn from 1..2,048, new tokens per request)
+    "1b": (LLAMA_1B, None, 256),
+    "13b": (LLAMA_13B, [2048, 1024, 512, 256, 128, 64, 16, 1], 1024),
+}
+
+
+def run_workload(name, repeats=2):
     """The generation workloads of the two other size sets, through the Python entry point:
     1b: 64 requests with prompts of 1 to 2,048 tokens (one ragged prefill step), 256 greedy tokens
-    each; 13b: 8 requests with prompts of 2,048 down to 1 tokens, 1,024 greedy tokens each."""
+    each; 13b: 8 requests with prompts of 2,048 down to 1 tokens, 1,024 greedy tokens each.  The
+    first run warms libraries, recorded steps and memory pools; the fastest of the others counts."""
     import torch
     import bitnet_c_b200 as bn
     from bitnet_c_b200.engine import Model
-    cfg = dict(LLAMA_1B if name == "1b" else LLAMA_13B)
+    base, lens, new = WORKLOADS[name]
+    cfg = dict(base)
     g = torch.Generator().manual_seed(7)
-    if name == "1b":
+    if lens is None:
         lens = torch.randint(1, 2049, (64,), generator=g).tolist()
-        new = 256
-    else:
-        lens = [2048, 1024, 512, 256, 128, 64, 16, 1]
-        new = 1024
     prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
     times = []
-    for _ in range(3):  # the first run warms libraries and memory pools; the faster of the next two counts
+    for _ in range(1 + repeats):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         out = bn.generate(model, prompts, max_new_tokens=new, temperature=0.0, stop_ids=[])
         torch.cuda.synchronize()
         times.append(time.perf_counter() - t0)
     made = sum(len(c.tokens) for c in out)
-    print(json.dumps({"metric": f"generated tokens/s, {name} workload (prefill of {sum(lens)} prompt tokens included)",
-                      "value": round(made / min(times[1:]), 1), "unit": "tokens/s", "seconds": round(min(times[1:]), 3),
-                      "seconds_all": [round(t, 3) for t in times],
-                      "generated": made, "prompt_tokens": sum(lens), "requests": len(lens), "dtype": "bf16",
-                      "data": "synthetic", "impl": "ours",
-                      "config": {"model": f"llama-{name}-sizes-random", "layers": cfg["num_hidden_layers"],
-                                 "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
-                                 "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                                 "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                                 "seq_len": cfg["max_position_embeddings"], "new_tokens": new}}))
-    return 0
+    # what the decode steps alone had to read, at the batch's mean length over the run
+    kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    mean_live = sum(lens) + len(lens) * new / 2
+    step_bytes = weight_bytes(model) - (0 if model.head is model.embedding else model.embedding.numel() * 2) + mean_live * kv_per_token
+    del model
+    torch.cuda.empty_cache()
+    best = min(times[1:])
+    return {"metric": f"generated tokens/s, {name} workload (prefill of {sum(lens)} prompt tokens included)",
+            "value": round(made / best, 1), "unit": "tokens/s", "seconds": round(best, 3),
+            "seconds_all": [round(t, 3) for t in times], "generated": made, "prompt_tokens": sum(lens),
+            "requests": len(lens), "decode_step_gb": round(step_bytes / 1e9, 2), "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": f"llama-{name}-sizes-random", "layers": cfg["num_hidden_layers"],
+                       "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                       "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                       "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                       "seq_len": cfg["max_position_embeddings"], "new_tokens": new}}
 
 
 def main():
@@ -386,10 +410,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
-    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64 and the prefill (quick runs)")
+    ap.add_argument("--skip-points", action="store_true", help="only the main decode run (quick runs, profiling)")
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill and print its record (profiling)")
     ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
-    ap.add_argument("--workload", choices=["1b", "13b"], help="run the generation workload of another size set instead")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run the generation workload of another size set instead")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -397,11 +421,11 @@ def main():
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.workload:
-        return run_workload(args.workload)
+        print(json.dumps(run_workload(args.workload)))
+        return 0
     warmup = max(3, args.warmup)
 
     import torch
-    import bitnet_c_b200 as bn
     from bitnet_c_b200.engine import Model
 
     cfg = dict(LLAMA_8B)
@@ -411,28 +435,31 @@ def main():
     pk = peaks()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
 
+    def prefill_record(m, c, ms, peak_tflops):
+        fl = prefill_flops(c, PREFILL_TOKENS)
+        return {"value": round(PREFILL_TOKENS / (ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
+                "frac": round(fl / (ms / 1e3) / (peak_tflops * 1e12), 4)}
+
     if args.only_prefill:
-        pre_ms = run_prefill(bn, model, cfg, warmup=2, iters=3)
-        fl = prefill_flops(cfg, PREFILL_TOKENS)
-        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
-                                      "ms": round(pre_ms, 3), "layers": cfg["num_hidden_layers"],
-                                      "frac": round(fl / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        rec = prefill_record(model, cfg, run_prefill(model, cfg, warmup=2, iters=3), pk["bf16_tflops"])
+        rec["layers"] = cfg["num_hidden_layers"]
+        print(json.dumps({"prefill": rec}))
         return 0
     B = args.batch
     # the prefill first: it is a burst of matrix products of a seventh of a second, and what it is
     # compared with is the burst peak; after seconds of decoding the GPU sits at its power cap
-    pre_ms = None if args.skip_points else run_prefill(bn, model, cfg)
-    e2e_run = run_decode(bn, model, cfg, B, args.steps, warmup, e2e=True)
-    e2e_value = B * args.steps / (e2e_run["wall_ms"] / 1e3)
-    main_run = run_decode(bn, model, cfg, B, args.steps, warmup, clock=ClockSampler())
-    ms_per_step = main_run["dev_ms"] / args.steps
-    value = B * args.steps / (main_run["dev_ms"] / 1e3)
-    read_bytes = decode_read_bytes(model, cfg, B, main_run["context"])
+    pre_ms = None if args.skip_points else run_prefill(model, cfg)
+    run = run_decode(model, cfg, B, args.steps, warmup, clock=ClockSampler())
+    ms_per_step = run["dev_ms"] / args.steps
+    value = B * args.steps / (run["dev_ms"] / 1e3)
+    e2e_value = B * args.steps / (run["wall_ms"] / 1e3)
+    read_bytes = decode_read_bytes(model, cfg, B, run["context"])
     achieved = read_bytes / (ms_per_step / 1e3) / 1e9
 
     out = {
         "metric": f"decode tokens/s at batch {B} (Llama-3.1-8B sizes, bf16)", "value": round(value, 2), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
+        "ms_per_step_median": round(run["median_ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {"model": "llama-3.1-8b-sizes-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
@@ -441,23 +468,49 @@ def main():
                    "global_batch": B, "seq_len": cfg["max_position_embeddings"], "prompt_len": PROMPT_LEN,
                    "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied": False,
                    "parallelism": "single-gpu", "l2": "inputs larger than L2 (15 GB of weights per step)",
-                   "peaks": pk["source"]},
-        "clocks": main_run["clocks"],
-        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": e2e_run["h2d"],
-                "d2h_bytes_per_step": e2e_run["d2h"]},
-        "gpu_launches": main_run["launches"],
+                   "peaks": pk["source"], "fp32_layers": FP32_LAYERS,
+                   "timing": "one loop: value by CUDA events around its steps, e2e by the wall clock around the same steps"},
+        "clocks": run["clocks"],
+        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": run["h2d"],
+                "d2h_bytes_per_step": run["d2h"]},
+        "gpu_launches": run["launches"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
     }
     if not args.skip_points:
-        fl = prefill_flops(cfg, PREFILL_TOKENS)
-        out["prefill"] = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
-                          "ms": round(pre_ms, 3), "frac": round(fl / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-        points = {}
+        out["prefill"] = prefill_record(model, cfg, pre_ms, pk["bf16_tflops"])
+        points, fracs = {}, {}
+        short = min(args.steps, 32)  # the further points take fewer steps each
+
+        def point(name, m, c, b, steps, prompt_len):
+            r = run_decode(m, c, b, steps, warmup, prompt_len=prompt_len)
+            points[name] = round(b * steps / (r["dev_ms"] / 1e3), 2)
+            fracs[name] = round(decode_read_bytes(m, c, b, r["context"]) / (r["dev_ms"] / steps / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
         for b in (1, 64):
-            r = run_decode(bn, model, cfg, b, args.steps, warmup)
-            points[f"decode_b{b}"] = round(b * args.steps / (r["dev_ms"] / 1e3), 2)
+            point(f"decode_b{b}", model, cfg, b, args.steps, PROMPT_LEN)
+        for ctx in (2048, 3900):  # longer contexts: the cache of the live requests becomes the larger part
+            for b in (1, 8, 64):
+                point(f"decode_b{b}_ctx{ctx}", model, cfg, b, short, ctx)
+        del model
+        torch.cuda.empty_cache()
+        # the true 32-bit path at the same layer sizes, FP32_LAYERS of the layers (named in config)
+        cfg32 = dict(cfg, num_hidden_layers=min(FP32_LAYERS, cfg["num_hidden_layers"]))
+        torch.backends.cuda.matmul.allow_tf32 = False
+        m32 = Model.from_random(cfg32, seed=0, dtype="float32", device="cuda:0", norm_std=0.0)
+        point("decode_b8_fp32", m32, cfg32, 8, short, PROMPT_LEN)
+        p32 = run_prefill(m32, cfg32, warmup=1, iters=3)
+        out["prefill_fp32"] = {"value": round(PREFILL_TOKENS / (p32 / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(p32, 3),
+                               "layers": cfg32["num_hidden_layers"]}
+        del m32
+        torch.cuda.empty_cache()
+        for name in sorted(WORKLOADS):
+            w = run_workload(name, repeats=1)
+            points[f"workload_{name}"] = w["value"]
+            out[f"workload_{name}"] = {"seconds": w["seconds"], "generated": w["generated"], "prompt_tokens": w["prompt_tokens"],
+                                       "requests": w["requests"], "decode_step_gb": w["decode_step_gb"]}
         out["points"] = points
+        out["points_frac"] = fracs
     print(json.dumps(out))
     return 0
 

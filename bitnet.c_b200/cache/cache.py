@@ -4,7 +4,8 @@ Every schedule entry whose mixer asks for cached keys and values gets a plane of
 the *group* of all entries with the same request (heads, head size, window).  A group has its
 own storage, page pool and page table, so runs with different needs never share memory:
 
-    k, v          [entries, pages, kv_heads, 64, head_dim]   compute type
+    k             [entries, pages, kv_heads, 64, head_dim]   compute type
+    v             [entries, pages, kv_heads, 64, v_head_dim] (a value head may be narrower or wider than a key head)
     page_table    [slots, pages_per_sequence]  int32, on the device and mirrored on the host
 
 A sequence lives in a *slot* from its first token to its end and holds, in each group, the
@@ -33,18 +34,32 @@ class KvView:
     """What a mixer sees of the cache for one run."""
 
     k: torch.Tensor  # [pages, kv_heads, PAGE, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor  # [pages, kv_heads, PAGE, v_head_dim]
     page_table: torch.Tensor  # [slots, pages_per_sequence] int32
     n_kv_heads: int
     head_dim: int
     window: int
     owner: bool  # False: this run reads another run's plane and must not write
+    v_head_dim: int = 0  # 0: as head_dim
+
+    @property
+    def v_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
     def append(self, x: torch.Tensor, k_off: int, v_off: int, ctx) -> None:
         """Write the key heads at ``k_off`` and value heads at ``v_off`` of each row of x."""
         from ..csrc import ops
         if not self.owner:
             raise CacheError("a run that reads another run's cache must not write it")
+        if self.v_dim != self.head_dim:
+            # values of another width than keys: the append kernel takes one width, so the rows are
+            # placed by index (page and row of every token from the device arrays of the step)
+            n = ctx.n_tokens
+            page = self.page_table[ctx.slots[ctx.tok_seq.long()].long(), (ctx.tok_pos // PAGE).long()].long()
+            row = (ctx.tok_pos % PAGE).long()
+            self.k[page, :, row] = x[:n, k_off:k_off + self.n_kv_heads * self.head_dim].reshape(n, self.n_kv_heads, self.head_dim)
+            self.v[page, :, row] = x[:n, v_off:v_off + self.n_kv_heads * self.v_dim].reshape(n, self.n_kv_heads, self.v_dim)
+            return
         ops.rope_append(x, 0, self.head_dim, 0, 1.0, ctx.tok_pos, k_off=k_off, v_off=v_off,
                         n_kv_heads=self.n_kv_heads, tok_seq=ctx.tok_seq, slots=ctx.slots,
                         page_table=self.page_table, k_cache=self.k, v_cache=self.v)
@@ -65,13 +80,13 @@ class KvGroup:
         shape = (len(entries), n_pages, request.n_kv_heads, PAGE, request.head_dim)
         if allocate:
             self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            self.v = torch.zeros(shape[:-1] + (request.v_dim,), dtype=dtype, device=device)
             self.page_table = torch.zeros((n_slots, pages_per_seq), dtype=torch.int32, device=device)
         else:  # bookkeeping only (tests without a device)
             self.k = self.v = self.page_table = None
 
     def bytes_per_token(self, itemsize: int) -> int:
-        return 2 * len(self.entries) * self.request.n_kv_heads * self.request.head_dim * itemsize
+        return len(self.entries) * self.request.n_kv_heads * (self.request.head_dim + self.request.v_dim) * itemsize
 
     def reserve(self, slot: int, old_len: int, new_len: int) -> None:
         """Hold pages for positions [first needed, new_len)."""
@@ -151,9 +166,9 @@ class Cache:
             if src not in self._plane:
                 raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which has none")
             a, b = kv_requests[i], kv_requests[src]
-            if a is not None and (a.n_kv_heads, a.head_dim) != (b.n_kv_heads, b.head_dim):
+            if a is not None and (a.n_kv_heads, a.head_dim, a.v_dim) != (b.n_kv_heads, b.head_dim, b.v_dim):
                 raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache: "
-                                 f"{a.n_kv_heads}x{a.head_dim} against {b.n_kv_heads}x{b.head_dim}")
+                                 f"{a.n_kv_heads}x{a.head_dim}/{a.v_dim} against {b.n_kv_heads}x{b.head_dim}/{b.v_dim}")
             self._reader[i] = src
         self.states: Dict[int, torch.Tensor] = {}
         self.state_requests = {i: r for i, r in enumerate(state_requests) if r is not None}
@@ -231,7 +246,8 @@ class Cache:
         gi, plane = self._plane[src]
         g = self.groups[gi]
         return KvView(k=g.k[plane], v=g.v[plane], page_table=g.page_table, n_kv_heads=g.request.n_kv_heads,
-                      head_dim=g.request.head_dim, window=g.request.window, owner=owner)
+                      head_dim=g.request.head_dim, window=g.request.window, owner=owner,
+                      v_head_dim=g.request.v_head_dim)
 
     def state(self, entry: int) -> Optional[torch.Tensor]:
         return self.states.get(entry)

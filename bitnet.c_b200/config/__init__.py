@@ -1,5 +1,5 @@
 """Typed configuration, the block-by-block model description, and the architecture registry."""
-from .spec import (AttentionSpec, BlockSpec, ConfigError, GatedMlpSpec, ModelSpec, NoPositionSpec,
+from .spec import (AttentionSpec, BlockSpec, ConfigError, GatedMlpSpec, LinearHeadSpec, ModelSpec, NoPositionSpec,
                    RmsNormSpec, RotarySpec, ScheduleEntry)
 from .registry import (Architecture, architecture, architecture_of, known_architectures,
                        read_config_json, register_architecture, unregister_architecture)
@@ -16,7 +16,7 @@ register_architecture(Architecture(
 ))
 
 __all__ = [
-    "AttentionSpec", "BlockSpec", "ConfigError", "GatedMlpSpec", "ModelSpec", "NoPositionSpec",
+    "AttentionSpec", "BlockSpec", "ConfigError", "GatedMlpSpec", "LinearHeadSpec", "ModelSpec", "NoPositionSpec",
     "RmsNormSpec", "RotarySpec", "ScheduleEntry", "Architecture", "architecture", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "unregister_architecture",
     "LlamaConfig",

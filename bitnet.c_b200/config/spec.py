@@ -97,6 +97,17 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class LinearHeadSpec:
+    """The output head: logits = scale * (W h), then optionally ``softcap * tanh(logits / softcap)``
+    (the reference's final soft-cap, src/transformer/logits.c:325-333; 0 means none).  W is the
+    head matrix, or the embedding table when the embeddings are tied."""
+
+    scale: float = 1.0
+    softcap: float = 0.0
+    kind: str = "linear"
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a block.
 
@@ -121,6 +132,7 @@ class ModelSpec:
     tie_embeddings: bool = False
     embedding_scale: float = 1.0
     stop_ids: Tuple[int, ...] = field(default_factory=tuple)
+    head: Any = field(default_factory=LinearHeadSpec)  # a head spec; its part turns normed rows into logits
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.width <= 0 or self.max_positions <= 0:

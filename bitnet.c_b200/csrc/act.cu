@@ -61,3 +61,23 @@ extern "C" int bn_silu_mul(const void* h, void* out, int dtype, int n_rows, int 
     return BN_ERR_BAD_ARG;
   return BN_OK;
 }
+
+// x = x * scale, then (cap != 0) x = tanhf(x / cap) * cap: an output head's logit scale and the
+// reference's final soft-cap (src/transformer/logits.c:325-333), float32 in place.
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t n, float scale, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = x[i] * scale;
+  if (cap != 0.0f) v = tanhf(v * (1.0f / cap)) * cap;
+  x[i] = v;
+}
+
+extern "C" int bn_scale_softcap(float* x, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return BN_OK;
+  if (!x) return BN_ERR_BAD_ARG;
+  unsigned blocks = (unsigned)(((size_t)n + 255) / 256);
+  BN_LAUNCH(scale_softcap_kernel, blocks, 256, 0, stream, x, (size_t)n, scale, cap);
+  return BN_OK;
+}

@@ -145,6 +145,14 @@ def silu_mul(h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def scale_softcap(x: torch.Tensor, scale: float, softcap: float) -> torch.Tensor:
+    """In place on float32 x: x * scale, then softcap * tanh(x / softcap) when softcap is not 0."""
+    _need(x, "x", torch.float32)
+    _check(_fn("act", "bn_scale_softcap")(_ptr(x), ctypes.c_longlong(x.numel()), c_float(scale), c_float(softcap),
+                                          _stream()), "scale_softcap")
+    return x
+
+
 # ---- rotary + cache append ----------------------------------------------------------------
 def rope_append(x: torch.Tensor, n_rot_heads: int, head_dim: int, rotary_dims: int, theta_scale: float,
                 tok_pos: torch.Tensor, *, k_off: int = 0, v_off: int = 0, n_kv_heads: int = 0,

@@ -53,6 +53,7 @@ class Model:
         b = BuildContext(dtype=self.dtype, device=self.device)
         self.blocks = [build_part("block", bs, b) for bs in spec.blocks]
         self.final_norm = build_part("norm", spec.final_norm, b)
+        self.head_part = build_part("head", spec.head, b)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self._bad_token: Optional[torch.Tensor] = None
@@ -60,6 +61,9 @@ class Model:
         for i, blk in enumerate(self.blocks):
             _walk(f"blocks.{i}", blk, self._owners)
         _walk("final_norm", self.final_norm, self._owners)
+        _walk("head", self.head_part, self._owners)  # a head's own parameters; the matrix is "head.weight"
+        if "head.weight" in self._owners:
+            raise ConfigError("a head part must not name a parameter 'weight': 'head.weight' is the head matrix")
 
     # ---- parameters -----------------------------------------------------------------------
     def parameter_table(self) -> Dict[str, ParamSpec]:
@@ -76,7 +80,7 @@ class Model:
         be recorded once and replayed (parts say so with ``graph_safe = True``)."""
         def ok(part) -> bool:
             return bool(getattr(part, "graph_safe", False)) and all(ok(c) for c in part.children().values())
-        return all(ok(b) for b in self.blocks) and ok(self.final_norm)
+        return all(ok(b) for b in self.blocks) and ok(self.final_norm) and ok(self.head_part)
 
     def decode_blocks_per_sequence(self) -> int:
         """The most thread blocks any part launches per sequence in a decode step (0: no part takes
@@ -88,11 +92,17 @@ class Model:
         for blk in self.blocks:
             fams.extend(blk.all_kernels())
         fams.extend(self.final_norm.all_kernels())
+        fams.extend(self.head_part.all_kernels())
         return list(dict.fromkeys(fams))
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> "Model":
-        """Hand every parameter to the part that owns it.  ``tensors`` maps paths to device tensors."""
+        """Hand every parameter to the part that owns it.  ``tensors`` maps paths to device tensors
+        (None, or no entry, for an optional parameter that the model does not have)."""
         table = self.parameter_table()
+        tensors = dict(tensors)
+        for path, p in table.items():
+            if p.optional:
+                tensors.setdefault(path, None)
         missing = sorted(set(table) - set(tensors))
         extra = sorted(set(tensors) - set(table))
         if missing or extra:
@@ -236,7 +246,7 @@ class Model:
             h = pending.value
         else:
             h = self.final_norm.add_norm(x, pending, ctx, rows=ctx.rows)
-        return ops.linear(h, self.head, out_dtype=torch.float32)
+        return self.head_part.forward(h, self.head, ctx)
 
 
 def require_cuda(device) -> None:

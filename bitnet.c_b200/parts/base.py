@@ -24,6 +24,10 @@ FeedForward    ``forward(h, ctx) -> delta [T, width]``.
 Block          ``forward(x, pending, ctx, kv, state) -> pending``: runs its parts on the residual
                x; ``pending`` is a delta not yet added to x (added by the next norm, which
                saves one pass over the residual).
+Head           ``forward(h, table, ctx) -> logits``: h are the final norm's rows (a tensor or
+               ``ops.RowScaled``), ``table`` the head matrix ``[vocab, width]`` (the embedding
+               table when tied); float32 logits ``[rows, vocab]``.  Parameters of its own (a
+               bias, say) are declared like any part's and live under ``head.<name>``.
 """
 from __future__ import annotations
 
@@ -40,6 +44,9 @@ class ParamSpec:
     shape: Tuple[int, ...]
     init: str = "normal"  # "normal": N(0, std) matrix; "ones": gain around 1; "zeros"
     integer: bool = False
+    # a tensor the file may lack (a bias, an extra norm): the part is then bound with None for it,
+    # as the reference treats such tensors as "present or NULL" (src/model.c:525-913)
+    optional: bool = False
 
 
 @dataclass(frozen=True)
@@ -51,11 +58,18 @@ class BuildContext:
 @dataclass(frozen=True)
 class KvRequest:
     """Keys and values per token that a mixer wants cached.  Runs whose requests are equal
-    share one storage group; ``window`` > 0 means only the last ``window`` positions are kept."""
+    share one storage group; ``window`` > 0 means only the last ``window`` positions are kept.
+    ``v_head_dim``: the width of a value head when it differs from a key head's (0: the same).
+    The library's attention kernels take equal widths; a mixer with others brings its own."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def v_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -147,6 +161,13 @@ class Norm(Part):
 
 class Position(Part):
     def rotate(self, x, n_heads, head_dim, ctx):
+        raise NotImplementedError
+
+
+class Head(Part):
+    graph_safe = True
+
+    def forward(self, h, table, ctx):
         raise NotImplementedError
 
 

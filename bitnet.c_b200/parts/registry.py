@@ -2,8 +2,8 @@
 
 ``@register_mixer("attention")`` and its siblings add a class; ``build_part`` looks a
 spec up by the role it plays and its ``kind``.  A new mixer, feed-forward, norm,
-position encoding or block arrangement is one class with one decorator; nothing
-else in the library has to change.
+position encoding, block arrangement or output head is one class with one decorator;
+nothing else in the library has to change.
 """
 from __future__ import annotations
 
@@ -13,7 +13,7 @@ from ..config.spec import ConfigError
 from .base import BuildContext, Part
 
 _REGISTRIES: Dict[str, Dict[str, Type[Part]]] = {
-    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "head": {},
 }
 
 
@@ -45,6 +45,10 @@ def register_position(kind: str):
 
 def register_block(kind: str):
     return _register("block", kind)
+
+
+def register_head(kind: str):
+    return _register("head", kind)
 
 
 def unregister(role: str, kind: str) -> None:

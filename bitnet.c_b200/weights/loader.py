@@ -90,7 +90,7 @@ def load_weights(model_dir: str, table: Mapping[str, "ParamSpec"], tensor_name: 
                     dup.append(f"tensor '{n}' is stored in two shards")
                 where[n] = f
         wanted = {tensor_name(path): path for path in table}
-        missing = sorted(n for n in wanted if n not in where)
+        missing = sorted(n for n, path in wanted.items() if n not in where and not table[path].optional)
         unexpected = sorted(n for n in where if n not in wanted)
         mismatched: List[str] = []
         for n, path in wanted.items():
@@ -109,6 +109,9 @@ def load_weights(model_dir: str, table: Mapping[str, "ParamSpec"], tensor_name: 
         out: Dict[str, torch.Tensor] = {}
         wide: List[str] = []
         for n, path in wanted.items():
+            if n not in where:  # an optional tensor that this file does not have
+                out[path] = None
+                continue
             t = where[n].read(n)
             keep = stored_dtype_to_kept(t.dtype, dtype, bool(table[path].integer))
             if keep == torch.float32 and dtype == torch.bfloat16 and t.dim() >= 2:

@@ -357,3 +357,234 @@ def test_norms_fused_into_products_agree_with_norm_kernels(cuda_device, monkeypa
     assert n_unfused == 20 and n_fused == 5 + 1 + 1 + 2
     for x, y in zip(a, b):
         assert np.abs(x - y).max() <= bf16_bound(x)
+
+
+@dataclass(frozen=True)
+class BiasedHeadSpec:
+    """A toy output head: logits = W h + bias, the bias being a parameter of the head's own that a
+    file may lack."""
+    vocab: int
+    kind: str = "toy_biased_head"
+
+
+def test_the_output_head_is_a_part_chosen_by_the_spec(cuda_device):
+    """The stock head with a logit scale and the reference's final soft-cap
+    (src/transformer/logits.c:325-333), and a toy head with an optional bias of its own that is
+    defined here: both come out of the model's spec; nothing in the library names them."""
+    from bitnet_c_b200.config import LinearHeadSpec
+    from bitnet_c_b200.parts import Head, register_head
+    from bitnet_c_b200.csrc import ops
+    from helpers import compare, replay, trace_tail, trace_whole
+
+    @register_head("toy_biased_head")
+    class BiasedHead(Head):
+        def params(self):
+            return {"bias": ParamSpec((self.spec.vocab,), init="zeros", optional=True)}
+
+        def bind(self, tensors):
+            self.bias = tensors["bias"]
+
+        def forward(self, h, table, ctx):
+            logits = ops.linear(h, table, out_dtype=torch.float32)
+            return logits if self.bias is None else logits + self.bias.float()
+
+    try:
+        attn = AttentionSpec(width=32, n_heads=2, n_kv_heads=1, head_dim=16, position=RotarySpec(16, 10000.0))
+        toks = {"p": np.random.default_rng(5).integers(0, 50, 40).tolist(), "q": [1, 2, 3]}
+        base = tiny_spec([attn])
+        for head, fn in ((LinearHeadSpec(scale=0.5, softcap=2.0), lambda l, w: np.tanh(0.5 * l / 2.0) * 2.0),
+                         (BiasedHeadSpec(50), lambda l, w: l + w["head.bias"]),
+                         (BiasedHeadSpec(50), lambda l, w: l)):
+            import dataclasses
+            spec = dataclasses.replace(base, head=head)
+            model = Model(spec, dtype="float32", device=cuda_device)
+            table = model.parameter_table()
+            assert ("head.bias" in table) == (head.kind == "toy_biased_head") and "head.weight" in table
+            w = random_bind(model, 12, scale=0.4)
+            if head.kind == "toy_biased_head" and fn(np.zeros(1), {"head.bias": np.ones(1)})[0] == 0:
+                # the same model without the optional tensor: bound with None
+                tensors = {k: torch.from_numpy(v).float().to(cuda_device) for k, v in w.items() if k != "head.bias"}
+                model.bind(tensors)
+                assert model.head_part.bias is None
+            elif head.kind == "toy_biased_head":
+                bias = torch.randn(50, generator=torch.Generator().manual_seed(1))
+                model.head_part.bias = bias.to(cuda_device)
+                w["head.bias"] = bias.double().numpy()
+            plain = {k: fn(plain_forward_spec(base, w, v), w) for k, v in toks.items()}
+            cache = model.new_cache(max_tokens=256, max_seqs=2)
+            for steps in (trace_whole(toks), trace_tail(toks, 8)):
+                compare(replay(model, cache, steps), plain, lambda r: 1e-4, f"head {head}")
+    finally:
+        unregister("head", "toy_biased_head")
+
+
+@dataclass(frozen=True)
+class NarrowValueSpec:
+    """A toy mixer whose cached values are narrower than its keys: one head, keys of ``k_dim``,
+    values of ``v_dim``, plain causal softmax attention, output W_o (v_dim -> width)."""
+    width: int
+    k_dim: int
+    v_dim: int
+    kind: str = "toy_narrow_values"
+
+
+def test_keys_and_values_of_different_widths_get_storage_of_their_own_shape(cuda_device):
+    from bitnet_c_b200.parts import KvRequest
+    from helpers import compare, replay, trace_batches, trace_tail, trace_whole
+
+    @register_mixer("toy_narrow_values")
+    class NarrowValues(Mixer):
+        def params(self):
+            s = self.spec
+            return {"qk": ParamSpec((2 * s.k_dim, s.width)), "v": ParamSpec((s.v_dim, s.width)), "o": ParamSpec((s.width, s.v_dim))}
+
+        def bind(self, tensors):
+            self.w = torch.cat([tensors["qk"], tensors["v"]]).float()
+            self.o = tensors["o"].float()
+
+        def cache_request(self):
+            return KvRequest(n_kv_heads=1, head_dim=self.spec.k_dim, v_head_dim=self.spec.v_dim)
+
+        def forward(self, h, ctx, kv, state):
+            s = self.spec
+            qkv = h.float() @ self.w.t()  # [T, k_dim (q) | k_dim (k) | v_dim]
+            kv.append(qkv, s.k_dim, 2 * s.k_dim, ctx)
+            out = torch.zeros(h.shape[0], s.v_dim, device=h.device)
+            at = 0
+            for slot, n, p0 in zip(ctx.host_slots, ctx.host_new, ctx.host_pos0):
+                for j in range(n):
+                    L = p0 + j + 1
+                    pages = kv.page_table[slot, : (L + 63) // 64].long()
+                    keys = kv.k[pages, 0].reshape(-1, s.k_dim)[:L].float()
+                    vals = kv.v[pages, 0].reshape(-1, s.v_dim)[:L].float()
+                    p = torch.softmax(keys @ qkv[at + j, : s.k_dim] * s.k_dim ** -0.5, dim=0)
+                    out[at + j] = p @ vals
+                at += n
+            return (out @ self.o.t()).to(h.dtype)
+
+    try:
+        spec = tiny_spec([NarrowValueSpec(32, 16, 8), AttentionSpec(width=32, n_heads=2, n_kv_heads=2, head_dim=16,
+                                                                    position=RotarySpec(16, 10000.0))])
+        model = Model(spec, dtype="float32", device=cuda_device)
+        w = random_bind(model, 21, scale=0.3)
+        cache = model.new_cache(max_tokens=512, max_seqs=2)
+        narrow = [g for g in cache.groups if g.request.v_head_dim][0]
+        assert narrow.k.shape[-1] == 16 and narrow.v.shape[-1] == 8 and len(cache.groups) == 2
+        assert narrow.bytes_per_token(4) == (16 + 8) * 4
+
+        def plain(tokens):
+            T = len(tokens)
+            x = w["embedding.table"][np.asarray(tokens)]
+            h = plain_llama.rmsnorm(x, w["blocks.0.mixer_norm.weight"], 1e-5)
+            qk = h @ w["blocks.0.mixer.qk"].T
+            q, k = qk[:, None, :16], qk[:, None, 16:]
+            v = (h @ w["blocks.0.mixer.v"].T)[:, None, :]
+            o = np.zeros((T, 8))
+            for t in range(T):
+                o[t] = plain_llama.softmax(k[: t + 1, 0] @ q[t, 0] * 0.25) @ v[: t + 1, 0]
+            x = x + o @ w["blocks.0.mixer.o"].T
+            h = plain_llama.rmsnorm(x, w["blocks.0.ffn_norm.weight"], 1e-5)
+            x = x + plain_llama.swiglu(h, w["blocks.0.ffn.gate"], w["blocks.0.ffn.up"], w["blocks.0.ffn.down"])
+            p = "blocks.1."
+            h = plain_llama.rmsnorm(x, w[p + "mixer_norm.weight"], 1e-5)
+            q2 = plain_llama.apply_rope((h @ w[p + "mixer.q"].T).reshape(T, 2, 16), range(T), 10000.0)
+            k2 = plain_llama.apply_rope((h @ w[p + "mixer.k"].T).reshape(T, 2, 16), range(T), 10000.0)
+            v2 = (h @ w[p + "mixer.v"].T).reshape(T, 2, 16)
+            x = x + plain_llama.attention(q2, k2, v2, 0.25).reshape(T, 32) @ w[p + "mixer.o"].T
+            h = plain_llama.rmsnorm(x, w[p + "ffn_norm.weight"], 1e-5)
+            x = x + plain_llama.swiglu(h, w[p + "ffn.gate"], w[p + "ffn.up"], w[p + "ffn.down"])
+            return plain_llama.rmsnorm(x, w["final_norm.weight"], 1e-5) @ w["head.weight"].T
+
+        toks = {"p": np.random.default_rng(2).integers(0, 50, 150).tolist(), "q": [4, 5, 6, 7]}
+        ref = {k: plain(v) for k, v in toks.items()}
+        for steps in (trace_whole(toks), trace_tail(toks, 20), trace_batches([{"p": (toks["p"], 9), "q": (toks["q"], 2)}])):
+            compare(replay(model, cache, steps), ref, lambda r: 2e-4, "narrow values")
+    finally:
+        unregister("mixer", "toy_narrow_values")
+
+
+def test_a_mixer_with_state_inside_recorded_decode_steps(cuda_device):
+    """The toy decaying-sum mixer written against the step's device arrays (``ctx.slots``), so that
+    it may be recorded: generation through the engine replays decode steps as CUDA graphs with the
+    state of fixed size updated inside them; requests one after another reuse a slot, whose state
+    must start at zero again."""
+    from bitnet_c_b200.engine import ModelEngine, generate
+    from bitnet_c_b200.sampling import SamplingParams
+
+    @register_mixer("toy_decay_mix")
+    class DecayMix(Mixer):
+        graph_safe = True
+
+        def params(self):
+            return {"w": ParamSpec((self.spec.width, self.spec.width))}
+
+        def bind(self, tensors):
+            self.w = tensors["w"]
+
+        def state_request(self):
+            return StateRequest((self.spec.width,), torch.float32)
+
+        def forward(self, h, ctx, kv, state):
+            hf = h.float()
+            if ctx.decode:  # one token per sequence: row b is sequence b; device arrays only
+                idx = ctx.slots.long()
+                s = state[idx] * self.spec.decay + hf
+                state.index_copy_(0, idx, s)
+                out = s
+            else:
+                out = torch.empty_like(hf)
+                at = 0
+                for slot, n in zip(ctx.host_slots, ctx.host_new):
+                    s = state[slot]
+                    for t in range(at, at + n):
+                        s = self.spec.decay * s + hf[t]
+                        out[t] = s
+                    state[slot] = s
+                    at += n
+            return (out @ self.w.float().t()).to(h.dtype)
+
+    try:
+        attn = AttentionSpec(width=32, n_heads=2, n_kv_heads=2, head_dim=16, position=RotarySpec(16, 10000.0))
+        spec = tiny_spec([DecayMixSpec(32, 0.8), attn])
+        model = Model(spec, dtype="float32", device=cuda_device)
+        assert model.graph_safe()
+        w = random_bind(model, 31, scale=0.5)
+
+        def plain_logits(tokens):
+            T = len(tokens)
+            x = w["embedding.table"][np.asarray(tokens)]
+            h = plain_llama.rmsnorm(x, w["blocks.0.mixer_norm.weight"], 1e-5)
+            s, rows = np.zeros(32), []
+            for t in range(T):
+                s = 0.8 * s + h[t]
+                rows.append(s)
+            x = x + np.stack(rows) @ w["blocks.0.mixer.w"].T
+            h = plain_llama.rmsnorm(x, w["blocks.0.ffn_norm.weight"], 1e-5)
+            x = x + plain_llama.swiglu(h, w["blocks.0.ffn.gate"], w["blocks.0.ffn.up"], w["blocks.0.ffn.down"])
+            p = "blocks.1."
+            h = plain_llama.rmsnorm(x, w[p + "mixer_norm.weight"], 1e-5)
+            q = plain_llama.apply_rope((h @ w[p + "mixer.q"].T).reshape(T, 2, 16), range(T), 10000.0)
+            k = plain_llama.apply_rope((h @ w[p + "mixer.k"].T).reshape(T, 2, 16), range(T), 10000.0)
+            v = (h @ w[p + "mixer.v"].T).reshape(T, 2, 16)
+            x = x + plain_llama.attention(q, k, v, 0.25).reshape(T, 32) @ w[p + "mixer.o"].T
+            h = plain_llama.rmsnorm(x, w[p + "ffn_norm.weight"], 1e-5)
+            x = x + plain_llama.swiglu(h, w[p + "ffn.gate"], w[p + "ffn.up"], w[p + "ffn.down"])
+            return plain_llama.rmsnorm(x, w["final_norm.weight"], 1e-5) @ w["head.weight"].T
+
+        def plain_generate(prompt, n):
+            toks = list(prompt)
+            for _ in range(n):
+                toks.append(int(np.argmax(plain_logits(toks)[-1])))
+            return toks[len(prompt):]
+
+        prompts = [np.random.default_rng(i).integers(0, 50, n).tolist() for i, n in enumerate([9, 1, 30, 4, 17])]
+        new = [12, 5, 8, 12, 3]
+        want = [plain_generate(p, n) for p, n in zip(prompts, new)]
+        for max_batch in (5, 2, 1):  # together; two at a time; one after another in the same slot
+            cache = model.new_cache(max_tokens=64 * max_batch * 2, max_seqs=max_batch)
+            eng = ModelEngine(model, cache, SamplingParams(temperature=0.0))
+            got = generate(eng, prompts, new, stop_ids=(), max_batch=max_batch)
+            assert [c.tokens for c in got] == want, f"max_batch={max_batch}"
+            assert eng.use_graphs and eng.runners and all(r.graphs for r in eng.runners.values())  # decode steps were recorded
+    finally:
+        unregister("mixer", "toy_decay_mix")
