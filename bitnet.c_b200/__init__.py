@@ -9,7 +9,7 @@ __version__ = "0.1.0"
 from .config import ConfigError, LlamaConfig, known_architectures  # noqa: E402,F401
 from .weights import WeightsError, write_random_model  # noqa: E402,F401
 from .cache import Cache, CacheError, CacheFull  # noqa: E402,F401
-from .engine import Completion, Model, SeqStep, StepError  # noqa: E402,F401
+from .engine import Completion, Diagnostics, Model, SeqStep, StepError  # noqa: E402,F401
 from .engine import generate_with_model as generate  # noqa: E402,F401
 from .sampling import SamplingParams  # noqa: E402,F401
 

@@ -8,7 +8,9 @@ is a folder with ``config.json`` and ``model.safetensors`` instead of a GGUF fil
 ``--random-weights`` writes such a folder from ``--config`` and ``--weight-seed``; ``--dtype`` picks
 bfloat16 or true float32; ``--prompt-token-ids`` may be given several times for a batch.  Options of
 the reference that select CPU threads, other backends, quantized caches, speculative decoding, chat
-mode or diagnostics of its GPU backends have no counterpart.
+mode or diagnostics of its GPU backends have no counterpart.  Its tensor dumps (``--dump-binary``,
+``--dump-tag``, ``--dump-layer``, ``--dump-pos``) are here, with ``--dump-stats`` for its text line of
+statistics, ``--top-logits`` for its BN_TOP_LOGITS and ``--profile`` for its per-category timers.
 """
 from __future__ import annotations
 
@@ -59,6 +61,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--config", default=None, help="config.json for --random-weights")
     ap.add_argument("--weight-seed", type=int, default=None, help="seed of --random-weights (default: --seed)")
     ap.add_argument("--stop-ids", default=None, help="comma-separated stop token ids (default: the model's eos_token_id)")
+    from .engine import diagnostics
+    diagnostics.add_arguments(ap)
     return ap
 
 
@@ -82,6 +86,10 @@ def main(argv=None) -> int:
     t0 = time.time()
     model = bn.load_model(args.model, dtype=args.dtype, max_seq=args.maxseq)
     load_ms = (time.time() - t0) * 1e3
+    from .engine import diagnostics
+    model.diagnostics = diagnostics.from_args(args)
+    if model.diagnostics is not None:
+        model.diagnostics.start_profile()
     vocab = model.spec.vocab_size
     prompts = [parse_ids(t, vocab) for t in args.prompt_token_ids]
     stop_ids = None if args.stop_ids is None else parse_ids(args.stop_ids, vocab)
@@ -118,6 +126,9 @@ def main(argv=None) -> int:
             print(f"Generation complete tokens={n_out} tok/s={n_out / max(total_ms, 1e-9) * 1e3:.2f} "
                   f"prompt_tokens={sum(len(p) for p in prompts)} total_ms={total_ms:.1f} load_ms={load_ms:.1f} "
                   f"requests={len(prompts)} dtype={args.dtype}", file=sys.stderr, flush=True)
+    if model.diagnostics is not None:
+        for line in model.diagnostics.profile_lines():
+            print(line, file=sys.stderr)
     if not args.quiet:
         for r in results:
             print(",".join(str(t) for t in r.tokens))

@@ -64,6 +64,17 @@ def _check(status: int, what: str) -> None:
 
 
 LAUNCHES = 0  # kernels of this library launched through this module (bench.py reads and resets it)
+PROFILE = None  # a dict while kernel classes are being timed (engine/diagnostics.py): entry point -> [(event, event)]
+
+
+def _timed(key: str, call):
+    """Run ``call`` between two CUDA events kept under ``key`` (only while PROFILE is a dict)."""
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    out = call()
+    b.record()
+    PROFILE.setdefault(key, []).append((a, b))
+    return out
 
 
 def _fn(family: str, name: str):
@@ -71,6 +82,8 @@ def _fn(family: str, name: str):
     LAUNCHES += 1
     f = getattr(build.library(family), name)
     f.restype = c_int
+    if PROFILE is not None:
+        return lambda *args: _timed(f"{family}.{name}", lambda: f(*args))
     return f
 
 
@@ -698,11 +711,12 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         if w.dtype == torch.float32:
             if torch.backends.cuda.matmul.allow_tf32:
                 raise KernelError("float32 products need torch.backends.cuda.matmul.allow_tf32 = False")
-            out = torch.matmul(x, w.t())
+            product = lambda: torch.matmul(x, w.t())
         elif out_dtype == torch.float32:
-            out = torch.mm(x, w.t(), out_dtype=torch.float32)
+            product = lambda: torch.mm(x, w.t(), out_dtype=torch.float32)
         else:
-            out = torch.matmul(x, w.t())
+            product = lambda: torch.matmul(x, w.t())
+        out = product() if PROFILE is None else _timed("library.matmul", product)
         out = out if out.dtype == out_dtype else out.to(out_dtype)
     if swiglu:
         act = torch.empty((M, N // 2), dtype=out.dtype, device=x.device)

@@ -55,6 +55,25 @@ class StepContext:
     host_new: List[int] = field(default_factory=list)  # the same facts on the host, for parts that
     host_pos0: List[int] = field(default_factory=list)  # loop over sequences there
     host_slots: List[int] = field(default_factory=list)
+    host_rows: List[int] = field(default_factory=list)  # the packed rows whose logits are wanted
+    # diagnostics (engine/diagnostics.py): None unless the model was given some; ``layer`` is the
+    # schedule entry that is running (-1 outside the layers)
+    diag: Optional[object] = None
+    layer: int = -1
+
+    def tap(self, tag: str, value, rows=None) -> None:
+        """Show a named intermediate tensor to the diagnostics, if there are any (a part calls this
+        with a tensor of one row per packed token, or a function that makes it)."""
+        if self.diag is not None:
+            self.diag.tap(self, tag, value, rows)
+
+    def host_positions(self):
+        """For every packed row its position and the index of its sequence in this step (host lists)."""
+        pos, seq = [], []
+        for i, (p0, n) in enumerate(zip(self.host_pos0, self.host_new)):
+            pos.extend(range(p0, p0 + n))
+            seq.extend([i] * n)
+        return pos, seq
 
 
 def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepContext:
@@ -103,4 +122,4 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
         tile_seq=dev[t0:t0 + n_tiles], tile_row0=dev[t0 + n_tiles:t0 + 2 * n_tiles],
         wide_tile_seq=dev[w0:w0 + n_wide], wide_tile_row0=dev[w0 + n_wide:w0 + 2 * n_wide], host_new=new,
         host_pos0=list(lengths),
-        host_slots=[s.slot for s in seqs])
+        host_slots=[s.slot for s in seqs], host_rows=[int(r) for r in rows])

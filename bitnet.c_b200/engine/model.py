@@ -57,6 +57,7 @@ class Model:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self._bad_token: Optional[torch.Tensor] = None
+        self.diagnostics = None  # engine/diagnostics.py: tensor dumps, top logits, kernel timers
         self._owners: Dict[str, tuple] = {}
         for i, blk in enumerate(self.blocks):
             _walk(f"blocks.{i}", blk, self._owners)
@@ -225,10 +226,17 @@ class Model:
         """Embedding, every scheduled run, final norm and head at the wanted rows."""
         x = torch.empty((ctx.n_tokens, self.spec.width), dtype=torch.float32, device=self.device)
         ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
+        diag = ctx.diag = self.diagnostics
+        ctx.layer = -1
+        ctx.tap("inp", x)
         pending = None
         sched = self.spec.schedule
         for i, e in enumerate(sched):
             blk = self.blocks[e.block]
+            if diag is not None:
+                if i > 0:
+                    ctx.tap("lout", lambda: _residual_after(x, pending))
+                ctx.layer = i
             if not getattr(blk, "accepts_normed", False):
                 pending = blk.forward(x, pending, ctx, cache.view(i), cache.state(i))
                 continue
@@ -240,13 +248,28 @@ class Model:
             else:
                 next_norm = self.final_norm if ctx.rows is not None and ctx.rows_all else None
             pending = blk.forward(x, pending, ctx, cache.view(i), cache.state(i), next_norm=next_norm)
+        if diag is not None:
+            ctx.tap("lout", lambda: _residual_after(x, pending))
+            ctx.layer = -1
         if ctx.rows is None:
             return None
         if isinstance(pending, Normed):
             h = pending.value
         else:
             h = self.final_norm.add_norm(x, pending, ctx, rows=ctx.rows)
-        return self.head_part.forward(h, self.head, ctx)
+        logits = self.head_part.forward(h, self.head, ctx)
+        if diag is not None:
+            ctx.tap("result_norm", h, rows=ctx.host_rows)
+            ctx.tap("result_output", logits, rows=ctx.host_rows)
+        return logits
+
+
+def _residual_after(x: torch.Tensor, pending) -> torch.Tensor:
+    """The residual stream with a block's last delta added (the delta is otherwise added by the next
+    norm; a product that prepared that norm in its epilogue has added it already)."""
+    if pending is None or isinstance(pending, Normed):
+        return x
+    return x + (pending.sum(0) if pending.dim() == 3 else pending).float()
 
 
 def require_cuda(device) -> None:

@@ -74,9 +74,12 @@ class ModelEngine(Engine):
         return torch.tensor(list(rows), dtype=torch.int32).to(self.model.device, non_blocking=True)
 
     def step_and_sample(self, seqs: Sequence[SeqStep], rows: Sequence[int]) -> List[int]:
-        if self.use_graphs and all(len(s.tokens) == 1 for s in seqs):
+        diag = self.model.diagnostics
+        if self.use_graphs and diag is None and all(len(s.tokens) == 1 for s in seqs):
             return self._decode_step(seqs, rows)
         logits = self.model.step(self.cache, seqs)
+        if diag is not None:
+            diag.show_top_logits(logits, rows)
         out = self.sampler.sample(logits, self._index(rows, self.sampler.n_rows))
         toks = out.cpu().tolist()
         self._check_kernels()

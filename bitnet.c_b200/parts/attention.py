@@ -65,15 +65,18 @@ class Attention(Mixer):
             # one token per sequence: position encoding, cache write, attention over the splits of
             # the keys and their combination are one kernel
             qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)
+            self._tap_raw(ctx, qkv)
             out = torch.empty((n, s.q_dim), dtype=self.build.dtype, device=h.device)
             rotary_dims, theta_scale = fusable()
             ops.attention_decode_fused(qkv, s.q_dim, s.q_dim + s.kv_dim, out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                        s.softmax_scale, s.window, rotary_dims, theta_scale, ctx.tok_pos, ctx.slots,
                                        kv.page_table, kv.k, kv.v, ctx.max_len, items=ctx.decode_items,
                                        item_group=ctx.decode_item_group)
+            ctx.tap("attn_out", out)
             return ops.linear(out, self.w_o, out_dtype=self.build.dtype, sink=sink)
         if kv.owner:
             qkv = ops.linear(h, self.w_qkv, out_dtype=self.build.dtype)
+            self._tap_raw(ctx, qkv)
             n_rot = s.n_heads + s.n_kv_heads
             fused = getattr(self.position, "rotate_and_append", None)
             if fused is not None:
@@ -85,6 +88,10 @@ class Attention(Mixer):
             # This run reads another run's keys and values: only the queries are needed.
             qkv = ops.linear(h, self.w_qkv[: s.q_dim], out_dtype=self.build.dtype)
             self.position.rotate(qkv, s.n_heads, s.head_dim, ctx)
+        if ctx.diag is not None:
+            ctx.tap("attn_q", lambda: qkv[:, : s.q_dim])
+            if kv.owner:
+                ctx.tap("attn_k", lambda: qkv[:, s.q_dim: s.q_dim + s.kv_dim])
         out = torch.empty((n, s.q_dim), dtype=self.build.dtype, device=h.device)
         if ctx.decode and qkv.dtype == torch.bfloat16:
             # one token per sequence: row b is sequence b; split over the keys
@@ -105,4 +112,12 @@ class Attention(Mixer):
             ops.attention_general(qkv, qkv.shape[1], out, n, s.n_heads, s.n_kv_heads, s.head_dim,
                                   s.softmax_scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
                                   kv.page_table, kv.k, kv.v)
+        ctx.tap("attn_out", out)
         return ops.linear(out, self.w_o, out_dtype=self.build.dtype, sink=sink)
+
+    def _tap_raw(self, ctx, qkv):
+        if ctx.diag is not None:
+            s = self.spec
+            ctx.tap("attn_q_raw", lambda: qkv[:, : s.q_dim].clone())
+            ctx.tap("attn_k_raw", lambda: qkv[:, s.q_dim: s.q_dim + s.kv_dim].clone())
+            ctx.tap("attn_v_raw", lambda: qkv[:, s.q_dim + s.kv_dim: s.q_dim + 2 * s.kv_dim].clone())

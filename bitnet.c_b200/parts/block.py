@@ -47,13 +47,18 @@ class PreNormBlock(Block):
 
     def forward(self, x, pending, ctx, kv, state, next_norm=None):
         h = pending.value if isinstance(pending, Normed) else self.mixer_norm.add_norm(x, pending, ctx)
+        ctx.tap("attn_norm", h)
         sink = self.ffn_norm.sink(x, ctx) if getattr(self.mixer, "accepts_sink", False) else None
         if sink is not None:
             h = self.mixer.forward(self._input_for(self.mixer, h), ctx, kv, state, sink=sink)
         else:
             d = self.mixer.forward(self._input_for(self.mixer, h), ctx, kv, state)
+            ctx.tap("attn_proj", d)
             h = self.ffn_norm.add_norm(x, d, ctx)
+        ctx.tap("ffn_norm", h)
         sink = next_norm.sink(x, ctx) if next_norm is not None and getattr(self.ffn, "accepts_sink", False) else None
         if sink is not None:
             return Normed(self.ffn.forward(self._input_for(self.ffn, h), ctx, sink=sink))
-        return self.ffn.forward(self._input_for(self.ffn, h), ctx)
+        d = self.ffn.forward(self._input_for(self.ffn, h), ctx)
+        ctx.tap("ffn_out", d)
+        return d
