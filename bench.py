@@ -414,6 +414,8 @@ def main():
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill and print its record (profiling)")
     ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run the generation workload of another size set instead")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -433,7 +435,12 @@ def main():
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     pk = peaks()
-    model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
+    if args.dtype == "float32":
+        if not (args.skip_points or args.only_prefill):
+            print("bench.py: --dtype float32 times the main run only; give --skip-points or --only-prefill")
+            return 2
+        torch.backends.cuda.matmul.allow_tf32 = False
+    model = Model.from_random(cfg, seed=0, dtype=args.dtype, device="cuda:0", norm_std=0.0)
 
     def prefill_record(m, c, ms, peak_tflops):
         fl = prefill_flops(c, PREFILL_TOKENS)
@@ -446,6 +453,7 @@ def main():
         print(json.dumps({"prefill": rec}))
         return 0
     B = args.batch
+    short_dtype = "bf16" if args.dtype == "bfloat16" else "fp32"
     # the prefill first: it is a burst of matrix products of a seventh of a second, and what it is
     # compared with is the burst peak; after seconds of decoding the GPU sits at its power cap
     pre_ms = None if args.skip_points else run_prefill(model, cfg)
@@ -457,11 +465,11 @@ def main():
     achieved = read_bytes / (ms_per_step / 1e3) / 1e9
 
     out = {
-        "metric": f"decode tokens/s at batch {B} (Llama-3.1-8B sizes, bf16)", "value": round(value, 2), "unit": "tokens/s",
+        "metric": f"decode tokens/s at batch {B} (Llama-3.1-8B sizes, {short_dtype})", "value": round(value, 2), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
         "ms_per_step_median": round(run["median_ms"], 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "impl": "ours",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": short_dtype, "data": "synthetic", "impl": "ours",
         "config": {"model": "llama-3.1-8b-sizes-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
