@@ -41,6 +41,7 @@ SOURCES: Dict[str, str] = {
     "linear": "linear.cu",
     "linear_mma": "linear_mma.cu",
     "linear_tc": "linear_tc.cu",
+    "gemm_tc": "gemm_tc.cu",
     "sampling": "sampling.cu",
     "argmax_noalloc": "argmax_noalloc.cu",
 }

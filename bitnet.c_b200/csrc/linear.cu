@@ -66,10 +66,9 @@ linear_skinny_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __r
     for (int kc = 0; kc < K; kc += SK_KC) {
       const int kn = min(SK_KC, K - kc);  // a multiple of 8
       __syncthreads();  // the chunk before this one has been used by every warp
-      for (int p = threadIdx.x; p < mt * (kn / VN); p += SK_WARPS * 32) {
-        const int i = p / (kn / VN), kk = (p - i * (kn / VN)) * VN;
-        *reinterpret_cast<uint4*>(&xs[i][kk]) = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(m0 + i) * K + kc + kk));
-      }
+      for (int i = 0; i < mt; ++i)
+        for (int kk = threadIdx.x * VN; kk < kn; kk += SK_WARPS * 32 * VN)
+          *reinterpret_cast<uint4*>(&xs[i][kk]) = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(m0 + i) * K + kc + kk));
       __syncthreads();
       if (nc <= 0) continue;
       // The order of the additions of one output depends on K alone: lane l adds the products of

@@ -548,7 +548,8 @@ def check_tc_status(device) -> None:
                 3: "linear_tc: the accumulator never completed",
                 4: "attention_decode_tc: a cache page never arrived (TMA load)",
                 5: "attention_prefill_tc: a wait inside the kernel gave up",
-                6: "linear_tc: a slice of partial sums from another block of the cluster never arrived"}.get(code, f"code {code}")
+                6: "linear_tc: a slice of partial sums from another block of the cluster never arrived",
+                7: "gemm_tc: a wait inside the kernel gave up"}.get(code, f"code {code}")
         raise KernelError(f"{what}; the result of that launch is not valid")
 
 
@@ -644,6 +645,73 @@ def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swigl
     return out
 
 
+USE_OWN_GEMM = False  # many-row bfloat16 products on this library's tcgen05 kernel (gemm_tc.cu) with SwiGLU and
+# residual + norm epilogues instead of the library product followed by separate kernels
+GEMM_MIN_ROWS = 65
+
+
+def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
+            sink: Optional[NormSink] = None):
+    """x[M, K] . w[N, K]^T for many rows in bfloat16 on tcgen05 tensor cores (gemm_tc.cu).  ``x`` may be
+    ``RowScaled``; ``swiglu`` and ``sink`` as for ``linear`` (the activation, or the residual add with
+    the next norm's gain and sums of squares, happen in the product's epilogue)."""
+    scaled = x if isinstance(x, RowScaled) else None
+    if scaled is not None:
+        x = scaled.x
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or K % 8 or N % 8 or (swiglu and N % 16) or (swiglu and sink is not None):
+        raise KernelError(f"gemm_tc: x {tuple(x.shape)}, w {tuple(w.shape)} not supported")
+    fn = _fn("gemm_tc", "bn_gemm_tc")
+    if scaled is not None:
+        _need(scaled.ss, "ss", torch.float32, 2)
+        if scaled.ss.shape[1] < M or scaled.width != K:
+            raise KernelError(f"gemm_tc: row sums {tuple(scaled.ss.shape)} of width {scaled.width} do not fit x {tuple(x.shape)}")
+        row = (_ptr(scaled.ss), c_int(scaled.ss.shape[0]), c_int(scaled.ss.shape[1]), c_float(1.0 / scaled.width),
+               c_float(scaled.eps))
+    else:
+        row = (c_void_p(None), c_int(0), c_int(0), c_float(0.0), c_float(0.0))
+    status = _ptr(tc_status(x.device))
+    if sink is not None:
+        res = sink.residual
+        _need(res, "residual", torch.float32, 2)
+        _need(sink.weight, "norm weight", dims=1)
+        if scaled is not None or tuple(res.shape) != (M, N) or sink.weight.shape[0] != N or sink.weight.dtype not in _DT:
+            raise KernelError(f"gemm_tc: residual {tuple(res.shape)} / norm weight {tuple(sink.weight.shape)} do not fit "
+                              f"a product [{M}, {N}]")
+        xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ss = torch.empty(((N + 255) // 256, M), dtype=torch.float32, device=x.device)
+        _check(fn(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), c_void_p(None), c_int(0), c_int(0), c_int(3), *row,
+                  _ptr(res), _ptr(sink.weight), c_int(_DT[sink.weight.dtype]), _ptr(xg), _ptr(ss), c_int(M), status,
+                  _stream()), "gemm_tc")
+        return RowScaled(xg, ss, N, sink.eps)
+    out_dtype = out_dtype or x.dtype
+    cols = N // 2 if swiglu else N
+    out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
+    _check(fn(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), _ptr(out), c_int(_DT[out_dtype]), c_int(cols),
+              c_int(2 if swiglu else 0), *row, c_void_p(None), c_void_p(None), c_int(0), c_void_p(None), c_void_p(None),
+              c_int(0), status, _stream()), "gemm_tc")
+    return out
+
+
+def gemm_pairs(on: Optional[bool] = None) -> bool:
+    """Whether ``gemm_tc`` runs pairs of blocks as one (tcgen05 cta_group::2, the default) or every block
+    alone; with an argument, sets it.  Returns the setting before the call."""
+    f = getattr(build.library("gemm_tc"), "bn_gemm_tc_pairs")
+    f.restype = c_int
+    return bool(f(c_int(-1 if on is None else int(bool(on)))))
+
+
+def _own_gemm_fits(x, w: torch.Tensor, swiglu: bool, out_dtype) -> bool:
+    M, K = x.shape
+    N = w.shape[0]
+    return (USE_OWN_GEMM and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and M >= GEMM_MIN_ROWS
+            and K % 8 == 0 and N % (16 if swiglu else 8) == 0 and (N // 2 if swiglu else N) % 8 == 0
+            and out_dtype in (None, torch.bfloat16, torch.float32))
+
+
 def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
            partial_sums: bool = False, sink: Optional[NormSink] = None):
     """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
@@ -670,12 +738,17 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
     if sink is not None:
         if fast and USE_FUSED_NORM and not swiglu and tuple(sink.residual.shape) == (M, N):
             return linear_tc(x, w, sink=sink)
+        if (not swiglu and not isinstance(x, RowScaled) and tuple(sink.residual.shape) == (M, N)
+                and _own_gemm_fits(x, w, False, None) and not partial_sums):
+            return gemm_tc(x, w, sink=sink)
         delta = linear(x, w, out_dtype=out_dtype, swiglu=swiglu)
         normed = torch.empty((M, sink.residual.shape[1]), dtype=delta.dtype, device=delta.device)
         return add_rmsnorm(sink.residual, delta, sink.weight, sink.eps, normed)
     if isinstance(x, RowScaled):
         if fast:
             return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
+        if _own_gemm_fits(x, w, swiglu, out_dtype) and not partial_sums:
+            return gemm_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
         x = x.dense()
     _need(x, "x", dims=2)
     out_dtype = out_dtype or x.dtype
@@ -683,6 +756,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         x = x.to(w.dtype)
     if streams:
         return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
+    if _own_gemm_fits(x, w, swiglu, out_dtype) and not partial_sums:
+        return gemm_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
     if small:
         fn = _fn("linear_mma", "bn_linear_mma")
         splits = _mma_splits(M, N, K, n_sms(x.device))

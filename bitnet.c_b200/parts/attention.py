@@ -16,7 +16,7 @@ class Attention(Mixer):
     over the causal range (optionally the last ``window`` keys); output projection.
     Order and formulas: src/transformer/cpu.c:859-939, src/transformer/gqa_scalar.c:61-121."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "attention", "attention_decode", "attention_decode_tc", "attention_prefill",
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "attention_decode", "attention_decode_tc", "attention_prefill",
                "attention_prefill_tc", "rope", "norm")
     graph_safe = True
     accepts_sink = True

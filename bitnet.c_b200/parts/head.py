@@ -16,7 +16,7 @@ class LinearHead(Head):
     (src/transformer/logits.c:325-333).  The Llama architecture uses scale 1 and no soft-cap, and
     then nothing but the product runs."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "act")
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "act")
 
     def forward(self, h, table, ctx):
         logits = ops.linear(h, table, out_dtype=torch.float32)

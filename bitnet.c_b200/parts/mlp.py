@@ -14,7 +14,7 @@ from .registry import register_ffn
 class GatedMlp(FeedForward):
     """y = W_down (silu(W_gate h) * (W_up h))   (src/transformer/cpu.c:1247-1303)."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "act", "norm")
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "act", "norm")
     graph_safe = True
     accepts_sink = True
 

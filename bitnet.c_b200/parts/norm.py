@@ -26,8 +26,9 @@ class RmsNorm(Norm):
 
     def sink(self, x, ctx):
         # a product of few rows in bfloat16 can add to the residual and prepare this norm's output
-        if (self.build.dtype == torch.bfloat16 and x.shape[0] <= ops.MMA_MAX_ROWS and ops.USE_TCGEN05
-                and ops.USE_FUSED_NORM and x.dtype == torch.float32):
+        if self.build.dtype != torch.bfloat16 or not ops.USE_FUSED_NORM or x.dtype != torch.float32:
+            return None
+        if (x.shape[0] <= ops.MMA_MAX_ROWS and ops.USE_TCGEN05) or (x.shape[0] >= ops.GEMM_MIN_ROWS and ops.USE_OWN_GEMM):
             return ops.NormSink(x, self.weight, self.spec.eps)
         return None
 

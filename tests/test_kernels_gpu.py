@@ -585,3 +585,64 @@ def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd,
     bits = lambda t: t.view(torch.int16)
     assert torch.equal(bits(k)[~touched], bits(k_before)[~touched]) and torch.equal(bits(v)[~touched], bits(v_before)[~touched])
     ops.check_tc_status(cuda_device)
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 264, 72), (128, 256, 64), (200, 1000, 200), (333, 512, 4096), (1000, 6144, 512),
+                                   (2048, 272, 1032)])
+@pytest.mark.parametrize("pairs", [True, False])
+def test_gemm_tc_store_swiglu_and_norm_epilogues(cuda_device, pairs, M, N, K):
+    """The many-row tcgen05 product with its epilogues: plain store (bfloat16 and float32), SwiGLU on
+    the interleaved gate/up layout, residual add + next norm's gain + sums of squares, and rows that
+    still lack their scale (the output of that epilogue) as input.  Sizes that are no multiples of
+    the 128 x 256 x 64 tiles; more tiles than blocks.  ``pairs``: two blocks work as one
+    (cta_group::2, tiles of 256 x 256) or every block alone."""
+    ops.gemm_pairs(pairs)
+    g = torch.Generator().manual_seed(40)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(cuda_device)
+    ref = x.double() @ w.double().t()
+    bound = 2e-5 * max(1.0, K / 64)
+    y = ops.gemm_tc(x, w, out_dtype=torch.float32)
+    assert y.shape == (M, N) and (y.double() - ref).abs().max().item() < bound
+    yb = ops.gemm_tc(x, w)
+    assert yb.dtype == torch.bfloat16 and ((yb.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + bound).all()
+    # SwiGLU: N/2 gate and N/2 up rows interleaved in blocks of 8
+    I = N // 16 * 8
+    gate, up = w[:I], (torch.randn(I, K, generator=g) * 0.05).to(torch.bfloat16).to(cuda_device)
+    a, b = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    refs = a / (1 + torch.exp(-a)) * b
+    ys = ops.gemm_tc(x, ops.interleave_gate_up(gate, up), out_dtype=torch.float32, swiglu=True)
+    assert ys.shape == (M, I) and (ys.double() - refs).abs().max().item() < 10 * bound
+    # residual + norm epilogue, then a product that consumes the rows that still lack their scale
+    res = torch.randn(M, N, generator=g).to(cuda_device)
+    gain = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).to(cuda_device)
+    eps = 1e-5
+    res2 = res.clone()
+    rs = ops.gemm_tc(x, w, sink=ops.NormSink(res2, gain, eps))
+    new = res.double() + ref
+    assert (res2.double() - new).abs().max().item() < bound + 1e-6
+    assert isinstance(rs, ops.RowScaled) and rs.ss.shape == ((N + 255) // 256, M)
+    assert ((rs.ss.double().sum(0) - (new * new).sum(1)).abs() <= 1e-4 * (new * new).sum(1)).all()
+    normed = new / torch.sqrt((new * new).mean(1, keepdim=True) + eps) * gain.double()
+    assert (rs.dense().double() - normed).abs().max().item() < 3e-2
+    w2 = (torch.randn(80, N, generator=g) * 0.05).to(torch.bfloat16).to(cuda_device)
+    y2 = ops.gemm_tc(rs, w2, out_dtype=torch.float32)
+    # the reference uses the rounded rows the kernel multiplied, then the scale
+    xg = rs.x.double()
+    scale = 1.0 / torch.sqrt(rs.ss.double().sum(0) / N + eps)
+    assert (y2.double() - (xg @ w2.double().t()) * scale[:, None]).abs().max().item() < 2e-4 * max(1.0, N / 256)
+    ops.check_tc_status(cuda_device)
+    ops.gemm_pairs(True)
+
+
+def test_linear_takes_the_own_gemm_when_asked(cuda_device, monkeypatch):
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(100, 512, generator=g).to(torch.bfloat16).to(cuda_device)
+    w = (torch.randn(304, 512, generator=g) * 0.05).to(torch.bfloat16).to(cuda_device)
+    a = ops.linear(x, w, out_dtype=torch.float32)
+    monkeypatch.setattr(ops, "USE_OWN_GEMM", True)
+    calls = []
+    real = ops.gemm_tc
+    monkeypatch.setattr(ops, "gemm_tc", lambda *p, **k: (calls.append(1), real(*p, **k))[1])
+    b = ops.linear(x, w, out_dtype=torch.float32)
+    assert calls and (a - b).abs().max().item() < 1e-4
