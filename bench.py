@@ -414,6 +414,8 @@ def main():
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill and print its record (profiling)")
     ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run the generation workload of another size set instead")
+    ap.add_argument("--own-gemm", action="store_true",
+                    help="many-row products on the library's own tcgen05 kernel (gemm_tc.cu) instead of cuBLAS (comparisons, profiling)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
     args = ap.parse_args()
@@ -435,6 +437,9 @@ def main():
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     pk = peaks()
+    if args.own_gemm:
+        from bitnet_c_b200.csrc import ops
+        ops.USE_OWN_GEMM = True
     if args.dtype == "float32":
         if not (args.skip_points or args.only_prefill):
             print("bench.py: --dtype float32 times the main run only; give --skip-points or --only-prefill")
@@ -450,6 +455,7 @@ def main():
     if args.only_prefill:
         rec = prefill_record(model, cfg, run_prefill(model, cfg, warmup=2, iters=3), pk["bf16_tflops"])
         rec["layers"] = cfg["num_hidden_layers"]
+        rec["many_row_products"] = "gemm_tc" if args.own_gemm else "library"
         print(json.dumps({"prefill": rec}))
         return 0
     B = args.batch
