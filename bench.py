@@ -519,7 +519,7 @@ def main():
         del m32
         torch.cuda.empty_cache()
         for name in sorted(WORKLOADS):
-            w = run_workload(name, repeats=1)
+            w = run_workload(name, repeats=2)
             points[f"workload_{name}"] = w["value"]
             out[f"workload_{name}"] = {"seconds": w["seconds"], "generated": w["generated"], "prompt_tokens": w["prompt_tokens"],
                                        "requests": w["requests"], "decode_step_gb": w["decode_step_gb"]}

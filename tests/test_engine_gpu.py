@@ -148,3 +148,27 @@ def test_a_model_drawn_on_the_device_is_the_model_of_the_folder(tmp_path, cuda_d
         for u, v in ((x.mixer.w_qkv, y.mixer.w_qkv), (x.mixer.w_o, y.mixer.w_o), (x.ffn.w_gate_up, y.ffn.w_gate_up),
                      (x.ffn.w_down, y.ffn.w_down), (x.mixer_norm.weight, y.mixer_norm.weight)):
             assert u.dtype == v.dtype and (u != v).float().mean().item() < 1e-4
+
+
+@pytest.mark.parametrize("case", ["c_sharp", "d_sharp"])
+def test_the_librarys_own_many_row_product_inside_the_model(tmp_path, cuda_device, monkeypatch, case):
+    """Prompts and continuation chunks with the many-row products on the library's own tcgen05 kernel
+    (``ops.USE_OWN_GEMM``): SwiGLU, residual + norm and rows that lack their scale all happen in its
+    epilogues, and the logits must still be the plain implementation's."""
+    from bitnet_c_b200.csrc import ops
+    cfg, seed, lens = CASES[case]
+    d = make_model_dir(tmp_path, cfg, seed, "bfloat16", matrix_std=sharp_std(cfg))
+    reqs = {f"r{i}": random_tokens(seed * 100 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)}
+    model = bn.load_model(d, dtype="bfloat16")
+    plain = plain_logits(d, reqs)
+    pcfg, w = plain_llama.read_model(d)
+    bounds = {r: measured_bf16_bound(pcfg, w, t, plain[r]) for r, t in reqs.items()}
+    monkeypatch.setattr(ops, "USE_OWN_GEMM", True)
+    calls = []
+    real = ops.gemm_tc
+    monkeypatch.setattr(ops, "gemm_tc", lambda *a, **k: (calls.append(k.get("sink") is not None), real(*a, **k))[1])
+    cache = model.new_cache(max_tokens=4096)
+    compare(replay(model, cache, trace_whole(reqs)), plain, bounds, "own products, whole")
+    assert any(calls) and not all(calls)  # with and without the norm epilogue
+    compare(replay(model, cache, trace_chunks(reqs, pieces=(130, 70, 1, 200))), plain, bounds, "own products, chunks")
+    model.check_kernels()
