@@ -111,7 +111,8 @@ class ClockSampler:
 
 
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
-REF_SOURCE = "/root/reference"
+# where an unmodified checkout of artalis-io/bitnet.c lies if baseline/_ref does not hold one yet
+REF_SOURCE = os.environ.get("BITNET_C_SOURCE") or os.path.join(os.path.dirname(ROOT), "reference")
 REF_PREFILL_BUDGET_S = 200.0  # the 2,048-token prompt is left out if the 512-token one says it would take longer
 REF_CUDA_NOTE = ("its CUDA backend cannot be built: nvcc 12.9 stops on src/gpu_cuda.cu with 119 errors in the source "
                  "itself (BnCudaBlockQ8_1 used at line 104 before its definition at line 179, 115 calls that pass "
