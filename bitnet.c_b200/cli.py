@@ -61,6 +61,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--config", default=None, help="config.json for --random-weights")
     ap.add_argument("--weight-seed", type=int, default=None, help="seed of --random-weights (default: --seed)")
     ap.add_argument("--stop-ids", default=None, help="comma-separated stop token ids (default: the model's eos_token_id)")
+    ap.add_argument("--loop-abort", action="store_true",
+                    help="end a request when its last four tokens repeat the four before (the reference does unless BN_DISABLE_LOOP_ABORT is set)")
     from .engine import diagnostics
     diagnostics.add_arguments(ap)
     return ap
@@ -118,7 +120,7 @@ def main(argv=None) -> int:
         else:
             results = bn.generate(model, prompts, max_new, temperature=args.temp, top_p=args.topp, seed=args.seed,
                                   repeat_penalty=args.repeat_penalty, stop_ids=stop_ids,
-                                  callback=emit if args.token_ids and measured else None)
+                                  callback=emit if args.token_ids and measured else None, loop_abort=args.loop_abort)
         torch.cuda.synchronize()
         total_ms = (time.time() - t1) * 1e3
         n_out = sum(len(r.tokens) for r in results)
@@ -159,7 +161,7 @@ def _generate_no_prefill(bn, model, prompts, max_new, args, stop_ids, emit):
     params = SamplingParams(temperature=args.temp, top_p=args.topp, seed=args.seed, repeat_penalty=args.repeat_penalty)
     stops = tuple(model.spec.stop_ids) if stop_ids is None else tuple(stop_ids)
     return generate(OneByOne(model, cache, params), prompts, max_new, stop_ids=stops,
-                    callback=emit if args.token_ids else None)
+                    callback=emit if args.token_ids else None, loop_abort=args.loop_abort)
 
 
 if __name__ == "__main__":

@@ -8,7 +8,9 @@ the sequence); when ``max_new_tokens`` are out, the sequence ends without anothe
 pass; otherwise the token is fed back.  The reference serves one sequence per session; here a
 batch of sequences starts together (all prompts in one step), every later step carries one
 token for each sequence still running, and a sequence that ends gives its slot back at once.
-The reference's n-gram loop detector (src/generate.c:162-176) is left out: it changes outputs.
+The reference's n-gram loop detector (src/generate.c:162-176: generation is aborted when the last
+four sampled tokens repeat the four before them) changes outputs and is off unless asked for
+(``loop_abort``; the reference has it on unless BN_DISABLE_LOOP_ABORT is set).
 
 The loop only decides; everything that touches the device is behind the small ``Engine``
 interface below, so the decisions are tested without a GPU against a scripted engine.
@@ -26,7 +28,8 @@ from .batch import SeqStep
 class Completion:
     """What one request produced.  ``finish_reason``: 'length' (max_new_tokens reached), 'stop'
     (a stop token was sampled; it is not among ``tokens``), 'context' (the context is full),
-    'callback' (the callback asked to stop)."""
+    'callback' (the callback asked to stop), 'loop' (the loop detector ended it; the token that
+    closed the repetition is not among ``tokens``)."""
 
     tokens: List[int] = field(default_factory=list)
     finish_reason: str = ""
@@ -82,11 +85,22 @@ def plan_batch(prompts: Sequence[Sequence[int]], max_new: Sequence[int], start: 
     return n
 
 
+LOOP_NGRAM = 4  # src/generate.c:62
+
+
+def closes_a_loop(sampled: Sequence[int]) -> bool:
+    """The reference's loop test on the tokens sampled so far for one request, the newest last
+    (src/generate.c:166-176): at least eight of them, and the last four equal the four before."""
+    n = LOOP_NGRAM
+    return len(sampled) >= 2 * n and list(sampled[-n:]) == list(sampled[-2 * n:-n])
+
+
 def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens, stop_ids: Sequence[int] = (),
-             callback: Optional[Callable[[int, int], bool]] = None, max_batch: Optional[int] = None
-             ) -> List[Completion]:
+             callback: Optional[Callable[[int, int], bool]] = None, max_batch: Optional[int] = None,
+             loop_abort: bool = False) -> List[Completion]:
     """Serve every prompt.  ``max_new_tokens`` is one number or one per prompt; ``callback(request,
-    token)`` is called for every emitted token and stops that request when it returns true."""
+    token)`` is called for every emitted token and stops that request when it returns true;
+    ``loop_abort`` ends a request whose last four sampled tokens repeat the four before them."""
     n_req = len(prompts)
     max_new = [int(max_new_tokens)] * n_req if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
     if len(max_new) != n_req:
@@ -128,6 +142,8 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens, s
                 reason = ""
                 if tok in stops:
                     reason = "stop"
+                elif loop_abort and closes_a_loop(done[i].tokens[-(2 * LOOP_NGRAM - 1):] + [tok]):
+                    reason = "loop"  # as in the reference, before the token is accepted or emitted
                 else:
                     done[i].tokens.append(tok)
                     emitted_tokens.append(tok)

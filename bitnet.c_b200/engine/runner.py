@@ -124,10 +124,11 @@ def generate_with_model(model: Model, prompts: Sequence[Sequence[int]], max_new_
                         repeat_penalty: float = 1.0, repeat_window: int = 64,
                         stop_ids: Optional[Sequence[int]] = None, max_batch: Optional[int] = None,
                         cache: Optional[Cache] = None, max_tokens: Optional[int] = None,
-                        callback=None) -> List[Completion]:
+                        callback=None, loop_abort: bool = False) -> List[Completion]:
     """Generate for every prompt (lists of token ids).  ``stop_ids`` default to the model's
     end-of-sequence ids.  The cache is sized for the whole call unless ``max_tokens`` or a
-    ``cache`` is given; requests that do not fit together run in batches one after another."""
+    ``cache`` is given; requests that do not fit together run in batches one after another.
+    ``loop_abort``: the reference's loop detector (off by default here)."""
     from ..cache.pages import PAGE, pages_for
     params = SamplingParams(temperature=temperature, top_p=top_p, seed=seed, repeat_penalty=repeat_penalty,
                             repeat_window=repeat_window)
@@ -143,4 +144,4 @@ def generate_with_model(model: Model, prompts: Sequence[Sequence[int]], max_new_
         cache = model.new_cache(max_tokens=max_tokens or max(need, PAGE), max_seqs=max_batch or max(n, 1))
     stops = tuple(model.spec.stop_ids) if stop_ids is None else tuple(stop_ids)
     return generate(ModelEngine(model, cache, params), prompts, mx, stop_ids=stops, callback=callback,
-                    max_batch=max_batch)
+                    max_batch=max_batch, loop_abort=loop_abort)

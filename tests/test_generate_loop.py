@@ -120,3 +120,40 @@ def test_context_limit_max_new_zero_and_callback():
         generate(Scripted(), [[]], 1)
     with pytest.raises(ValueError, match="exceeds the context"):
         generate(Scripted(max_positions=3), [[1, 2, 3, 4]], 1)
+
+
+class Cycling(Scripted):
+    """Emits a fixed script of tokens per slot, whatever it is fed."""
+
+    def __init__(self, scripts, **kw):
+        super().__init__(**kw)
+        self.scripts, self.at = scripts, {}
+
+    def open(self):
+        s = super().open()
+        self.at[s] = 0
+        return s
+
+    def step_and_sample(self, seqs, rows):
+        out = []
+        for s, r in zip(seqs, rows):
+            out.append(self.scripts[r][self.at[s.slot]])
+            self.at[s.slot] += 1
+        return out
+
+
+def test_the_loop_detector_is_the_references_and_is_off_unless_asked_for():
+    """src/generate.c:162-176: once eight tokens have been sampled, a request whose last four equal
+    the four before them ends, and the token that closed the repetition is not emitted."""
+    from bitnet_c_b200.engine.generate import closes_a_loop
+    assert not closes_a_loop([1, 2, 3, 1, 2, 3, 1]) and closes_a_loop([9, 1, 2, 3, 4, 1, 2, 3, 4])
+    assert not closes_a_loop([1, 2, 3, 4, 1, 2, 3, 5]) and closes_a_loop([7] * 8) and not closes_a_loop([7] * 7)
+    scripts = [[5, 6, 7, 8, 5, 6, 7, 8, 5, 6, 7, 8], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12]]
+    prompts = [[3], [4, 4]]
+    free = generate(Cycling(scripts), prompts, 12)
+    assert [c.tokens for c in free] == scripts and all(c.finish_reason == "length" for c in free)
+    e = Cycling(scripts)
+    got = generate(e, prompts, 12, loop_abort=True)
+    assert got[0].tokens == [5, 6, 7, 8, 5, 6, 7] and got[0].finish_reason == "loop"
+    assert got[1].tokens == scripts[1] and got[1].finish_reason == "length"
+    assert sorted(e.free) == [0, 1, 2, 3] and not e.seq  # both slots came back
