@@ -5,8 +5,6 @@ from __future__ import annotations
 
 import numpy as np
 
-_STATE = {}
-
 
 def _bn():
     import bitnet_c_b200 as bn
@@ -23,6 +21,7 @@ class ModelHandle:
         self.cache = self.model.new_cache(max_tokens=max_tokens, max_seqs=max_seqs)
         self.vocab = self.model.spec.vocab_size
         self.seq_len = self.model.spec.max_positions
+        self.engine = None  # the generation engine of bn_generate_batch, kept from call to call
 
 
 class SessionHandle:
@@ -123,8 +122,8 @@ def generate_batch(m: ModelHandle, prompts, max_new, temperature, topp, penalty,
     from bitnet_c_b200.sampling import SamplingParams
     params = SamplingParams(temperature=temperature, top_p=topp if 0.0 < topp < 1.0 else 1.0, seed=int(seed),
                             repeat_penalty=penalty, repeat_window=max(1, window))
-    eng = _STATE.get(id(m))
+    eng = m.engine
     if eng is None or eng.params != params:
-        eng = _STATE[id(m)] = ModelEngine(m.model, m.cache, params)
+        eng = m.engine = ModelEngine(m.model, m.cache, params)
     out = generate(eng, [_ints(p) for p in prompts], [int(max_new)] * len(prompts), stop_ids=tuple(_ints(stop_ids)))
     return [np.asarray(c.tokens, dtype="<i4").tobytes() for c in out]

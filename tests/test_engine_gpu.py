@@ -11,7 +11,7 @@ import bitnet_c_b200 as bn
 import plain_llama
 from helpers import (TOL_F32, bf16_bound, collect_trace_output, compare, make_model_dir, measured_bf16_bound, plain_logits,
                      random_tokens, replay, sharp_std, steps_to_jsonl, trace_batches, trace_chunks, trace_tail, trace_whole)
-from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D, TINY_E, TINY_F
 
 pytestmark = pytest.mark.gpu
 
@@ -20,6 +20,8 @@ CASES = {
     "b": (TINY_B, 22, [17, 1, 40, 200, 129, 256]),
     "c": (TINY_C, 33, [70, 300, 64, 513, 97]),
     "d": (TINY_D, 44, [700, 130, 1, 260, 64, 500]),
+    "e": (TINY_E, 55, [150, 64, 3, 400, 129, 66]),
+    "f": (TINY_F, 66, [90, 300, 1, 64, 500, 130]),
 }
 # the same four with matrices of scale 1/sqrt(width) ("sharp", helpers.sharp_std): attention scores
 # spread over several units, so that rotation, softmax scale and which key gets which weight all

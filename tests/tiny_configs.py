@@ -38,3 +38,23 @@ TINY_D = {
     "vocab_size": 1000, "max_position_embeddings": 2048, "rope_theta": 1000000.0,
     "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
 }
+
+# Head sizes the other four do not have: 80 (a step of 16 between the kernels' instantiations for 64
+# and 128, padded inside them) with five query heads on one key/value head, and 256 (the largest
+# allowed; prefill attention then runs on the mma.sync kernel), widths and vocabularies that are
+# no powers of two.
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 200, "intermediate_size": 312, "num_hidden_layers": 2,
+    "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 80,
+    "vocab_size": 515, "max_position_embeddings": 512, "rope_theta": 20000.0,
+    "rms_norm_eps": 2e-6, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+
+TINY_F = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 264, "intermediate_size": 400, "num_hidden_layers": 1,
+    "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 256,
+    "vocab_size": 777, "max_position_embeddings": 640, "rope_theta": 300000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
+}
