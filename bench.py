@@ -522,6 +522,10 @@ def main():
         for name in sorted(WORKLOADS):
             w = run_workload(name, repeats=2)
             points[f"workload_{name}"] = w["value"]
+            new = WORKLOADS[name][2]
+            # the whole run's time (prefill included) spread over its decode steps: a lower bound of the
+            # decode steps' fraction of the copy bandwidth
+            fracs[f"workload_{name}"] = round(w["decode_step_gb"] / (w["seconds"] / new) / pk["hbm_gbs"], 4)
             out[f"workload_{name}"] = {"seconds": w["seconds"], "generated": w["generated"], "prompt_tokens": w["prompt_tokens"],
                                        "requests": w["requests"], "decode_step_gb": w["decode_step_gb"]}
         out["points"] = points
