@@ -164,6 +164,28 @@ def test_context_limit_and_errors(models):
         model.step(cache, [bn.SeqStep(slot, list(range(29)))])
     assert cache.length(slot) == 100
     cache.check()
+    # a step that fails after its pages were reserved gives them back and leaves the lengths alone
+    free_before = cache.tokens_free()
+    real_forward = model.forward
+    model.forward = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("injected"))
+    try:
+        with pytest.raises(RuntimeError, match="injected"):
+            model.step(cache, [bn.SeqStep(slot, list(range(20)))])
+    finally:
+        model.forward = real_forward
+    assert cache.length(slot) == 100 and cache.tokens_free() == free_before
+    cache.check()
+    model.step(cache, [bn.SeqStep(slot, list(range(20)))])  # and the same step then runs
+    assert cache.length(slot) == 120
+    # an id outside the table that reaches the embedding kernel (the host check is what normally
+    # stops it) is flagged on the device, and the next look at the kernels' status says so
+    import torch
+    from bitnet_c_b200.csrc import ops
+    out = torch.empty(1, cfg["hidden_size"], device="cuda:0")
+    ops.embed_gather(model.embedding, torch.tensor([cfg["vocab_size"] + 5], dtype=torch.int32, device="cuda:0"), out, model._bad_token)
+    with pytest.raises(bn.StepError, match="outside the embedding table"):
+        model.check_kernels()
+    model.check_kernels()  # reported once, then clear
 
 
 def test_bfloat16_generation_stays_near_the_plain_logits(tmp_path, cuda_device):
