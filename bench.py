@@ -63,37 +63,58 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs.
+
+    nvidia-smi needs a moment before its first line, and a timed region of a few dozen decode
+    steps is shorter than that: ``launch`` starts it before the warm-up steps, every line is
+    stamped when it arrives, and ``stop`` keeps the lines between ``start`` and ``stop``.  If
+    fewer than three fall into the timed region, the lines of the warm-up steps (the same steps,
+    directly before) are counted too, and ``window`` says so."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    PERIOD_MS = 20
 
     def __init__(self):
         self.lines, self.proc = [], None
+        self.t_launch = self.t_start = self.t_stop = None
 
-    def start(self):
+    def launch(self):
+        if self.proc is not None:
+            return
+        self.t_launch = time.monotonic()
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.PERIOD_MS)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
+    def start(self):
+        self.launch()
+        self.t_start = time.monotonic()
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def stop(self):
+        self.t_stop = time.monotonic()
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        timed = [l for t, l in self.lines if self.t_start <= t <= self.t_stop]
+        window = "timed steps"
+        if len(timed) < 3:
+            timed = [l for t, l in self.lines if t <= self.t_stop]
+            window = "warm-up and timed steps"
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in timed:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -107,7 +128,7 @@ class ClockSampler:
                     reasons.add(n)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
@@ -302,6 +323,8 @@ def run_decode(model, cfg, batch, steps, warmup, prompt_len=PROMPT_LEN, clock=No
     def one_step(t):
         return eng.step_and_sample([SeqStep(slots[i], [t[i]], [0]) for i in range(batch)], rows)
 
+    if clock is not None:
+        clock.launch()
     for _ in range(warmup):
         toks = one_step(toks)
     torch.cuda.synchronize()
