@@ -438,8 +438,10 @@ def main():
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill and print its record (profiling)")
     ap.add_argument("--batch", type=int, default=8, help="batch of the main decode run (default 8; other values for profiling)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run the generation workload of another size set instead")
-    ap.add_argument("--own-gemm", action="store_true",
-                    help="many-row products on the library's own tcgen05 kernel (gemm_tc.cu) instead of cuBLAS (comparisons, profiling)")
+    ap.add_argument("--own-gemm", choices=["off", "fused", "all"],
+                    help="which many-row products run on the library's own tcgen05 kernel (gemm_tc.cu) instead of cuBLAS: "
+                         "none, those whose epilogue replaces a separate kernel (the library's default), or all "
+                         "(comparisons, profiling)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
     args = ap.parse_args()
@@ -463,7 +465,7 @@ def main():
     pk = peaks()
     if args.own_gemm:
         from bitnet_c_b200.csrc import ops
-        ops.USE_OWN_GEMM = True
+        ops.USE_OWN_GEMM = {"off": False, "fused": "fused", "all": True}[args.own_gemm]
     if args.dtype == "float32":
         if not (args.skip_points or args.only_prefill):
             print("bench.py: --dtype float32 times the main run only; give --skip-points or --only-prefill")
@@ -479,7 +481,9 @@ def main():
     if args.only_prefill:
         rec = prefill_record(model, cfg, run_prefill(model, cfg, warmup=2, iters=3), pk["bf16_tflops"])
         rec["layers"] = cfg["num_hidden_layers"]
-        rec["many_row_products"] = "gemm_tc" if args.own_gemm else "library"
+        from bitnet_c_b200.csrc import ops as _ops
+        rec["many_row_products"] = {False: "library", "fused": "gemm_tc where its epilogue replaces a kernel, else library",
+                                    True: "gemm_tc"}[_ops.USE_OWN_GEMM]
         print(json.dumps({"prefill": rec}))
         return 0
     B = args.batch

@@ -56,12 +56,10 @@ struct GmArgs {
 
 __device__ __forceinline__ float gm_silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
-// The epilogue of one tile for one thread: row m of the output, the 256 columns from n0 on, read
-// from the thread's TMEM lane at acc_addr (see the modes at the top of this file).
-__device__ __forceinline__ void gm_finish_tile(const GmArgs& a, unsigned acc_addr, int m, int n0, int nt, float scale,
-                                               const float* gains) {
+// The epilogue of one tile for one thread in modes 0 and 2: row m of the output, the 256 columns
+// from n0 on, read from the thread's TMEM lane at acc_addr (see the modes at the top of this file).
+__device__ __forceinline__ void gm_finish_tile(const GmArgs& a, unsigned acc_addr, int m, int n0, float scale) {
   const bool live = m < a.M;
-  float ss_new = 0.f;
 #pragma unroll 1
   for (int c = 0; c < GM_BN; c += 32) {
     float v[32];
@@ -84,7 +82,7 @@ __device__ __forceinline__ void gm_finish_tile(const GmArgs& a, unsigned acc_add
           if (n0 + c + g * 4 < a.N)
             *reinterpret_cast<float4*>(o + g * 4) = make_float4(v[g * 4] * scale, v[g * 4 + 1] * scale, v[g * 4 + 2] * scale, v[g * 4 + 3] * scale);
       }
-    } else if (a.mode == 2) {
+    } else {
       // two blocks of 8 gate + 8 up values -> 16 outputs at column (n0 + c) / 2
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
@@ -101,27 +99,63 @@ __device__ __forceinline__ void gm_finish_tile(const GmArgs& a, unsigned acc_add
           *reinterpret_cast<float4*>((float*)a.out + oc + 4) = make_float4(r[4], r[5], r[6], r[7]);
         }
       }
-    } else {
-      float* res = a.residual + (size_t)m * a.N + n0 + c;
-      __nv_bfloat16* xg = a.xg + (size_t)m * a.N + n0 + c;
-      const float* gs = gains + c;
+    }
+  }
+}
+
+// The epilogue of one tile for one warp in mode 3: rows m0 .. m0 + 31 (the warp's TMEM lanes).  A
+// thread that walks its own row touches 32 cache lines with every load or store of the warp, and
+// the residual is read and written in float32: that kept the load/store unit busy for longer than
+// the tile's products took.  So the accumulator goes through shared memory 32 columns at a time
+// (stage: [32 rows][33] floats of this warp), and comes back with eight lanes on the 32 columns of a
+// row, four rows per instruction: whole 128-byte lines of the residual, 64 bytes of the rows for
+// the next product.  The squares of a row are summed per lane over the tile's columns in a fixed
+// order, then over the row's eight lanes.
+#define GM_STG 33
+__device__ __forceinline__ void gm_finish_tile_rows(const GmArgs& a, unsigned acc_addr, int m0, int n0, int nt, const float* gains,
+                                                    float* stage, int lane) {
+  const int sub = lane >> 3, q4 = (lane & 7) * 4;
+  float ssl[8];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        if (n0 + c + g * 8 >= a.N) continue;
-        float4 o0 = *reinterpret_cast<const float4*>(res + g * 8), o1 = *reinterpret_cast<const float4*>(res + g * 8 + 4);
-        float x[8] = {o0.x + v[g * 8], o0.y + v[g * 8 + 1], o0.z + v[g * 8 + 2], o0.w + v[g * 8 + 3],
-                      o1.x + v[g * 8 + 4], o1.y + v[g * 8 + 5], o1.z + v[g * 8 + 6], o1.w + v[g * 8 + 7]};
-        *reinterpret_cast<float4*>(res + g * 8) = make_float4(x[0], x[1], x[2], x[3]);
-        *reinterpret_cast<float4*>(res + g * 8 + 4) = make_float4(x[4], x[5], x[6], x[7]);
+  for (int it = 0; it < 8; ++it) ssl[it] = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < GM_BN; c += 32) {
+    float v[32];
+    tmem_ld32(acc_addr + c, v);
+    __syncwarp();  // the chunk before this one has been read
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss_new = fmaf(x[e], x[e], ss_new);
-        *reinterpret_cast<uint4*>(xg + g * 8) =
-            make_uint4(pack_bf16x2(x[0] * gs[g * 8], x[1] * gs[g * 8 + 1]), pack_bf16x2(x[2] * gs[g * 8 + 2], x[3] * gs[g * 8 + 3]),
-                       pack_bf16x2(x[4] * gs[g * 8 + 4], x[5] * gs[g * 8 + 5]), pack_bf16x2(x[6] * gs[g * 8 + 6], x[7] * gs[g * 8 + 7]));
+    for (int j = 0; j < 32; ++j) stage[lane * GM_STG + j] = v[j];
+    __syncwarp();
+    const int col = n0 + c + q4;
+    if (col < a.N) {  // the same for a whole group of four columns: N is a multiple of 8
+      const float4 g4 = *reinterpret_cast<const float4*>(gains + c + q4);
+      float4 old[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int m = m0 + it * 4 + sub;
+        old[it] = m < a.M ? *reinterpret_cast<const float4*>(a.residual + (size_t)m * a.N + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + sub, m = m0 + r;
+        if (m >= a.M) continue;
+        const float* sv = stage + r * GM_STG + q4;
+        const float x0 = old[it].x + sv[0], x1 = old[it].y + sv[1], x2 = old[it].z + sv[2], x3 = old[it].w + sv[3];
+        *reinterpret_cast<float4*>(a.residual + (size_t)m * a.N + col) = make_float4(x0, x1, x2, x3);
+        *reinterpret_cast<uint2*>(a.xg + (size_t)m * a.N + col) = make_uint2(pack_bf16x2(x0 * g4.x, x1 * g4.y), pack_bf16x2(x2 * g4.z, x3 * g4.w));
+        ssl[it] = fmaf(x3, x3, fmaf(x2, x2, fmaf(x1, x1, fmaf(x0, x0, ssl[it]))));
       }
     }
   }
-  if (a.mode == 3 && live) a.ss_out[(size_t)nt * a.ss_out_stride + m] = ss_new;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    float t = ssl[it];
+    t += __shfl_xor_sync(0xffffffffu, t, 1);
+    t += __shfl_xor_sync(0xffffffffu, t, 2);
+    t += __shfl_xor_sync(0xffffffffu, t, 4);
+    const int m = m0 + it * 4 + sub;
+    if ((lane & 7) == 0 && m < a.M) a.ss_out[(size_t)nt * a.ss_out_stride + m] = t;
+  }
 }
 
 __global__ void __launch_bounds__(GM_THREADS, 1)
@@ -143,6 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   unsigned* tmem_slot = (unsigned*)(bars + 2 * GM_STAGES + 4);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
   float* gain_s = (float*)(tmem_slot + 4);  // [2][256]: the gains of the tile's columns, per accumulator
+  float* stage_s = gain_s + 2 * GM_BN;      // [4 warps][32][GM_STG]: mode 3, an accumulator chunk on its way to whole rows
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles_total = a.m_tiles * a.n_tiles;
@@ -252,7 +287,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) continue;  // walk the remaining tiles without work (their barrier above is still kept)
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      gm_finish_tile(a, lane_addr + buf * GM_BN, m, n0, nt, scale, gain_s + buf * GM_BN);
+      if (a.mode == 3)
+        gm_finish_tile_rows(a, lane_addr + buf * GM_BN, mt * GM_BM + quad * 32, n0, nt, gain_s + buf * GM_BN,
+                            stage_s + (warp - 2) * 32 * GM_STG, lane);
+      else
+        gm_finish_tile(a, lane_addr + buf * GM_BN, m, n0, scale);
       // the accumulator may be written again
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -342,6 +381,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   unsigned* tmem_slot = (unsigned*)(bars + 2 * GM2_STAGES + 4);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
   float* gain_s = (float*)(tmem_slot + 4);
+  float* stage_s = gain_s + 2 * GM_BN;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const unsigned rank = gm_cluster_rank();
@@ -455,7 +495,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) continue;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      gm_finish_tile(a, lane_addr + buf * GM_BN, m, n0, nt, scale, gain_s + buf * GM_BN);
+      if (a.mode == 3)
+        gm_finish_tile_rows(a, lane_addr + buf * GM_BN, mp * 2 * GM_BM + (int)rank * GM_BM + quad * 32, n0, nt,
+                            gain_s + buf * GM_BN, stage_s + (warp - 2) * 32 * GM_STG, lane);
+      else
+        gm_finish_tile(a, lane_addr + buf * GM_BN, m, n0, scale);
       // the pair's accumulator may be written again once all eight epilogue warps have said so
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -489,10 +533,13 @@ static int gm_sm_count() {
   return n;
 }
 
+// How many parts of sums of squares a mode-3 product of N columns writes (rows of ss_out).
+extern "C" int bn_gemm_tc_parts(int N) { return N <= 0 ? 0 : (N + GM_BN - 1) / GM_BN; }
+
 // x: [M, K] bfloat16 rows (K a multiple of 8, 16-byte aligned), w: [N, K] bfloat16.
 // mode 0: out [M, ldo] of out_dtype (N a multiple of 8).  mode 2: out [M, ldo], ldo >= N / 2 (N a
 // multiple of 16).  mode 3: residual [M, N] float32 (in place), gain [N], xg [M, N] bfloat16, ss_out
-// [ceil(N / 256)][ss_out_stride >= M] (N a multiple of 8).  row_ss (or null): [ss_parts][ss_stride]
+// [bn_gemm_tc_parts(N)][ss_out_stride >= M] (N a multiple of 8).  row_ss (or null): [ss_parts][ss_stride]
 // sums of squares of the rows of x over a width of 1 / inv_width, eps of that norm.  status: one
 // int on the device, left as it is unless a wait inside the kernel gave up (then 7).
 extern "C" int bn_gemm_tc(const void* x, const void* w, int M, int N, int K, void* out, int out_dtype, int ldo, int mode,
@@ -525,7 +572,7 @@ extern "C" int bn_gemm_tc(const void* x, const void* w, int M, int N, int K, voi
   a.residual = residual; a.gain = gain; a.gain_dtype = gain_dtype; a.xg = (__nv_bfloat16*)xg; a.ss_out = ss_out;
   a.ss_out_stride = ss_out_stride; a.status = status;
   if (pairs) {
-    size_t smem = (size_t)GM2_STAGES * (GM_BM + GM_BN / 2) * GM_BK * 2 + (2 * GM2_STAGES + 4) * 8 + 16 + 2 * GM_BN * 4 + 1024;
+    size_t smem = (size_t)GM2_STAGES * (GM_BM + GM_BN / 2) * GM_BK * 2 + (2 * GM2_STAGES + 4) * 8 + 16 + 2 * GM_BN * 4 + 4 * 32 * GM_STG * 4 + 1024;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -539,7 +586,7 @@ extern "C" int bn_gemm_tc(const void* x, const void* w, int M, int N, int K, voi
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     return BN_OK;
   }
-  size_t smem = (size_t)GM_STAGES * (GM_BM + GM_BN) * GM_BK * 2 + (2 * GM_STAGES + 4) * 8 + 16 + 2 * GM_BN * 4 + 1024;
+  size_t smem = (size_t)GM_STAGES * (GM_BM + GM_BN) * GM_BK * 2 + (2 * GM_STAGES + 4) * 8 + 16 + 2 * GM_BN * 4 + 4 * 32 * GM_STG * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

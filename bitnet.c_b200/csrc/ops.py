@@ -645,9 +645,25 @@ def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swigl
     return out
 
 
-USE_OWN_GEMM = False  # many-row bfloat16 products on this library's tcgen05 kernel (gemm_tc.cu) with SwiGLU and
-# residual + norm epilogues instead of the library product followed by separate kernels
-GEMM_MIN_ROWS = 65
+# Many-row bfloat16 products on this library's tcgen05 kernel (gemm_tc.cu) instead of the library product
+# followed by separate kernels.  "fused": where the kernel's epilogue replaces a pass over the activations
+# and that saves more than its main loop loses against the library's (measured on a B200 at widths 4096
+# and 14336: the SwiGLU epilogue from 1,024 rows on, 0.88 to 0.98 of the library product + activation
+# kernel; the residual + norm epilogue from 2,048 rows on for inner sizes up to 8192, 0.85 to 0.95 of the
+# library product + norm kernel; plain products are 1.09 to 1.16 of the library's and stay there).
+# True: every product that fits.  False: none.
+USE_OWN_GEMM = "fused"
+GEMM_MIN_ROWS = 65            # True: from so many rows on
+OWN_GEMM_SWIGLU_MIN_ROWS = 1024
+OWN_GEMM_SINK_MIN_ROWS = 2048
+OWN_GEMM_SINK_MAX_K = 8192
+
+
+def own_gemm_sink_rows(rows: int) -> bool:
+    """Whether a product of so many rows may take the residual + norm epilogue of ``gemm_tc``."""
+    if USE_OWN_GEMM is True:
+        return rows >= GEMM_MIN_ROWS
+    return USE_OWN_GEMM == "fused" and rows >= OWN_GEMM_SINK_MIN_ROWS
 
 
 def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
@@ -682,7 +698,9 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu:
             raise KernelError(f"gemm_tc: residual {tuple(res.shape)} / norm weight {tuple(sink.weight.shape)} do not fit "
                               f"a product [{M}, {N}]")
         xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        ss = torch.empty(((N + 255) // 256, M), dtype=torch.float32, device=x.device)
+        parts = getattr(build.library("gemm_tc"), "bn_gemm_tc_parts")
+        parts.restype = c_int
+        ss = torch.empty((parts(c_int(N)), M), dtype=torch.float32, device=x.device)
         _check(fn(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), c_void_p(None), c_int(0), c_int(0), c_int(3), *row,
                   _ptr(res), _ptr(sink.weight), c_int(_DT[sink.weight.dtype]), _ptr(xg), _ptr(ss), c_int(M), status,
                   _stream()), "gemm_tc")
@@ -704,12 +722,22 @@ def gemm_pairs(on: Optional[bool] = None) -> bool:
     return bool(f(c_int(-1 if on is None else int(bool(on)))))
 
 
-def _own_gemm_fits(x, w: torch.Tensor, swiglu: bool, out_dtype) -> bool:
+def _own_gemm_fits(x, w: torch.Tensor, swiglu: bool, out_dtype, kind: str) -> bool:
+    """``kind``: "plain", "swiglu", "sink", or "scaled" (rows that lack their scale: the library product
+    would need them made dense first)."""
     M, K = x.shape
     N = w.shape[0]
-    return (USE_OWN_GEMM and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and M >= GEMM_MIN_ROWS
+    if not (USE_OWN_GEMM and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and M >= GEMM_MIN_ROWS
             and K % 8 == 0 and N % (16 if swiglu else 8) == 0 and (N // 2 if swiglu else N) % 8 == 0
-            and out_dtype in (None, torch.bfloat16, torch.float32))
+            and out_dtype in (None, torch.bfloat16, torch.float32)):
+        return False
+    if USE_OWN_GEMM is True or kind == "scaled":
+        return True
+    if kind == "swiglu":
+        return M >= OWN_GEMM_SWIGLU_MIN_ROWS
+    if kind == "sink":
+        return M >= OWN_GEMM_SINK_MIN_ROWS and K <= OWN_GEMM_SINK_MAX_K
+    return False
 
 
 def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
@@ -739,7 +767,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         if fast and USE_FUSED_NORM and not swiglu and tuple(sink.residual.shape) == (M, N):
             return linear_tc(x, w, sink=sink)
         if (not swiglu and not isinstance(x, RowScaled) and tuple(sink.residual.shape) == (M, N)
-                and _own_gemm_fits(x, w, False, None) and not partial_sums):
+                and _own_gemm_fits(x, w, False, None, "sink") and not partial_sums):
             return gemm_tc(x, w, sink=sink)
         delta = linear(x, w, out_dtype=out_dtype, swiglu=swiglu)
         normed = torch.empty((M, sink.residual.shape[1]), dtype=delta.dtype, device=delta.device)
@@ -747,7 +775,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
     if isinstance(x, RowScaled):
         if fast:
             return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
-        if _own_gemm_fits(x, w, swiglu, out_dtype) and not partial_sums:
+        if _own_gemm_fits(x.x, w, swiglu, out_dtype, "scaled") and not partial_sums:
             return gemm_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
         x = x.dense()
     _need(x, "x", dims=2)
@@ -756,7 +784,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         x = x.to(w.dtype)
     if streams:
         return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
-    if _own_gemm_fits(x, w, swiglu, out_dtype) and not partial_sums:
+    if _own_gemm_fits(x, w, swiglu, out_dtype, "swiglu" if swiglu else "plain") and not partial_sums:
         return gemm_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
     if small:
         fn = _fn("linear_mma", "bn_linear_mma")

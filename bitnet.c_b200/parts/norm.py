@@ -25,10 +25,10 @@ class RmsNorm(Norm):
         self.weight = tensors["weight"]
 
     def sink(self, x, ctx):
-        # a product of few rows in bfloat16 can add to the residual and prepare this norm's output
+        # a product in bfloat16 of few rows, or of many, can add to the residual and prepare this norm's output
         if self.build.dtype != torch.bfloat16 or not ops.USE_FUSED_NORM or x.dtype != torch.float32:
             return None
-        if (x.shape[0] <= ops.MMA_MAX_ROWS and ops.USE_TCGEN05) or (x.shape[0] >= ops.GEMM_MIN_ROWS and ops.USE_OWN_GEMM):
+        if (x.shape[0] <= ops.MMA_MAX_ROWS and ops.USE_TCGEN05) or ops.own_gemm_sink_rows(x.shape[0]):
             return ops.NormSink(x, self.weight, self.spec.eps)
         return None
 

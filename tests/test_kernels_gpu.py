@@ -588,7 +588,7 @@ def test_attention_decode_fused(cuda_device, monkeypatch, splits, H, KV, hd, rd,
 
 
 @pytest.mark.parametrize("M,N,K", [(65, 264, 72), (128, 256, 64), (200, 1000, 200), (333, 512, 4096), (1000, 6144, 512),
-                                   (2048, 272, 1032)])
+                                   (2048, 272, 1032), (2048, 4096, 576)])
 @pytest.mark.parametrize("pairs", [True, False])
 def test_gemm_tc_store_swiglu_and_norm_epilogues(cuda_device, pairs, M, N, K):
     """The many-row tcgen05 product with its epilogues: plain store (bfloat16 and float32), SwiGLU on
@@ -622,6 +622,7 @@ def test_gemm_tc_store_swiglu_and_norm_epilogues(cuda_device, pairs, M, N, K):
     new = res.double() + ref
     assert (res2.double() - new).abs().max().item() < bound + 1e-6
     assert isinstance(rs, ops.RowScaled) and rs.ss.shape == ((N + 255) // 256, M)
+    assert torch.equal(rs.dense(), ops.gemm_tc(x, w, sink=ops.NormSink(res.clone(), gain, eps)).dense())  # and the same again
     assert ((rs.ss.double().sum(0) - (new * new).sum(1)).abs() <= 1e-4 * (new * new).sum(1)).all()
     normed = new / torch.sqrt((new * new).mean(1, keepdim=True) + eps) * gain.double()
     assert (rs.dense().double() - normed).abs().max().item() < 3e-2
