@@ -152,11 +152,16 @@ def test_a_model_drawn_on_the_device_is_the_model_of_the_folder(tmp_path, cuda_d
             assert u.dtype == v.dtype and (u != v).float().mean().item() < 1e-4
 
 
+@pytest.mark.parametrize("policy", ["all", "fused"])
 @pytest.mark.parametrize("case", ["c_sharp", "d_sharp"])
-def test_the_librarys_own_many_row_product_inside_the_model(tmp_path, cuda_device, monkeypatch, case):
+def test_the_librarys_own_many_row_product_inside_the_model(tmp_path, cuda_device, monkeypatch, case, policy):
     """Prompts and continuation chunks with the many-row products on the library's own tcgen05 kernel
     (``ops.USE_OWN_GEMM``): SwiGLU, residual + norm and rows that lack their scale all happen in its
-    epilogues, and the logits must still be the plain implementation's."""
+    epilogues, and the logits must still be the plain implementation's.  ``all``: every product;
+    ``fused``: the default policy (the kernel where its epilogue replaces a separate kernel, the
+    library product elsewhere) with its row limits lowered to these prompts and the inner-size limit of
+    the residual + norm epilogue set so that the model with the wider feed-forward (d) mixes both
+    kinds: O through the kernel, down through the library product and the norm kernel."""
     from bitnet_c_b200.csrc import ops
     cfg, seed, lens = CASES[case]
     d = make_model_dir(tmp_path, cfg, seed, "bfloat16", matrix_std=sharp_std(cfg))
@@ -165,12 +170,23 @@ def test_the_librarys_own_many_row_product_inside_the_model(tmp_path, cuda_devic
     plain = plain_logits(d, reqs)
     pcfg, w = plain_llama.read_model(d)
     bounds = {r: measured_bf16_bound(pcfg, w, t, plain[r]) for r, t in reqs.items()}
-    monkeypatch.setattr(ops, "USE_OWN_GEMM", True)
+    if policy == "all":
+        monkeypatch.setattr(ops, "USE_OWN_GEMM", True)
+    else:
+        assert ops.USE_OWN_GEMM == "fused"  # the default
+        monkeypatch.setattr(ops, "OWN_GEMM_SWIGLU_MIN_ROWS", 65)
+        monkeypatch.setattr(ops, "OWN_GEMM_SINK_MIN_ROWS", 65)
+        monkeypatch.setattr(ops, "OWN_GEMM_SINK_MAX_K", cfg["num_attention_heads"] * cfg["head_dim"])
     calls = []
     real = ops.gemm_tc
     monkeypatch.setattr(ops, "gemm_tc", lambda *a, **k: (calls.append(k.get("sink") is not None), real(*a, **k))[1])
+    norms = []
+    real_norm = ops.add_rmsnorm
+    monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (norms.append(a[0].shape[0]), real_norm(*a, **k))[1])
     cache = model.new_cache(max_tokens=4096)
     compare(replay(model, cache, trace_whole(reqs)), plain, bounds, "own products, whole")
     assert any(calls) and not all(calls)  # with and without the norm epilogue
+    if policy == "fused" and cfg["intermediate_size"] > cfg["num_attention_heads"] * cfg["head_dim"]:
+        assert any(n >= 65 for n in norms)  # the down product's norm went through the norm kernel
     compare(replay(model, cache, trace_chunks(reqs, pieces=(130, 70, 1, 200))), plain, bounds, "own products, chunks")
     model.check_kernels()

@@ -72,3 +72,39 @@ def test_whole_tail_and_unequal_batches_at_real_layer_sizes(real, dtype):
 def test_the_bfloat16_bounds_at_real_sizes_are_a_few_roundings(real):
     for r, ref in real["plain"].items():
         assert real["bounds"][r] < 0.05 * float(np.abs(ref).max()), (r, real["bounds"][r], float(np.abs(ref).max()))
+
+
+def test_a_step_of_more_than_2048_rows_takes_the_own_products_and_agrees_with_the_library_ones(real, monkeypatch):
+    """At 2,048 rows and more the default policy sends the gate|up product (SwiGLU epilogue) and the O
+    product (residual + norm epilogue) to the library's own tcgen05 kernel.  One ragged step of 2,100 + 40
+    tokens: the last positions' logits are those of the same step with every many-row product on the
+    library product and separate kernels, within the bound of a few roundings."""
+    from bitnet_c_b200.csrc import ops
+    from bitnet_c_b200.engine import SeqStep
+    m = _model(real, "bfloat16")
+    cfg_vocab = real["plain"]["long"].shape[-1]
+    reqs = [random_tokens(900, 2100, cfg_vocab), random_tokens(901, 40, cfg_vocab)]
+
+    def run():
+        cache = m.new_cache(max_tokens=2304, max_seqs=2)
+        slots = [cache.open() for _ in reqs]
+        out = m.step(cache, [SeqStep(slot=s, tokens=t, want=[len(t) - 1]) for s, t in zip(slots, reqs)])
+        for s in slots:
+            cache.close(s)
+        return out.float().cpu().numpy()
+
+    assert ops.USE_OWN_GEMM == "fused"
+    kinds = []
+    real_gemm = ops.gemm_tc
+    monkeypatch.setattr(ops, "gemm_tc", lambda *a, **k: (kinds.append("sink" if k.get("sink") is not None else
+                                                                      "swiglu" if k.get("swiglu") else "plain"),
+                                                         real_gemm(*a, **k))[1])
+    own = run()
+    assert "sink" in kinds and "swiglu" in kinds
+    monkeypatch.setattr(ops, "USE_OWN_GEMM", False)
+    kinds.clear()
+    lib = run()
+    assert not kinds
+    bound = max(real["bounds"].values())
+    assert np.abs(own - lib).max() < bound, (float(np.abs(own - lib).max()), bound)
+    m.check_kernels()
