@@ -238,6 +238,13 @@ def test_decode_batches_of_twenty_and_seventy_sequences(tmp_path, cuda_device, d
     prompts = [random_tokens(7000 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)]
     got = bn.generate(model, prompts, max_new_tokens=new, stop_ids=[])
     assert [len(g.tokens) for g in got] == new
+    assert _tokens_that_are_the_plain_choice(pcfg, w, prompts, got, dtype) >= 0.97 * sum(new)  # nearly all are the plain argmax itself
+
+
+def _tokens_that_are_the_plain_choice(pcfg, w, prompts, got, dtype):
+    """Every emitted token must be the plain implementation's choice at its place, or lie within
+    the rounding bound of it (measured on this very sequence); returns how many are the plain
+    argmax itself."""
     exact = 0
     for i, (p, g) in enumerate(zip(prompts, got)):
         toks = list(p) + g.tokens[:-1]
@@ -247,29 +254,37 @@ def test_decode_batches_of_twenty_and_seventy_sequences(tmp_path, cuda_device, d
             row = ref[len(p) - 1 + j]
             assert row[t] >= row.max() - 2 * slack, f"request {i} (prompt of {len(p)}), new token {j}"
             exact += int(t == int(np.argmax(row)))
-    assert exact >= 0.97 * sum(new)  # nearly all are the plain argmax itself
+    return exact
 
 
 @pytest.mark.parametrize("group", [1, 2, 3])
 def test_a_work_list_for_unequal_lengths_changes_no_tokens(tmp_path, cuda_device, monkeypatch, group):
     """Decode steps of a batch of unequal lengths with the attention kernel's work list forced on
     (long sequences split over ``group`` blocks and started first): the same tokens as without,
-    also when the short sequences end and the list is made again."""
+    also when the short sequences end and the list is made again.  The model is sharp (scores of
+    order one, so that a wrong far key, page or position moves the logits far beyond rounding),
+    the sequences cross page ends and the 1,024-position edge of the recorded steps' buckets, and
+    the tokens of both runs are held against the plain implementation."""
     from bitnet_c_b200.csrc import ops
-    d = make_model_dir(tmp_path, TINY_D, 77, "bfloat16")
+    d = make_model_dir(tmp_path, TINY_D, 77, "bfloat16", matrix_std=sharp_std(TINY_D))
     model = bn.load_model(d, dtype="bfloat16")
+    pcfg, w = plain_llama.read_model(d)
     prompts = [random_tokens(60 + i, n, TINY_D["vocab_size"]) for i, n in enumerate([1500, 90, 40, 700, 1000])]
     new = [40, 12, 30, 5, 40]
     base = bn.generate(model, prompts, max_new_tokens=new, stop_ids=[])
+    assert _tokens_that_are_the_plain_choice(pcfg, w, prompts, base, "bfloat16") >= 0.9 * sum(new)
     monkeypatch.setattr(ops, "_FORCE_ITEM_GROUP", group)
     calls = []
     real = ops.attention_decode_fused
     monkeypatch.setattr(ops, "attention_decode_fused", lambda *a, **k: (calls.append(k.get("item_group", 0)), real(*a, **k))[1])
     got = bn.generate(model, prompts, max_new_tokens=new, stop_ids=[])
     assert group in calls  # the recorded steps were made with the list
+    assert [len(g.tokens) for g in got] == new
+    assert _tokens_that_are_the_plain_choice(pcfg, w, prompts, got, "bfloat16") >= 0.9 * sum(new)
     same = sum(a == b for g, h in zip(got, base) for a, b in zip(g.tokens, h.tokens))
     total = sum(len(h.tokens) for h in base)
-    assert [len(g.tokens) for g in got] == new and same >= total - 2, (same, total)  # bfloat16: a tie may fall the other way
+    # bfloat16: a near-tie may fall the other way, and what follows it in that sequence differs then
+    assert same >= 0.6 * total, (same, total)
 
 
 def test_command_line(tmp_path, cuda_device):
