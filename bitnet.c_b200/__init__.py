@@ -26,3 +26,16 @@ def load_model(model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", 
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
     return Model.from_dir(model_dir, dtype=dtype, device=device, max_seq=max_seq)
+
+
+def load_plugins(modules) -> None:
+    """Import the named Python modules.  A module may register parts (``parts.register_mixer`` and
+    the like) or a whole architecture (``config.register_architecture``) of its own, which
+    ``load_model`` then finds by config.json's ``architectures`` like the ones that ship; this is
+    what the command line's and ``bin/trace_run``'s ``--plugin`` do."""
+    import importlib
+    for name in modules or ():
+        try:
+            importlib.import_module(name)
+        except ImportError as e:
+            raise ConfigError(f"plugin module '{name}' cannot be imported: {e}") from None

@@ -64,6 +64,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--loop-abort", action="store_true",
                     help="end a request when its last four tokens repeat the four before (the reference does unless BN_DISABLE_LOOP_ABORT is set)")
     from .engine import diagnostics
+    ap.add_argument("--plugin", action="append", default=[], metavar="MODULE",
+                    help="a Python module to import before the model is read: it may register parts or a whole "
+                         "architecture of its own (may be repeated)")
     diagnostics.add_arguments(ap)
     return ap
 
@@ -73,6 +76,7 @@ def main(argv=None) -> int:
     import bitnet_c_b200 as bn
     from .engine.batch import SeqStep
 
+    bn.load_plugins(args.plugin)
     if args.random_weights:
         if not args.config:
             raise SystemExit("--random-weights needs --config <config.json>")

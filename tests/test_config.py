@@ -65,7 +65,7 @@ def test_missing_key_and_unknown_architecture(tmp_path):
         architecture("MambaForCausalLM")
     with pytest.raises(ConfigError, match="architectures"):
         architecture_of({"hidden_size": 8})
-    assert known_architectures() == ["LlamaForCausalLM"]
+    assert "LlamaForCausalLM" in known_architectures()  # (another test file registers a toy architecture of its own)
     p = tmp_path / "config.json"
     p.write_text("{ not json")
     with pytest.raises(ConfigError, match="not valid JSON"):
