@@ -23,7 +23,7 @@ import sys
 import tempfile
 import threading
 import time
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, Iterable, List
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
