@@ -807,8 +807,18 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         return out
     if M <= SKINNY_MAX_ROWS and K % 8 == 0:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        # a matrix with few rows shares its inner dimension out over several blocks (a property of the matrix alone)
+        n_splits = getattr(build.library("linear"), "bn_linear_skinny_splits")
+        n_splits.restype = c_int
+        splits = n_splits(c_int(N), c_int(K))
+        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
         _check(_fn("linear", "bn_linear_skinny")(_ptr(x), _ptr(w), c_int(_code(w)), _ptr(out), c_int(_DT[out_dtype]),
-                                                 c_int(M), c_int(N), c_int(K), c_int(N), _stream()), "linear_skinny")
+                                                 c_int(M), c_int(N), c_int(K), c_int(N),
+                                                 _ptr(partial) if partial is not None else c_void_p(None), _stream()),
+               "linear_skinny")
+        if splits > 1:
+            global LAUNCHES
+            LAUNCHES += 1  # the kernel that adds the splits
     else:
         # Many rows: the library product, float32 accumulation, no reduced-precision float32 mode.
         if w.dtype == torch.float32:
