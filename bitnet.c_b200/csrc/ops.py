@@ -45,6 +45,10 @@ def _stream() -> c_void_p:
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    # the usual case in one test (a launch asks this of ten tensors); what fails it is named below
+    if (t.__class__ is torch.Tensor and t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype is dtype)
+            and (dims is None or t.dim() == dims)):
+        return
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
     if not t.is_contiguous():
@@ -77,14 +81,27 @@ def _timed(key: str, call):
     return out
 
 
+_entry_points = {}  # (family, name) -> the library's entry point, its result type set
+
+
 def _fn(family: str, name: str):
     global LAUNCHES
     LAUNCHES += 1
-    f = getattr(build.library(family), name)
-    f.restype = c_int
+    f = _entry_points.get((family, name))
+    if f is None:
+        f = getattr(build.library(family), name)
+        f.restype = c_int
+        _entry_points[(family, name)] = f
     if PROFILE is not None:
         return lambda *args: _timed(f"{family}.{name}", lambda: f(*args))
     return f
+
+
+# Arguments that never change, made once: building a ctypes object costs a fifth of a microsecond, and
+# a launch has twenty of them.  (Python ints go to C as int without a wrapper; pointers need c_void_p,
+# an int would be cut to 32 bits; floats need c_float.)
+_NULL = c_void_p(None)
+_F0 = c_float(0.0)
 
 
 # ---- embedding ----------------------------------------------------------------------------
@@ -538,6 +555,17 @@ def tc_status(device) -> torch.Tensor:
     return got
 
 
+_tc_status_ptr = {}
+
+
+def _tc_status_arg(device: torch.device) -> c_void_p:
+    """The status word of ``device`` as a launch argument (made once per device)."""
+    got = _tc_status_ptr.get(device.index)
+    if got is None:
+        got = _tc_status_ptr[device.index] = _ptr(tc_status(device))
+    return got
+
+
 def check_tc_status(device) -> None:
     """Raise if a TMA-fed kernel on ``device`` reported a wait that gave up (synchronises)."""
     code = int(tc_status(device).item())
@@ -594,30 +622,33 @@ USE_FUSED_NORM = True  # products of few rows add to the residual and prepare th
 
 
 def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-              cluster: int = 0, sink: Optional[NormSink] = None):
+              cluster: int = 0, sink: Optional[NormSink] = None, _checked: bool = False):
     """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands.
     ``cluster`` blocks (1 to 8) share the inner dimension of each 128-row tile of w and add their
     parts up through distributed shared memory (0: chosen from the number of tiles).  ``x`` may be
     ``RowScaled``.  With ``sink`` the product is added to ``sink.residual`` in place and the result
-    is the ``RowScaled`` output of the norm that follows."""
+    is the ``RowScaled`` output of the norm that follows.  (``_checked``: ``linear`` has looked at w
+    and at the sizes already.)"""
     scaled = x if isinstance(x, RowScaled) else None
     if scaled is not None:
         x = scaled.x
     _need(x, "x", torch.bfloat16, 2)
-    _need(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or M > TC_MAX_ROWS or K % 8 or (swiglu and N % 16) or not 0 <= cluster <= 8:
-        raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, cluster {cluster} not supported")
+    if not _checked:
+        _need(w, "w", torch.bfloat16, 2)
+        if w.shape[1] != K or M > TC_MAX_ROWS or K % 8 or (swiglu and N % 16) or not 0 <= cluster <= 8:
+            raise KernelError(f"linear_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, cluster {cluster} not supported")
     fn = _fn("linear_tc", "bn_linear_tc_ex")
+    dev = x.device
     if scaled is not None:
-        _need(scaled.ss, "ss", torch.float32, 2)
-        if scaled.ss.shape[1] < M or scaled.width != K:
-            raise KernelError(f"linear_tc: row sums {tuple(scaled.ss.shape)} of width {scaled.width} do not fit x {tuple(x.shape)}")
-        row = (_ptr(scaled.ss), c_int(scaled.ss.shape[0]), c_int(scaled.ss.shape[1]), c_float(1.0 / scaled.width),
-               c_float(scaled.eps))
+        ss_rows = scaled.ss
+        _need(ss_rows, "ss", torch.float32, 2)
+        if ss_rows.shape[1] < M or scaled.width != K:
+            raise KernelError(f"linear_tc: row sums {tuple(ss_rows.shape)} of width {scaled.width} do not fit x {tuple(x.shape)}")
+        row = (c_void_p(ss_rows.data_ptr()), ss_rows.shape[0], ss_rows.shape[1], c_float(1.0 / scaled.width), c_float(scaled.eps))
     else:
-        row = (c_void_p(None), c_int(0), c_int(0), c_float(0.0), c_float(0.0))
+        row = (_NULL, 0, 0, _F0, _F0)
     if sink is not None:
         res = sink.residual
         _need(res, "residual", torch.float32, 2)
@@ -626,23 +657,32 @@ def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swigl
             raise KernelError(f"linear_tc: residual {tuple(res.shape)} / norm weight {tuple(sink.weight.shape)} do not fit "
                               f"a product [{M}, {N}]")
         if cluster == 0:
-            f = getattr(build.library("linear_tc"), "bn_linear_tc_auto_cluster")
-            f.restype = c_int
-            cluster = int(f(c_int(N), c_int(K)))
+            cluster = _auto_cluster(N, K)
         tiles = (N + 127) // 128
-        xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        ss = torch.empty((tiles * cluster, M), dtype=torch.float32, device=x.device)
-        _check(fn(_ptr(x), _ptr(w), _ptr(res), c_int(_DT[torch.float32]), c_int(M), c_int(N), c_int(K), c_int(N), c_int(3),
-                  c_int(cluster), *row, _ptr(sink.weight), c_int(_DT[sink.weight.dtype]), _ptr(xg), _ptr(ss), c_int(M),
-                  _ptr(tc_status(x.device)), _stream()), "linear_tc")
+        xg = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        ss = torch.empty((tiles * cluster, M), dtype=torch.float32, device=dev)
+        _check(fn(c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_void_p(res.data_ptr()), 0, M, N, K, N, 3,
+                  cluster, *row, c_void_p(sink.weight.data_ptr()), _DT[sink.weight.dtype], c_void_p(xg.data_ptr()),
+                  c_void_p(ss.data_ptr()), M, _tc_status_arg(dev), _stream()), "linear_tc")
         return RowScaled(xg, ss, N, sink.eps)
     out_dtype = out_dtype or x.dtype
     cols = N // 2 if swiglu else N
-    out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
-    _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(cols),
-              c_int(2 if swiglu else 0), c_int(cluster), *row, c_void_p(None), c_int(0), c_void_p(None), c_void_p(None),
-              c_int(0), _ptr(tc_status(x.device)), _stream()), "linear_tc")
+    out = torch.empty((M, cols), dtype=out_dtype, device=dev)
+    _check(fn(c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), _DT[out_dtype], M, N, K, cols,
+              2 if swiglu else 0, cluster, *row, _NULL, 0, _NULL, _NULL, 0, _tc_status_arg(dev), _stream()), "linear_tc")
     return out
+
+
+_auto_clusters = {}  # (N, K) -> how many blocks share a tile's inner dimension (a property of the sizes and the device)
+
+
+def _auto_cluster(N: int, K: int) -> int:
+    got = _auto_clusters.get((N, K))
+    if got is None:
+        f = getattr(build.library("linear_tc"), "bn_linear_tc_auto_cluster")
+        f.restype = c_int
+        got = _auto_clusters[(N, K)] = int(f(c_int(N), c_int(K)))
+    return got
 
 
 # Many-row bfloat16 products on this library's tcgen05 kernel (gemm_tc.cu) instead of the library product
@@ -765,7 +805,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
     fast = streams and x.dtype == torch.bfloat16
     if sink is not None:
         if fast and USE_FUSED_NORM and not swiglu and tuple(sink.residual.shape) == (M, N):
-            return linear_tc(x, w, sink=sink)
+            return linear_tc(x, w, sink=sink, _checked=True)
         if (not swiglu and not isinstance(x, RowScaled) and tuple(sink.residual.shape) == (M, N)
                 and _own_gemm_fits(x, w, False, None, "sink") and not partial_sums):
             return gemm_tc(x, w, sink=sink)
@@ -774,7 +814,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         return add_rmsnorm(sink.residual, delta, sink.weight, sink.eps, normed)
     if isinstance(x, RowScaled):
         if fast:
-            return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
+            return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu, _checked=True)
         if _own_gemm_fits(x.x, w, swiglu, out_dtype, "scaled") and not partial_sums:
             return gemm_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
         x = x.dense()
@@ -783,7 +823,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
     if x.dtype != w.dtype:
         x = x.to(w.dtype)
     if streams:
-        return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
+        return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu, _checked=True)
     if _own_gemm_fits(x, w, swiglu, out_dtype, "swiglu" if swiglu else "plain") and not partial_sums:
         return gemm_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
     if small:
