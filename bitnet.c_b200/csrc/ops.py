@@ -115,8 +115,8 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, b
     n, width = tokens.shape[0], table.shape[1]
     if out.shape[0] < n or out.shape[1] != width:
         raise KernelError(f"out {tuple(out.shape)} does not hold {n} rows of width {width}")
-    _check(_fn("embed", "bn_embed_gather")(_ptr(table), _code(table), _ptr(tokens), _ptr(out), c_int(n),
-                                           c_int(width), c_int(table.shape[0]), c_float(scale),
+    _check(_fn("embed", "bn_embed_gather")(_ptr(table), _code(table), _ptr(tokens), _ptr(out), int(n),
+                                           int(width), int(table.shape[0]), c_float(scale),
                                            _ptr(bad_token), _stream()), "embed_gather")
     return out
 
@@ -146,10 +146,10 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         n_rows = x.shape[0]
     if out.shape[0] < n_rows:
         raise KernelError(f"out has {out.shape[0]} rows, {n_rows} are written")
-    _check(_fn("norm", "bn_add_rmsnorm")(_ptr(x), _ptr(delta), c_int(_code(delta) if delta is not None else 0),
-                                         c_int(n_parts), ctypes.c_longlong(part_stride), _ptr(weight), c_int(_code(weight)), _ptr(out), c_int(_code(out)),
-                                         _ptr(rows), c_int(n_rows), c_int(width), c_float(eps),
-                                         c_int(1 if write_x else 0), _stream()), "add_rmsnorm")
+    _check(_fn("norm", "bn_add_rmsnorm")(_ptr(x), _ptr(delta), int(_code(delta) if delta is not None else 0),
+                                         int(n_parts), ctypes.c_longlong(part_stride), _ptr(weight), int(_code(weight)), _ptr(out), int(_code(out)),
+                                         _ptr(rows), int(n_rows), int(width), c_float(eps),
+                                         int(1 if write_x else 0), _stream()), "add_rmsnorm")
     return out
 
 
@@ -170,7 +170,7 @@ def silu_mul(h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     inter = h.shape[1] // 2
     if h.shape[1] != 2 * inter or out.shape != (h.shape[0], inter):
         raise KernelError(f"silu_mul: h {tuple(h.shape)} and out {tuple(out.shape)} do not fit")
-    _check(_fn("act", "bn_silu_mul")(_ptr(h), _ptr(out), c_int(_code(h)), c_int(h.shape[0]), c_int(inter),
+    _check(_fn("act", "bn_silu_mul")(_ptr(h), _ptr(out), int(_code(h)), int(h.shape[0]), int(inter),
                                      _stream()), "silu_mul")
     return out
 
@@ -208,10 +208,10 @@ def rope_append(x: torch.Tensor, n_rot_heads: int, head_dim: int, rotary_dims: i
         if max(k_off, v_off) + n_kv_heads * head_dim > x.shape[1]:
             raise KernelError("rope_append: key/value offsets run past the row")
         pt_stride = page_table.shape[1]
-    _check(_fn("rope", "bn_rope_append")(_ptr(x), c_int(_code(x)), c_int(n), c_int(x.shape[1]), c_int(n_rot_heads),
-                                         c_int(head_dim), c_int(rotary_dims), c_float(theta_scale), _ptr(tok_pos),
-                                         c_int(k_off), c_int(v_off), c_int(n_kv_heads), _ptr(tok_seq), _ptr(slots),
-                                         _ptr(page_table), c_int(pt_stride), _ptr(k_cache), _ptr(v_cache),
+    _check(_fn("rope", "bn_rope_append")(_ptr(x), int(_code(x)), int(n), int(x.shape[1]), int(n_rot_heads),
+                                         int(head_dim), int(rotary_dims), c_float(theta_scale), _ptr(tok_pos),
+                                         int(k_off), int(v_off), int(n_kv_heads), _ptr(tok_seq), _ptr(slots),
+                                         _ptr(page_table), int(pt_stride), _ptr(k_cache), _ptr(v_cache),
                                          _stream()), "rope_append")
 
 
@@ -238,9 +238,9 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     if out.shape[0] < n_tokens or out.shape[1] != n_heads * head_dim:
         raise KernelError("attention: out does not fit")
     _check(_fn("attention", "bn_attention_general")(
-        _ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), c_int(_code(q)), c_int(n_tokens), c_int(n_heads),
-        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), _ptr(tok_seq), _ptr(tok_pos),
-        _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()),
+        _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
+        int(n_kv_heads), int(head_dim), c_float(scale), int(window), _ptr(tok_seq), _ptr(tok_pos),
+        _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()),
         "attention_general")
     return out
 
@@ -267,9 +267,9 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     if out.shape[1] != n_heads * head_dim or q_stride % 8:
         raise KernelError("attention_prefill: out or q_stride does not fit")
     _check(_fn("attention_prefill", "bn_attention_prefill")(
-        _ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), c_int(tile_seq.shape[0]), c_int(n_heads),
-        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), _ptr(tile_seq), _ptr(tile_row0),
-        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
+        _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
+        int(n_kv_heads), int(head_dim), c_float(scale), int(window), _ptr(tile_seq), _ptr(tile_row0),
+        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache),
         _ptr(v_cache), _stream()), "attention_prefill")
     return out
 
@@ -300,10 +300,10 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_he
     if out.shape[1] != n_heads * head_dim or q_stride % 8 or n_heads * head_dim > q_stride or out.shape[0] < q.shape[0]:
         raise KernelError("attention_prefill_tc: out or q_stride does not fit")
     _check(_fn("attention_prefill_tc", "bn_attention_prefill_tc")(
-        _ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), c_int(out.shape[1]), c_int(tile_seq.shape[0]),
-        c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), _ptr(tile_seq), _ptr(tile_row0),
-        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
-        _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(tc_status(q.device)), _stream()), "attention_prefill_tc")
+        _ptr(q), int(q_stride), int(q.shape[0]), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]),
+        int(n_heads), int(n_kv_heads), int(head_dim), c_float(scale), int(window), _ptr(tile_seq), _ptr(tile_row0),
+        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache),
+        _ptr(v_cache), int(k_cache.shape[0]), _ptr(tc_status(q.device)), _stream()), "attention_prefill_tc")
     return out
 
 
@@ -333,9 +333,9 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_seqs: 
     part_o = torch.empty((n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
     _check(_fn("attention_decode", "bn_attention_decode")(
-        _ptr(q), c_int(q_stride), _ptr(out), c_int(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads),
-        c_int(head_dim), c_float(scale), c_int(window), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
-        c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part_o), _ptr(part_ml), c_int(n_splits),
+        _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(n_seqs), int(n_heads), int(n_kv_heads),
+        int(head_dim), c_float(scale), int(window), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
+        int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part_o), _ptr(part_ml), int(n_splits),
         _stream()), "attention_decode")
     return out
 
@@ -469,11 +469,11 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
         part_ml = torch.empty((n_seqs * n_heads * item_group * 2,), dtype=torch.float32, device=qkv.device)
         _scr, counters = _split_scratch(qkv.device)
         _check(_fn("attention_decode_tc", "bn_attention_decode_tc_items")(
-            _ptr(qkv), c_int(qkv.shape[1]), c_int(k_off), c_int(v_off), _ptr(out), c_int(out.shape[1]), c_int(n_seqs),
-            c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(rotary_dims),
-            c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
-            _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(tc_status(qkv.device)), _ptr(part_o), _ptr(part_ml), _ptr(counters),
-            c_int(counters.numel()), _ptr(items), c_int(items.shape[0]), c_int(item_group), _stream()), "attention_decode_fused")
+            _ptr(qkv), int(qkv.shape[1]), int(k_off), int(v_off), _ptr(out), int(out.shape[1]), int(n_seqs),
+            int(n_heads), int(n_kv_heads), int(head_dim), c_float(scale), int(window), int(rotary_dims),
+            c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache),
+            _ptr(v_cache), int(k_cache.shape[0]), _ptr(tc_status(qkv.device)), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+            int(counters.numel()), _ptr(items), int(items.shape[0]), int(item_group), _stream()), "attention_decode_fused")
         return out
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     blocks_per_split = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
@@ -486,12 +486,12 @@ def attention_decode_fused(qkv: torch.Tensor, k_off: int, v_off: int, out: torch
     part_ml = torch.empty((n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
     _scr, counters = _split_scratch(qkv.device)
     _check(_fn("attention_decode_tc", "bn_attention_decode_tc")(
-        _ptr(qkv), c_int(qkv.shape[1]), c_int(k_off), c_int(v_off), _ptr(out), c_int(out.shape[1]), c_int(n_seqs),
-        c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(rotary_dims),
-        c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache),
-        _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(tc_status(qkv.device)), _ptr(part_o), _ptr(part_ml), c_int(n_splits),
-        c_int(pages_per_block), _ptr(counters),
-        c_int(counters.numel()), _stream()), "attention_decode_fused")
+        _ptr(qkv), int(qkv.shape[1]), int(k_off), int(v_off), _ptr(out), int(out.shape[1]), int(n_seqs),
+        int(n_heads), int(n_kv_heads), int(head_dim), c_float(scale), int(window), int(rotary_dims),
+        c_float(theta_scale), _ptr(tok_pos), _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache),
+        _ptr(v_cache), int(k_cache.shape[0]), _ptr(tc_status(qkv.device)), _ptr(part_o), _ptr(part_ml), int(n_splits),
+        int(pages_per_block), _ptr(counters),
+        int(counters.numel()), _stream()), "attention_decode_fused")
     return out
 
 
@@ -681,7 +681,7 @@ def _auto_cluster(N: int, K: int) -> int:
     if got is None:
         f = getattr(build.library("linear_tc"), "bn_linear_tc_auto_cluster")
         f.restype = c_int
-        got = _auto_clusters[(N, K)] = int(f(c_int(N), c_int(K)))
+        got = _auto_clusters[(N, K)] = int(f(int(N), int(K)))
     return got
 
 
@@ -725,10 +725,10 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu:
         _need(scaled.ss, "ss", torch.float32, 2)
         if scaled.ss.shape[1] < M or scaled.width != K:
             raise KernelError(f"gemm_tc: row sums {tuple(scaled.ss.shape)} of width {scaled.width} do not fit x {tuple(x.shape)}")
-        row = (_ptr(scaled.ss), c_int(scaled.ss.shape[0]), c_int(scaled.ss.shape[1]), c_float(1.0 / scaled.width),
+        row = (_ptr(scaled.ss), int(scaled.ss.shape[0]), int(scaled.ss.shape[1]), c_float(1.0 / scaled.width),
                c_float(scaled.eps))
     else:
-        row = (c_void_p(None), c_int(0), c_int(0), c_float(0.0), c_float(0.0))
+        row = (c_void_p(None), int(0), int(0), c_float(0.0), c_float(0.0))
     status = _ptr(tc_status(x.device))
     if sink is not None:
         res = sink.residual
@@ -740,17 +740,17 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu:
         xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         parts = getattr(build.library("gemm_tc"), "bn_gemm_tc_parts")
         parts.restype = c_int
-        ss = torch.empty((parts(c_int(N)), M), dtype=torch.float32, device=x.device)
-        _check(fn(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), c_void_p(None), c_int(0), c_int(0), c_int(3), *row,
-                  _ptr(res), _ptr(sink.weight), c_int(_DT[sink.weight.dtype]), _ptr(xg), _ptr(ss), c_int(M), status,
+        ss = torch.empty((parts(int(N)), M), dtype=torch.float32, device=x.device)
+        _check(fn(_ptr(x), _ptr(w), int(M), int(N), int(K), c_void_p(None), int(0), int(0), int(3), *row,
+                  _ptr(res), _ptr(sink.weight), int(_DT[sink.weight.dtype]), _ptr(xg), _ptr(ss), int(M), status,
                   _stream()), "gemm_tc")
         return RowScaled(xg, ss, N, sink.eps)
     out_dtype = out_dtype or x.dtype
     cols = N // 2 if swiglu else N
     out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
-    _check(fn(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), _ptr(out), c_int(_DT[out_dtype]), c_int(cols),
-              c_int(2 if swiglu else 0), *row, c_void_p(None), c_void_p(None), c_int(0), c_void_p(None), c_void_p(None),
-              c_int(0), status, _stream()), "gemm_tc")
+    _check(fn(_ptr(x), _ptr(w), int(M), int(N), int(K), _ptr(out), int(_DT[out_dtype]), int(cols),
+              int(2 if swiglu else 0), *row, c_void_p(None), c_void_p(None), int(0), c_void_p(None), c_void_p(None),
+              int(0), status, _stream()), "gemm_tc")
     return out
 
 
@@ -759,7 +759,7 @@ def gemm_pairs(on: Optional[bool] = None) -> bool:
     alone; with an argument, sets it.  Returns the setting before the call."""
     f = getattr(build.library("gemm_tc"), "bn_gemm_tc_pairs")
     f.restype = c_int
-    return bool(f(c_int(-1 if on is None else int(bool(on)))))
+    return bool(f(int(-1 if on is None else int(bool(on)))))
 
 
 def _own_gemm_fits(x, w: torch.Tensor, swiglu: bool, out_dtype, kind: str) -> bool:
@@ -830,30 +830,30 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         fn = _fn("linear_mma", "bn_linear_mma")
         splits = _mma_splits(M, N, K, n_sms(x.device))
         scratch, counters = _split_scratch(x.device)
-        tail = (_ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters), c_int(counters.numel()), _stream())
+        tail = (_ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters), int(counters.numel()), _stream())
         if swiglu:
             out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
-            _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(N // 2),
-                      c_int(2), c_int(splits), *tail), "linear_mma")
+            _check(fn(_ptr(x), _ptr(w), _ptr(out), int(_DT[out_dtype]), int(M), int(N), int(K), int(N // 2),
+                      int(2), int(splits), *tail), "linear_mma")
             return out
         if partial_sums and splits > 1:
             out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
-            _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(0), c_int(M), c_int(N), c_int(K), c_int(N), c_int(1),
-                      c_int(splits), *tail), "linear_mma")
+            _check(fn(_ptr(x), _ptr(w), _ptr(out), int(0), int(M), int(N), int(K), int(N), int(1),
+                      int(splits), *tail), "linear_mma")
             return out
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        _check(fn(_ptr(x), _ptr(w), _ptr(out), c_int(_DT[out_dtype]), c_int(M), c_int(N), c_int(K), c_int(N), c_int(0),
-                  c_int(splits), *tail), "linear_mma")
+        _check(fn(_ptr(x), _ptr(w), _ptr(out), int(_DT[out_dtype]), int(M), int(N), int(K), int(N), int(0),
+                  int(splits), *tail), "linear_mma")
         return out
     if M <= SKINNY_MAX_ROWS and K % 8 == 0:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         # a matrix with few rows shares its inner dimension out over several blocks (a property of the matrix alone)
         n_splits = getattr(build.library("linear"), "bn_linear_skinny_splits")
         n_splits.restype = c_int
-        splits = n_splits(c_int(N), c_int(K))
+        splits = n_splits(int(N), int(K))
         partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
-        _check(_fn("linear", "bn_linear_skinny")(_ptr(x), _ptr(w), c_int(_code(w)), _ptr(out), c_int(_DT[out_dtype]),
-                                                 c_int(M), c_int(N), c_int(K), c_int(N),
+        _check(_fn("linear", "bn_linear_skinny")(_ptr(x), _ptr(w), int(_code(w)), _ptr(out), int(_DT[out_dtype]),
+                                                 int(M), int(N), int(K), int(N),
                                                  _ptr(partial) if partial is not None else c_void_p(None), _stream()),
                "linear_skinny")
         if splits > 1:
@@ -888,7 +888,7 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
         raise KernelError(f"argmax: at most {counters.numel()} rows at a time")
     part_v = torch.empty(n * 64, dtype=torch.float32, device=logits.device)
     part_i = torch.empty(n * 64, dtype=torch.int32, device=logits.device)
-    _check(_fn("sampling", "bn_argmax")(_ptr(logits), c_int(logits.shape[1]), c_int(n), c_int(logits.shape[1]),
+    _check(_fn("sampling", "bn_argmax")(_ptr(logits), int(logits.shape[1]), int(n), int(logits.shape[1]),
                                         _ptr(out), _ptr(part_v), _ptr(part_i), _ptr(counters), _stream()), "argmax")
     return out
 
@@ -905,8 +905,8 @@ def sample_temperature(logits: torch.Tensor, temperature: float, rng_state: torc
         raise KernelError("sample_temperature: one generator state per row is needed")
     out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, 1)
-    _check(_fn("sampling", "bn_sample_temperature")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
-                                                    c_int(logits.shape[1]), c_float(temperature), _ptr(rng_state),
+    _check(_fn("sampling", "bn_sample_temperature")(_ptr(logits), int(logits.shape[1]), int(logits.shape[0]),
+                                                    int(logits.shape[1]), c_float(temperature), _ptr(rng_state),
                                                     _ptr(index), _ptr(out), _stream()), "sample_temperature")
     return out
 
@@ -927,8 +927,8 @@ def sample_topp(logits: torch.Tensor, temperature: float, topp: float, rng_state
         raise KernelError("sample_topp: probs scratch does not fit")
     out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, 1)
-    _check(_fn("sampling", "bn_sample_topp")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
-                                             c_int(logits.shape[1]), c_float(temperature), c_float(topp),
+    _check(_fn("sampling", "bn_sample_topp")(_ptr(logits), int(logits.shape[1]), int(logits.shape[0]),
+                                             int(logits.shape[1]), c_float(temperature), c_float(topp),
                                              _ptr(rng_state), _ptr(index), _ptr(probs), _ptr(out), _stream()),
            "sample_topp")
     return out
@@ -943,8 +943,8 @@ def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch
     _need(recent_len, "recent_len", torch.int32, 1)
     if index is not None:
         _need(index, "index", torch.int32, 1)
-    _check(_fn("sampling", "bn_repeat_penalty")(_ptr(logits), c_int(logits.shape[1]), c_int(logits.shape[0]),
-                                                c_int(logits.shape[1]), _ptr(recent), c_int(recent.shape[1]),
+    _check(_fn("sampling", "bn_repeat_penalty")(_ptr(logits), int(logits.shape[1]), int(logits.shape[0]),
+                                                int(logits.shape[1]), _ptr(recent), int(recent.shape[1]),
                                                 _ptr(recent_len), _ptr(index), c_float(penalty), _stream()),
            "repeat_penalty")
 
@@ -958,6 +958,6 @@ def sampler_accept(recent: torch.Tensor, recent_len: torch.Tensor, recent_pos: t
     _need(tokens, "tokens", torch.int32, 1)
     if index is not None:
         _need(index, "index", torch.int32, 1)
-    _check(_fn("sampling", "bn_sampler_accept")(_ptr(recent), c_int(recent.shape[1]), _ptr(recent_len),
-                                                _ptr(recent_pos), _ptr(index), _ptr(tokens), c_int(tokens.shape[0]),
+    _check(_fn("sampling", "bn_sampler_accept")(_ptr(recent), int(recent.shape[1]), _ptr(recent_len),
+                                                _ptr(recent_pos), _ptr(index), _ptr(tokens), int(tokens.shape[0]),
                                                 _stream()), "sampler_accept")
